@@ -1,0 +1,329 @@
+"""Benchmark: faces/s of the INT8 IR-ResNet50 (ArcFace r50) forward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
+
+One process per GPU (torchrun sets RANK/LOCAL_RANK/WORLD_SIZE); faces are independent,
+so every rank runs its own batch stream with no data-path collective ("weak" scaling:
+per-GPU work is fixed).  A step is one forward pass over one batch of B seeded
+synthetic faces through the seeded synthetic model (the reference's shipped weights are
+not redistributable).  Rank 0 prints ONE JSON line.
+
+  value : faces/s with the fp32 input batch already resident in HBM, K steps timed with
+          CUDA events on the library's compute stream, max over ranks.
+  e2e   : faces/s through the public C API (fastface_embed_batch) with pinned HOST
+          buffers: H2D of the fp32 faces and D2H of the embeddings inside the timed region.
+  roofline : the tensor-core implicit-GEMM kernel (every conv but the stem, and the FC),
+          algorithmic int8 ops of those launches / their summed CUDA-event time, against
+          2 x the measured dense bf16 peak (int8 runs at twice the bf16 rate).
+  cpu_baseline : the reference's own batched CLI (compiled from its sources into
+          oracle/_ref/) timed on this host through its --server protocol, N=1 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "faces/sec (IR-ResNet50 INT8, 112x112)"
+GOP_PER_FACE = 12.619          # 6.3093 GMAC: 53 convs + FC, real K, no padding
+FACE_BYTES = 112 * 112 * 3 * 4
+EMB_BYTES = 512 * 4
+
+
+def rank_env():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+
+
+class Clocks:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu: int):
+        self.gpu, self.rows, self.proc = gpu, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].startswith("Active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def load_measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d.get("hbm_gbs"), "bf16_burst": d.get("bf16_tflops"),
+                "bf16_sustained": d.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+def layer_ops(l, batch):
+    """Algorithmic int8 ops (2 x MAC, real K) of one launch of the tensor-core kernel."""
+    if l["kind"] == 3:
+        return 2.0 * batch * l["Cin"] * l["Cout"]
+    return 2.0 * batch * l["Ho"] * l["Wo"] * l["Cout"] * l["Cin"] * l["Kh"] * l["Kw"]
+
+
+def reference_server_rate(model_root, ffw4, batch, steps, warmup, budget_s, threads):
+    """faces/s of the reference's fastface_int8_batched through its --server protocol
+    (arcface_forward_int8_batched.c:531-553): write B faces to stdin, read B embeddings."""
+    from fastface_b200 import synth
+    from oracle import ffo
+    exe = os.path.join(ffo.REF_DIR, "fastface_int8_batched")
+    env = dict(os.environ, OMP_NUM_THREADS=str(threads))
+    env.pop("OPSC2_PATH", None)
+    faces = synth.faces(batch, seed=1).tobytes()
+    p = subprocess.Popen([exe, os.path.abspath(ffw4), "--batch", str(batch), "--server"], cwd=model_root, env=env,
+                         stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, bufsize=0)
+
+    def one():
+        p.stdin.write(faces)
+        p.stdin.flush()
+        need, got = batch * EMB_BYTES, 0
+        while got < need:
+            chunk = p.stdout.read(need - got)
+            if not chunk:
+                raise RuntimeError("reference server closed its pipe")
+            got += len(chunk)
+
+    try:
+        for _ in range(warmup):
+            one()
+        t0 = time.perf_counter()
+        done = 0
+        for _ in range(steps):
+            one()
+            done += 1
+            if time.perf_counter() - t0 > budget_s:
+                break
+        dt = time.perf_counter() - t0
+    finally:
+        try:
+            p.stdin.close()
+            p.wait(timeout=10)
+        except Exception:
+            p.kill()
+    return done * batch / dt, done, dt
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_baseline(model_root, ffw4, batch=8, steps=12, warmup=1, budget_s=25.0):
+    """Reference CPU path on this host: the compiled reference when it can run here,
+    else the plain-C oracle port (single box, bounded sample)."""
+    from fastface_b200 import synth
+    from oracle import ffo
+    threads = host_threads()
+    if ffo.ref_available() and os.path.exists(os.path.join(ffo.REF_DIR, "fastface_int8_batched")):
+        rate, done, dt = reference_server_rate(model_root, ffw4, batch, steps, warmup, budget_s, threads)
+        return {"value": round(rate, 2), "unit": "faces/s", "cores": threads, "kind": "reference",
+                "sample": f"reference fastface_int8_batched --batch {batch} --server, {done} batches in {dt:.1f} s, "
+                          f"OMP_NUM_THREADS={threads}, avx_vnni=yes"}
+    orc = ffo.Oracle(ffw4, os.path.join(model_root, "models", "op_scales.bin"),
+                     os.path.join(model_root, "models", "op_scales_v2.bin"))
+    faces = synth.faces(batch, seed=1)
+    orc.forward(faces[:1])
+    t0 = time.perf_counter()
+    done = 0
+    while done < steps and time.perf_counter() - t0 < budget_s:
+        orc.forward(faces)
+        done += 1
+    dt = time.perf_counter() - t0
+    return {"value": round(done * batch / dt, 2), "unit": "faces/s", "cores": threads, "kind": "port",
+            "sample": f"oracle/ff_oracle.c (scalar C + OpenMP), {done} batches of {batch} in {dt:.1f} s; "
+                      f"compiled reference not runnable here (avx_vnni={'yes' if ffo.host_has_avx_vnni() else 'no'})"}
+
+
+def run_reference_arm(args, rank, world):
+    """--impl reference: the reference's own CPU implementation, rank 0 only."""
+    if rank != 0:
+        return
+    from fastface_b200 import synth
+    batch = args.ref_batch
+    with tempfile.TemporaryDirectory() as root:
+        ffw4 = synth.materialize(root, 0)
+        cb = cpu_baseline(root, ffw4, batch=batch, steps=args.steps, warmup=max(1, args.warmup), budget_s=150.0)
+    rate = cb["value"]
+    line = {"impl": "reference", "metric": METRIC, "value": rate, "unit": "faces/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1000.0 * batch / rate, 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": f"IR-ResNet50 INT8 forward on the host CPU, batch {batch} per step (bounded sample "
+                                   f"of the batch-{args.batch} workload)", "batch_per_step": batch},
+            "cpu_baseline": cb,
+            "e2e": {"value": rate, "unit": "faces/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def pinned_array(shape, dtype=np.float32):
+    """numpy view of page-locked host memory (torch is used only as the allocator)."""
+    import torch
+    t = torch.empty(shape, dtype=torch.float32, pin_memory=True)
+    return t, t.numpy()
+
+
+def run_own_arm(args, rank, local_rank, world):
+    import fastface_b200 as ff
+    from fastface_b200 import synth
+    import torch
+    import torch.distributed as dist
+
+    if world > 1:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    B, K, W = args.batch, args.steps, args.warmup
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    tmp = tempfile.TemporaryDirectory()
+    root = tmp.name
+    ffw4 = synth.materialize(root, 0)
+    eng = ff.FastFace(ffw4, cwd=root, devices=[local_rank], max_batch=B)
+    pin_t, faces = pinned_array((B, 112, 112, 3))
+    faces[...] = synth.faces(B, seed=100 + rank)
+    out_t, out = pinned_array((B, 512))
+
+    # ---- warm-up (>= 3), device-resident and end-to-end ----
+    eng.bench_resident(faces, max(3, W))
+    for _ in range(max(3, W)):
+        eng.embed_into(faces, out)
+
+    # ---- value: K steps, input resident in HBM, CUDA events on the compute stream ----
+    barrier()
+    with Clocks(local_rank) as clk:
+        ms = eng.bench_resident(faces, K)
+        barrier()
+        # ---- e2e: K steps through the public API from pinned host memory ----
+        t0 = time.perf_counter()
+        for _ in range(K):
+            eng.embed_into(faces, out)
+        e2e_s = time.perf_counter() - t0
+    ms = max_over_ranks(ms)
+    e2e_s = max_over_ranks(e2e_s)
+    value = world * K * B / (ms * 1e-3)
+    e2e = world * K * B / e2e_s
+
+    line = None
+    if rank == 0:
+        peaks = load_measured_peaks()
+        layers = eng.layers()
+        per_layer = eng.bench_layers(faces, 3)
+        tc = [(l, t / 3.0) for l, t in zip(layers, per_layer) if l["tensor_core"]]
+        tc_ops = sum(layer_ops(l, B) for l, _ in tc)
+        tc_ms = sum(t for _, t in tc)
+        all_ms = sum(per_layer) / 3.0
+        achieved = tc_ops / (tc_ms * 1e-3) / 1e12 if tc_ms > 0 else 0.0
+        peak = 2.0 * peaks["bf16_sustained"]
+        roof = {"bound": "tensor", "achieved": round(achieved, 1), "peak": round(peak, 1), "unit": "TOP/s",
+                "frac": round(achieved / peak, 4), "traffic": None,
+                "kernel": "conv_tc_kernel (tcgen05 kind::i8 implicit GEMM)",
+                "note": f"{len(tc)} launches per forward, {tc_ops / 1e9:.1f} GOP algorithmic, {tc_ms:.3f} ms summed "
+                        f"CUDA-event time ({100.0 * tc_ms / all_ms:.1f}% of the per-layer total); peak = 2 x bf16 "
+                        f"sustained of {peaks['source']} MEASURED_PEAKS"}
+        clocks = clk.summary()
+        cb = None
+        if world == 1 and not args.no_cpu_baseline:
+            cb = cpu_baseline(root, ffw4)
+        line = {"metric": METRIC, "value": round(value, 1), "unit": "faces/s", "n_gpus": world, "steps": K, "warmup": max(3, W),
+                "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "int8", "data": "synthetic",
+                "config": {"workload": f"IR-ResNet50 (ArcFace r50) INT8 forward, 112x112, batch {B} per GPU per step, "
+                                       f"seeded synthetic weights and faces", "batch_per_gpu": B,
+                           "l2": "per-layer activations at this batch exceed the 126 MB L2",
+                           "parallelism": f"batch sharding x{world}, no collective"},
+                "e2e": {"value": round(e2e, 1), "unit": "faces/s", "h2d_bytes_per_step": B * FACE_BYTES,
+                        "d2h_bytes_per_step": B * EMB_BYTES},
+                "gpu_launches": eng.launches_per_forward * K,
+                "roofline": roof,
+                "roofline_forward": {"achieved_gop_s": round(GOP_PER_FACE * value / world, 1),
+                                     "frac_of_int8_peak": round(GOP_PER_FACE * value / world / 1e3 / peak, 4)},
+                "clocks": clocks}
+        if cb is not None:
+            line["cpu_baseline"] = cb
+        if args.layers:
+            line["layers_ms"] = [{"op": l["op_index"], "kind": l["kind"], "tc": l["tensor_core"], "ms": round(t / 3.0, 4),
+                                  "shape": [l["Cin"], l["Cout"], l["Kh"], l["stride"], l["H"]]} for l, t in zip(layers, per_layer)]
+    eng.close()
+    barrier()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    tmp.cleanup()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=1024)
+    ap.add_argument("--ref-batch", type=int, default=8)
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", action="store_true", help="add per-layer milliseconds to the JSON line")
+    args = ap.parse_args()
+    rank, local_rank, world = rank_env()
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+    if world == 1 and args.gpus > 1:
+        print(json.dumps({"error": "launch with torch.distributed.run for --gpus > 1"}), flush=True)
+        sys.exit(2)
+    run_own_arm(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,547 @@
+// conv_tc.cu -- INT8 implicit-GEMM convolution / FC on the sm_100a tensor cores.
+//
+// Takes over the reference's im2col + VNNI GEMM + fused epilogue
+// (kernels/conv2d_nhwc.c:179-220, kernels/gemm_int8_v2.c:86-110,
+// kernels/int8_epilogue.c:25-112) and, as a 1x1 "conv" over a [B,1,1,K] tensor,
+// the final Linear (kernels/gemm_int8_matvec.c:33-81).
+//
+//   D[128 pixels x BN channels] (int32, TMEM) += A[128 x 32B] (smem) * B[BN x 32B] (smem)
+//
+// * A is never materialised: for each filter tap (kh,kw) and each KC-byte slice of
+//   the input channels one 4-D TMA box {KC, TW, TH, TB} of the NHWC activation
+//   tensor, shifted by the tap, lands in shared memory as 128 K-major rows.
+//   Out-of-bounds rows/columns are zero-filled by TMA (= the conv's zero padding);
+//   stride-2 convs use the tensor map's element strides.
+// * B is the weight matrix repacked [Cout][kh][kw][Cin], a 2-D TMA box {KC, BN}.
+// * tcgen05.mma kind::i8, cta_group::1, M=128, N=BN, K=32 per instruction;
+//   accumulators double-buffered in TMEM so the epilogue of tile i overlaps the
+//   MMAs of tile i+1.
+// * Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (+TMEM alloc),
+//   warps 2..5 = epilogue (tcgen05.ld -> exact fp32 chain -> int8 NHWC stores).
+// * Every wait is bounded; on expiry the kernel records an error word, drains
+//   and frees its TMEM, and returns.  No cluster launch, no multicast.
+
+#include "ffcu_internal.cuh"
+
+#include <stdio.h>
+#include <string.h>
+
+#define TC_THREADS 192
+#define TC_TILE_M 128
+#define TC_MAX_COUT 512
+#define TC_WAIT_NS 2000000000ull   // 2 s per wait
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint64_t globaltimer_ns()
+{
+    uint64_t t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false (and raises the CTA-wide abort flag + the global error
+// word) when the barrier did not flip within TC_WAIT_NS or another role already aborted.
+__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code)
+{
+    if (mbar_try(bar, parity)) return true;
+    uint64_t t0 = globaltimer_ns();
+    for (uint32_t spin = 1;; spin++) {
+        if (mbar_try(bar, parity)) return true;
+        if ((spin & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > TC_WAIT_NS) {
+                *abort_flag = 1;
+                atomicCAS(err, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3)
+{
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the mbarrier once every MMA issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, int (&v)[32])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major shared-memory matrix descriptor: rows of ROWB bytes (= swizzle span), 8-row groups
+// 8*ROWB bytes apart, descriptor version 1 (sm_100), layout 2 = 128B swizzle / 4 = 64B swizzle.
+template <int ROWB>
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr)
+{
+    uint64_t d = (uint64_t)((saddr >> 4) & 0x3fff);
+    d |= (uint64_t)1 << 16;                              // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)((8 * ROWB) >> 4) << 32;              // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                              // version
+    d |= (uint64_t)(ROWB == 128 ? 2 : 4) << 61;          // swizzle mode
+    return d;
+}
+
+// kind::i8 instruction descriptor: D=s32, A=B=s8, both K-major, M=128, N=BN.
+__host__ __device__ constexpr uint32_t idesc_i8(int bn)
+{
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_TILE_M >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------
+// kernel
+// ---------------------------------------------------------------------------
+struct TcParams {
+    EpiTables t;
+    const int8_t* res;
+    int32_t* acc_out;
+    void* out;
+    int* err;
+    int batch, Ho, Wo, Cout;
+    int taps, Kw, cin_blocks, Cp;
+    int stride, pad;
+    int TW, TH, TB;
+    int tiles_w, tiles_h, tiles_b, tiles_n, total_tiles;
+    int stages;
+};
+
+#define TC_MAX_STAGES 8
+
+struct TcShared {                 // lives after the stage ring and the tables
+    uint64_t full[TC_MAX_STAGES];
+    uint64_t empty[TC_MAX_STAGES];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <int BN, int KC, bool CONTRACT, bool OUT_F32>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    // stage ring must start on a 1024-byte boundary (swizzle atoms)
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int A_BYTES = TC_TILE_M * KC;
+    constexpr int B_BYTES = BN * KC;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;    // 128 / 256 / 512: powers of two
+    constexpr uint32_t IDESC = idesc_i8(BN);
+
+    float* tab = (float*)(smem + (size_t)p.stages * STAGE_BYTES);       // [5][Cout]
+    TcShared* sh = (TcShared*)(tab + 5 * TC_MAX_COUT);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int kblocks = p.taps * p.cin_blocks;
+
+    // ---- set-up -----------------------------------------------------------
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; s++) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&sh->acc_full[a]), 1); mbar_init(smem_u32(&sh->acc_empty[a]), 4); }
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    for (int i = threadIdx.x; i < p.Cout; i += TC_THREADS) {
+        tab[0 * TC_MAX_COUT + i] = p.t.w_scale[i];
+        tab[1 * TC_MAX_COUT + i] = p.t.bias[i];
+        tab[2 * TC_MAX_COUT + i] = p.t.slope ? p.t.slope[i] : 0.0f;
+        tab[3 * TC_MAX_COUT + i] = p.t.res_scale ? p.t.res_scale[i] : 0.0f;
+        tab[4 * TC_MAX_COUT + i] = p.t.inv_out ? p.t.inv_out[i] : 0.0f;
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&sh->tmem_base)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+    volatile int* abort_flag = &sh->abort_flag;
+
+    // ---- roles ------------------------------------------------------------
+    if (warp == 0) {
+        if (lane == 0) {
+            // TMA producer
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+                const int tn = tile % p.tiles_n;
+                int m = tile / p.tiles_n;
+                const int tw = m % p.tiles_w; m /= p.tiles_w;
+                const int th = m % p.tiles_h;
+                const int tb = m / p.tiles_h;
+                const int x0 = tw * p.TW * p.stride - p.pad;
+                const int y0 = th * p.TH * p.stride - p.pad;
+                const int b0 = tb * p.TB;
+                const int n0 = tn * BN;
+                for (int kb = 0; kb < kblocks; kb++) {
+                    ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, p.err, FFCU_ERR_EMPTY_TIMEOUT);
+                    if (!ok) break;
+                    const int tap = kb / p.cin_blocks;
+                    const int c0 = (kb - tap * p.cin_blocks) * KC;
+                    const int kh = tap / p.Kw, kw = tap - kh * p.Kw;
+                    const uint32_t bar = smem_u32(&sh->full[stage]);
+                    const uint32_t sa = smem_u32(smem + (size_t)stage * STAGE_BYTES);
+                    mbar_expect_tx(bar, STAGE_BYTES);
+                    tma_load_4d(sa, &mapA, bar, c0, x0 + kw, y0 + kh, b0);
+                    tma_load_2d(sa + A_BYTES, &mapB, bar, tap * p.Cp + c0, n0);
+                    if (++stage == p.stages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // MMA issuer
+            int stage = 0; uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, local++) {
+                const int a = local & 1;
+                const uint32_t aphase = (uint32_t)(local >> 1) & 1;
+                ok = mbar_wait(smem_u32(&sh->acc_empty[a]), aphase ^ 1, abort_flag, p.err, FFCU_ERR_TMEM_TIMEOUT);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
+                for (int kb = 0; kb < kblocks; kb++) {
+                    ok = mbar_wait(smem_u32(&sh->full[stage]), phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + (size_t)stage * STAGE_BYTES);
+                    const uint64_t da = smem_desc<KC>(sa);
+                    const uint64_t db = smem_desc<KC>(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < KC / 32; k++)
+                        umma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, (kb | k) ? 1u : 0u);
+                    umma_commit(smem_u32(&sh->empty[stage]));   // frees the stage once these MMAs have read it
+                    if (++stage == p.stages) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit(smem_u32(&sh->acc_full[a]));
+            }
+        }
+    } else {
+        // epilogue: warp w may only touch TMEM lanes [32*(w%4), 32*(w%4)+32)
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const int iw = row % p.TW;
+        const int ih = (row / p.TW) % p.TH;
+        const int ib = row / (p.TW * p.TH);
+        const bool has_res = (p.res != nullptr) && (p.t.res_scale != nullptr);
+        const bool has_slope = p.t.slope != nullptr;
+        int local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, local++) {
+            const int tn = tile % p.tiles_n;
+            int m = tile / p.tiles_n;
+            const int tw = m % p.tiles_w; m /= p.tiles_w;
+            const int th = m % p.tiles_h;
+            const int tb = m / p.tiles_h;
+            const int ow = tw * p.TW + iw, oh = th * p.TH + ih, b = tb * p.TB + ib;
+            const bool valid = (ow < p.Wo) && (oh < p.Ho) && (b < p.batch);
+            const size_t pix = ((size_t)b * p.Ho + oh) * p.Wo + ow;
+            const int n0 = tn * BN;
+            const int a = local & 1;
+            const uint32_t aphase = (uint32_t)(local >> 1) & 1;
+            ok = mbar_wait(smem_u32(&sh->acc_full[a]), aphase, abort_flag, p.err, FFCU_ERR_EPI_TIMEOUT);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (uint32_t)(a * BN) + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int j = 0; j < BN / 32; j++) {
+                int v[32];
+                tmem_ld32(taddr + (uint32_t)(j * 32), v);
+                if (!valid) continue;
+                const int cb = n0 + j * 32;
+                const size_t o = pix * p.Cout + cb;
+                if (p.acc_out) {
+                    int4* dst = (int4*)(p.acc_out + o);
+#pragma unroll
+                    for (int g = 0; g < 8; g++) dst[g] = make_int4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+                }
+                if (OUT_F32) {
+                    float4* dst = (float4*)((float*)p.out + o);
+#pragma unroll
+                    for (int g = 0; g < 8; g++) {
+                        const float4 ws = *(const float4*)&tab[0 * TC_MAX_COUT + cb + 4 * g];
+                        const float4 bi = *(const float4*)&tab[1 * TC_MAX_COUT + cb + 4 * g];
+                        float4 r;
+                        r.x = ffcu_fc_fp<CONTRACT>(v[4 * g + 0], ws.x, bi.x);
+                        r.y = ffcu_fc_fp<CONTRACT>(v[4 * g + 1], ws.y, bi.y);
+                        r.z = ffcu_fc_fp<CONTRACT>(v[4 * g + 2], ws.z, bi.z);
+                        r.w = ffcu_fc_fp<CONTRACT>(v[4 * g + 3], ws.w, bi.w);
+                        dst[g] = r;
+                    }
+                } else {
+                    int rw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                    if (has_res) {
+                        const int4* rp = (const int4*)(p.res + o);
+                        int4 r0 = rp[0], r1 = rp[1];
+                        rw[0] = r0.x; rw[1] = r0.y; rw[2] = r0.z; rw[3] = r0.w;
+                        rw[4] = r1.x; rw[5] = r1.y; rw[6] = r1.z; rw[7] = r1.w;
+                    }
+                    int ow_[8];
+#pragma unroll
+                    for (int g = 0; g < 8; g++) {
+                        const float4 ws = *(const float4*)&tab[0 * TC_MAX_COUT + cb + 4 * g];
+                        const float4 bi = *(const float4*)&tab[1 * TC_MAX_COUT + cb + 4 * g];
+                        const float4 sl = *(const float4*)&tab[2 * TC_MAX_COUT + cb + 4 * g];
+                        const float4 rs = *(const float4*)&tab[3 * TC_MAX_COUT + cb + 4 * g];
+                        const float4 iv = *(const float4*)&tab[4 * TC_MAX_COUT + cb + 4 * g];
+                        const int r = rw[g];
+                        float f0 = ffcu_conv_fp<CONTRACT>(v[4 * g + 0], ws.x, bi.x, has_res, (int)(int8_t)(r & 0xff), rs.x, has_slope, sl.x);
+                        float f1 = ffcu_conv_fp<CONTRACT>(v[4 * g + 1], ws.y, bi.y, has_res, (int)(int8_t)((r >> 8) & 0xff), rs.y, has_slope, sl.y);
+                        float f2 = ffcu_conv_fp<CONTRACT>(v[4 * g + 2], ws.z, bi.z, has_res, (int)(int8_t)((r >> 16) & 0xff), rs.z, has_slope, sl.z);
+                        float f3 = ffcu_conv_fp<CONTRACT>(v[4 * g + 3], ws.w, bi.w, has_res, (int)(int8_t)((r >> 24) & 0xff), rs.w, has_slope, sl.w);
+                        int q0 = ffcu_requant(f0, iv.x), q1 = ffcu_requant(f1, iv.y);
+                        int q2 = ffcu_requant(f2, iv.z), q3 = ffcu_requant(f3, iv.w);
+                        ow_[g] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
+                    }
+                    int4* dst = (int4*)((int8_t*)p.out + o);
+                    dst[0] = make_int4(ow_[0], ow_[1], ow_[2], ow_[3]);
+                    dst[1] = make_int4(ow_[4], ow_[5], ow_[6], ow_[7]);
+                }
+            }
+            // all of this warp's TMEM reads are complete (tcgen05.wait::ld inside tmem_ld32)
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[a]));
+        }
+    }
+
+    // ---- teardown -----------------------------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        // a wait ran out: give bulk copies still in flight time to land before the
+        // shared memory is handed back (bounded: about 1 ms)
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side: tile geometry, tensor maps, launch
+// ---------------------------------------------------------------------------
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static encode_tiled_fn get_encode()
+{
+    static encode_tiled_fn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (encode_tiled_fn)p;
+    }
+    return fn;
+}
+
+struct TcGeom { int TW, TH, TB; CUtensorMap mapA; bool valid; };
+
+struct TcPlan {
+    ffcu_layer d;
+    int max_batch;
+    int BN, KC, stages, smem_bytes;
+    bool out_f32;
+    const int8_t* d_in;
+    CUtensorMap mapB;
+    int n_sm;
+    TcGeom geoms[8];
+    int n_geoms;
+};
+
+// Output-tile shape {TW, TH, TB} with TW*TH*TB = 128 that wastes the fewest rows for this
+// feature-map size and batch; ties go to the widest tile.
+static void pick_geometry(int Wo, int Ho, int batch, int* TW, int* TH, int* TB)
+{
+    double best = 1e300; int bw = 1, bh = 1, bb = 128;
+    for (int tw = 128; tw >= 1; tw >>= 1)
+        for (int th = 128 / tw; th >= 1; th >>= 1) {
+            int tb = 128 / (tw * th);
+            double padded = (double)((Wo + tw - 1) / tw * tw) * ((Ho + th - 1) / th * th) * ((batch + tb - 1) / tb * tb);
+            if (padded < best) { best = padded; bw = tw; bh = th; bb = tb; }
+        }
+    *TW = bw; *TH = bh; *TB = bb;
+}
+
+static bool encode_A(const TcPlan* p, TcGeom* g)
+{
+    encode_tiled_fn enc = get_encode();
+    if (!enc) { ffcu_set_error("cuTensorMapEncodeTiled is not available"); return false; }
+    const ffcu_layer& d = p->d;
+    const cuuint64_t Cp = (cuuint64_t)d.Cin_pad;
+    cuuint64_t dims[4] = {Cp, (cuuint64_t)d.W, (cuuint64_t)d.H, (cuuint64_t)p->max_batch};
+    cuuint64_t strides[3] = {Cp, Cp * d.W, Cp * d.W * d.H};
+    cuuint32_t box[4] = {(cuuint32_t)p->KC, (cuuint32_t)(g->TW * d.stride), (cuuint32_t)(g->TH * d.stride), (cuuint32_t)g->TB};
+    cuuint32_t estr[4] = {1, (cuuint32_t)d.stride, (cuuint32_t)d.stride, 1};
+    if (d.stride > 1) {      // a unit-extent dimension needs no traversal stride
+        if (g->TW == 1) { box[1] = 1; estr[1] = 1; }
+        if (g->TH == 1) { box[2] = 1; estr[2] = 1; }
+    }
+    CUresult r = enc(&g->mapA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)p->d_in, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     p->KC == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { ffcu_set_error("cuTensorMapEncodeTiled(A) failed: %d", (int)r); return false; }
+    return true;
+}
+
+TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, const int8_t* d_w, int device)
+{
+    if (L.kind != FFCU_CONV && L.kind != FFCU_FC) return nullptr;
+    const int Cp = L.Cin_pad;
+    if (Cp % 64 != 0 || L.Cout % 64 != 0 || L.Cout > TC_MAX_COUT) return nullptr;
+    if (L.stride < 1 || L.stride > 2 || L.Kh * L.Kw > 9) return nullptr;
+    if (L.stride == 2 && getenv("FF_TC_STRIDE2") && atoi(getenv("FF_TC_STRIDE2")) == 0) return nullptr;
+    encode_tiled_fn enc = get_encode();
+    if (!enc) return nullptr;
+    TcPlan* p = new TcPlan();
+    p->d = L; p->max_batch = max_batch; p->d_in = d_in; p->n_geoms = 0;
+    p->out_f32 = (L.kind == FFCU_FC);
+    p->KC = (Cp % 128 == 0) ? 128 : 64;
+    p->BN = L.Cout >= 256 ? 256 : L.Cout;
+    const char* bn_env = getenv("FF_TC_BN");
+    if (bn_env) { int v = atoi(bn_env); if ((v == 64 || v == 128 || v == 256) && L.Cout % v == 0) p->BN = v; }
+    const int stage_bytes = (TC_TILE_M + p->BN) * p->KC;
+    const int fixed = 5 * TC_MAX_COUT * 4 + (int)sizeof(TcShared) + 1024;
+    int stages = (232448 - fixed) / stage_bytes;
+    if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
+    if (stages < 2) { delete p; return nullptr; }
+    p->stages = stages;
+    p->smem_bytes = stages * stage_bytes + fixed;
+    cudaDeviceGetAttribute(&p->n_sm, cudaDevAttrMultiProcessorCount, device);
+    // weights: [Cout][taps*Cp] K-major
+    cuuint64_t Ktot = (cuuint64_t)L.Kh * L.Kw * Cp;
+    cuuint64_t dims[2] = {Ktot, (cuuint64_t)L.Cout};
+    cuuint64_t strides[1] = {Ktot};
+    cuuint32_t box[2] = {(cuuint32_t)p->KC, (cuuint32_t)p->BN};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&p->mapB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)d_w, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     p->KC == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { ffcu_set_error("cuTensorMapEncodeTiled(B) failed: %d", (int)r); delete p; return nullptr; }
+    return p;
+}
+
+void ffcu_tc_free(TcPlan* p) { delete p; }
+
+template <int BN, int KC>
+static int launch_variant(const TcPlan* p, const TcGeom* g, const TcParams& prm, int mode, int grid, cudaStream_t s)
+{
+#define TC_LAUNCH(CONTRACT, F32)                                                                         \
+    do {                                                                                                 \
+        auto kern = conv_tc_kernel<BN, KC, CONTRACT, F32>;                                               \
+        FFCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->smem_bytes)); \
+        kern<<<grid, TC_THREADS, p->smem_bytes, s>>>(g->mapA, p->mapB, prm);                             \
+    } while (0)
+    if (p->out_f32) { if (mode) TC_LAUNCH(true, true); else TC_LAUNCH(false, true); }
+    else            { if (mode) TC_LAUNCH(true, false); else TC_LAUNCH(false, false); }
+#undef TC_LAUNCH
+    FFCU_CHECK(cudaGetLastError());
+    return 0;
+}
+
+int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, const int8_t* res,
+                   int32_t* acc_out, void* out, int* d_err, cudaStream_t s)
+{
+    TcPlan* p = const_cast<TcPlan*>(cp);
+    if (batch < 1 || batch > p->max_batch) { ffcu_set_error("tc launch: batch out of range"); return -1; }
+    const ffcu_layer& d = p->d;
+    int TW, TH, TB;
+    pick_geometry(d.Wo, d.Ho, batch, &TW, &TH, &TB);
+    TcGeom* g = nullptr;
+    for (int i = 0; i < p->n_geoms; i++)
+        if (p->geoms[i].TW == TW && p->geoms[i].TH == TH && p->geoms[i].TB == TB) g = &p->geoms[i];
+    if (!g) {
+        if (p->n_geoms == 8) p->n_geoms = 0;
+        g = &p->geoms[p->n_geoms];
+        g->TW = TW; g->TH = TH; g->TB = TB;
+        if (!encode_A(p, g)) return -1;
+        p->n_geoms++;
+    }
+    TcParams prm;
+    prm.t = t; prm.res = res; prm.acc_out = acc_out; prm.out = out; prm.err = d_err;
+    prm.batch = batch; prm.Ho = d.Ho; prm.Wo = d.Wo; prm.Cout = d.Cout;
+    prm.taps = d.Kh * d.Kw; prm.Kw = d.Kw; prm.Cp = d.Cin_pad; prm.cin_blocks = d.Cin_pad / p->KC;
+    prm.stride = d.stride; prm.pad = d.pad;
+    prm.TW = TW; prm.TH = TH; prm.TB = TB;
+    prm.tiles_w = (d.Wo + TW - 1) / TW; prm.tiles_h = (d.Ho + TH - 1) / TH; prm.tiles_b = (batch + TB - 1) / TB;
+    prm.tiles_n = d.Cout / p->BN;
+    prm.total_tiles = prm.tiles_w * prm.tiles_h * prm.tiles_b * prm.tiles_n;
+    prm.stages = p->stages;
+    int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
+    if (p->KC == 128) {
+        if (p->BN == 64) return launch_variant<64, 128>(p, g, prm, mode, grid, s);
+        if (p->BN == 128) return launch_variant<128, 128>(p, g, prm, mode, grid, s);
+        return launch_variant<256, 128>(p, g, prm, mode, grid, s);
+    }
+    if (p->BN == 64) return launch_variant<64, 64>(p, g, prm, mode, grid, s);
+    if (p->BN == 128) return launch_variant<128, 64>(p, g, prm, mode, grid, s);
+    return launch_variant<256, 64>(p, g, prm, mode, grid, s);
+}

@@ -1,0 +1,391 @@
+// ffcu_context.cu -- device context behind include/ff_cuda.h: buffers, the static
+// launch list, submit / wait, dump points and the resident-input timing loop.
+
+#include "ffcu_internal.cuh"
+
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <vector>
+
+static thread_local char g_cu_err[512];
+
+void ffcu_set_error(const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_cu_err, sizeof g_cu_err, fmt, ap);
+    va_end(ap);
+}
+
+extern "C" const char* ffcu_last_error(void) { return g_cu_err; }
+
+struct DevLayer {
+    ffcu_layer d;          // host-side description; pointer members are NOT valid on the device
+    int8_t* w = nullptr;
+    float* tab[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    EpiTables epi{};
+    TcPlan* tc = nullptr;  // non-NULL: tensor-core implicit GEMM takes this layer
+};
+
+struct ffcu_ctx {
+    int device = 0;
+    int max_batch = 0;
+    int n_bufs = 0;
+    size_t bytes_per_face = 0;
+    int8_t* bufs[FFCU_MAX_BUFS] = {};
+    float* d_in = nullptr;       // [max_batch][112][112][3] f32
+    float* d_out = nullptr;      // [max_batch][512] f32
+    int* d_err = nullptr;        // device error word
+    int* h_err = nullptr;        // pinned mirror
+    cudaStream_t stream = nullptr;
+    std::vector<DevLayer> layers;
+    int mode = 1;
+    int force_simt = 0;          // FF_CONV_IMPL=simt: every conv on the CUDA-core kernel
+    int launches = 0;
+    bool finalized = false;
+};
+
+extern "C" int ffcu_device_count(void)
+{
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) { ffcu_set_error("cudaGetDeviceCount: %s", cudaGetErrorString(e)); return -1; }
+    return n;
+}
+
+static float* upload_f32(const float* src, int n)
+{
+    if (!src) return nullptr;
+    float* d = nullptr;
+    if (cudaMalloc(&d, (size_t)n * sizeof(float)) != cudaSuccess) return nullptr;
+    cudaMemcpy(d, src, (size_t)n * sizeof(float), cudaMemcpyHostToDevice);
+    return d;
+}
+
+extern "C" ffcu_ctx* ffcu_create(int device, int max_batch, int n_bufs, size_t bytes_per_face)
+{
+    if (n_bufs < 1 || n_bufs > FFCU_MAX_BUFS || max_batch < 1) { ffcu_set_error("bad ffcu_create arguments"); return nullptr; }
+    if (cudaSetDevice(device) != cudaSuccess) { ffcu_set_error("cudaSetDevice(%d) failed", device); return nullptr; }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { ffcu_set_error("cudaGetDeviceProperties failed"); return nullptr; }
+    if (prop.major != 10) {
+        ffcu_set_error("device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+        return nullptr;
+    }
+    ffcu_ctx* c = new ffcu_ctx();
+    c->device = device; c->max_batch = max_batch; c->n_bufs = n_bufs; c->bytes_per_face = bytes_per_face;
+    bool ok = true;
+    // 1 KiB of slack after each tensor: TMA boxes of partial tiles stay inside the allocation
+    size_t act = (size_t)max_batch * bytes_per_face + 1024;
+    for (int i = 0; i < n_bufs && ok; i++) ok = cudaMalloc(&c->bufs[i], act) == cudaSuccess;
+    ok = ok && cudaMalloc(&c->d_in, (size_t)max_batch * 37632 * sizeof(float)) == cudaSuccess;
+    ok = ok && cudaMalloc(&c->d_out, (size_t)max_batch * 512 * sizeof(float)) == cudaSuccess;
+    ok = ok && cudaMalloc(&c->d_err, sizeof(int)) == cudaSuccess;
+    ok = ok && cudaHostAlloc(&c->h_err, sizeof(int), cudaHostAllocDefault) == cudaSuccess;
+    ok = ok && cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess;
+    if (ok) { cudaMemset(c->d_err, 0, sizeof(int)); *c->h_err = 0; }
+    const char* impl = getenv("FF_CONV_IMPL");
+    c->force_simt = (impl && strcmp(impl, "simt") == 0) ? 1 : 0;
+    if (!ok) {
+        ffcu_set_error("device allocation failed on device %d: %s", device, cudaGetErrorString(cudaGetLastError()));
+        ffcu_destroy(c);
+        return nullptr;
+    }
+    return c;
+}
+
+extern "C" void ffcu_destroy(ffcu_ctx* c)
+{
+    if (!c) return;
+    cudaSetDevice(c->device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    for (auto& L : c->layers) {
+        cudaFree(L.w);
+        for (float* t : L.tab) cudaFree(t);
+        ffcu_tc_free(L.tc);
+    }
+    for (int i = 0; i < FFCU_MAX_BUFS; i++) cudaFree(c->bufs[i]);
+    cudaFree(c->d_in); cudaFree(c->d_out); cudaFree(c->d_err);
+    if (c->h_err) cudaFreeHost(c->h_err);
+    if (c->stream) cudaStreamDestroy(c->stream);
+    delete c;
+}
+
+extern "C" int ffcu_add_layer(ffcu_ctx* c, const ffcu_layer* l)
+{
+    if (!c || !l || c->finalized) { ffcu_set_error("ffcu_add_layer: bad state"); return -1; }
+    cudaSetDevice(c->device);
+    DevLayer L;
+    L.d = *l;
+    const int C = l->Cout;
+    if (l->w && l->w_bytes) {
+        if (cudaMalloc(&L.w, l->w_bytes + 1024) != cudaSuccess) { ffcu_set_error("weight allocation failed"); return -1; }
+        cudaMemset(L.w, 0, l->w_bytes + 1024);
+        cudaMemcpy(L.w, l->w, l->w_bytes, cudaMemcpyHostToDevice);
+    }
+    const float* src[8] = {l->w_scale, l->bias, l->slope, l->res_scale, l->inv_out, l->in_scale, l->bn_scale, l->bn_offset};
+    for (int k = 0; k < 8; k++) {
+        int n = (l->kind == FFCU_QUANT) ? 3 : C;
+        if (src[k]) {
+            L.tab[k] = upload_f32(src[k], n);
+            if (!L.tab[k]) { ffcu_set_error("table allocation failed"); return -1; }
+        }
+    }
+    L.epi.w_scale = L.tab[0]; L.epi.bias = L.tab[1]; L.epi.slope = L.tab[2];
+    L.epi.res_scale = L.tab[3]; L.epi.inv_out = L.tab[4];
+    L.d.w = nullptr;
+    L.d.w_scale = L.d.bias = L.d.slope = L.d.res_scale = L.d.inv_out = nullptr;
+    L.d.in_scale = L.d.bn_scale = L.d.bn_offset = nullptr;
+    if (cudaGetLastError() != cudaSuccess) { ffcu_set_error("upload failed"); return -1; }
+    c->layers.push_back(L);
+    return (int)c->layers.size() - 1;
+}
+
+extern "C" int ffcu_finalize(ffcu_ctx* c)
+{
+    if (!c) return -1;
+    cudaSetDevice(c->device);
+    for (auto& L : c->layers) {
+        if ((L.d.kind == FFCU_CONV || L.d.kind == FFCU_FC) && !c->force_simt) {
+            if (L.d.src_buf < 0 || L.d.src_buf >= c->n_bufs) { ffcu_set_error("layer source buffer out of range"); return -1; }
+            L.tc = ffcu_tc_plan(L.d, c->max_batch, c->bufs[L.d.src_buf], L.w, c->device);
+        }
+    }
+    c->finalized = true;
+    return 0;
+}
+
+extern "C" int ffcu_set_mode(ffcu_ctx* c, int mode)
+{
+    if (!c || (mode != 0 && mode != 1)) return -1;
+    c->mode = mode;
+    return 0;
+}
+
+extern "C" int ffcu_launches_per_forward(const ffcu_ctx* c) { return c ? c->launches : 0; }
+
+// ---------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------
+
+// Launch layer k for n faces.  acc_dbg (optional) receives the conv's int32 accumulators.
+static int launch_layer(ffcu_ctx* c, size_t k, int n, int32_t* acc_dbg)
+{
+    DevLayer& L = c->layers[k];
+    const ffcu_layer& d = L.d;
+    cudaStream_t s = c->stream;
+    switch (d.kind) {
+    case FFCU_QUANT:
+        return ffcu_launch_quant(c->d_in, n * d.H * d.W, L.tab[4], c->bufs[d.dst_buf], s);
+    case FFCU_CONV: {
+        const int8_t* res = d.res_buf >= 0 ? c->bufs[d.res_buf] : nullptr;
+        if (L.tc) return ffcu_tc_launch(L.tc, n, c->mode, L.epi, res, acc_dbg, c->bufs[d.dst_buf], c->d_err, s);
+        return ffcu_launch_conv_simt(d, n, c->mode, c->bufs[d.src_buf], L.w, L.epi, res, acc_dbg, c->bufs[d.dst_buf], s);
+    }
+    case FFCU_BN:
+        return ffcu_launch_bn(c->bufs[d.src_buf], c->bufs[d.dst_buf], (size_t)n * d.H * d.W, d.Cout,
+                              L.tab[5], L.tab[6], L.tab[7], L.tab[4], s);
+    case FFCU_FC:
+        if (L.tc) return ffcu_tc_launch(L.tc, n, c->mode, L.epi, nullptr, nullptr, c->d_out, c->d_err, s);
+        return ffcu_launch_fc_simt(c->bufs[d.src_buf], L.w, L.epi.w_scale, L.epi.bias, n, d.Cout, d.Cin,
+                                   c->mode, c->d_out, s);
+    }
+    ffcu_set_error("unknown layer kind %d", d.kind);
+    return -1;
+}
+
+static int launch_forward(ffcu_ctx* c, int n)
+{
+    for (size_t k = 0; k < c->layers.size(); k++) {
+        int rc = launch_layer(c, k, n, nullptr);
+        if (rc != 0) return rc;
+    }
+    c->launches = (int)c->layers.size();
+    return 0;
+}
+
+extern "C" int ffcu_submit(ffcu_ctx* c, const float* host_in, int n, float* host_out)
+{
+    if (!c || !c->finalized || !host_in || !host_out || n < 1 || n > c->max_batch) {
+        ffcu_set_error("ffcu_submit: bad arguments");
+        return -1;
+    }
+    FFCU_CHECK(cudaSetDevice(c->device));
+    FFCU_CHECK(cudaMemcpyAsync(c->d_in, host_in, (size_t)n * 37632 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    int rc = launch_forward(c, n);
+    if (rc != 0) return rc;
+    FFCU_CHECK(cudaMemcpyAsync(host_out, c->d_out, (size_t)n * 512 * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+    return 0;
+}
+
+extern "C" int ffcu_wait(ffcu_ctx* c)
+{
+    if (!c) return -1;
+    FFCU_CHECK(cudaSetDevice(c->device));
+    FFCU_CHECK(cudaMemcpyAsync(c->h_err, c->d_err, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+    FFCU_CHECK(cudaStreamSynchronize(c->stream));
+    if (*c->h_err != 0) {
+        ffcu_set_error("device reported error word %d (a bounded wait inside a kernel ran out)", *c->h_err);
+        int e = *c->h_err;
+        cudaMemsetAsync(c->d_err, 0, sizeof(int), c->stream);
+        return 1000 + e;
+    }
+    return 0;
+}
+
+extern "C" int ffcu_trace(ffcu_ctx* c, const float* host_in, int n, float* host_out,
+                          ffcu_trace_fn fn, void* user)
+{
+    if (!c || !c->finalized || !host_in || !host_out || n < 1 || n > c->max_batch) return -1;
+    FFCU_CHECK(cudaSetDevice(c->device));
+    size_t max_elems = (size_t)n * c->bytes_per_face;
+    std::vector<uint8_t> host(max_elems * 4);
+    int32_t* d_acc = nullptr;
+    FFCU_CHECK(cudaMalloc(&d_acc, max_elems * sizeof(int32_t)));
+    FFCU_CHECK(cudaMemcpyAsync(c->d_in, host_in, (size_t)n * 37632 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    int rc = 0;
+    for (size_t k = 0; k < c->layers.size() && rc == 0; k++) {
+        const ffcu_layer& d = c->layers[k].d;
+        rc = launch_layer(c, k, n, d.kind == FFCU_CONV ? d_acc : nullptr);
+        if (rc != 0) break;
+        rc = ffcu_wait(c);
+        if (rc != 0 || !fn) continue;
+        if (d.kind == FFCU_QUANT) {
+            size_t npix = (size_t)n * d.H * d.W;
+            cudaMemcpy(host.data(), c->bufs[d.dst_buf], npix * 4, cudaMemcpyDeviceToHost);
+            std::vector<int8_t> q(npix * 3);     // dump in the reference's 3-channel layout
+            for (size_t p = 0; p < npix; p++)
+                for (int ch = 0; ch < 3; ch++) q[p * 3 + ch] = (int8_t)host[p * 4 + ch];
+            fn(user, d.op_index, 'Q', q.data(), npix * 3);
+        } else if (d.kind == FFCU_CONV) {
+            size_t ne = (size_t)n * d.Ho * d.Wo * d.Cout;
+            cudaMemcpy(host.data(), d_acc, ne * 4, cudaMemcpyDeviceToHost);
+            fn(user, d.op_index, 'A', host.data(), ne);
+            cudaMemcpy(host.data(), c->bufs[d.dst_buf], ne, cudaMemcpyDeviceToHost);
+            fn(user, d.op_index, 'O', host.data(), ne);
+        } else if (d.kind == FFCU_BN) {
+            size_t ne = (size_t)n * d.H * d.W * d.Cout;
+            cudaMemcpy(host.data(), c->bufs[d.dst_buf], ne, cudaMemcpyDeviceToHost);
+            fn(user, d.op_index, 'B', host.data(), ne);
+        } else if (d.kind == FFCU_FC) {
+            cudaMemcpy(host.data(), c->d_out, (size_t)n * 512 * 4, cudaMemcpyDeviceToHost);
+            fn(user, d.op_index, 'F', host.data(), (size_t)n * 512);
+        }
+    }
+    if (rc == 0) {
+        cudaMemcpy(host_out, c->d_out, (size_t)n * 512 * sizeof(float), cudaMemcpyDeviceToHost);
+        if (cudaGetLastError() != cudaSuccess) rc = -100;
+    }
+    cudaFree(d_acc);
+    return rc;
+}
+
+extern "C" int ffcu_bench_resident(ffcu_ctx* c, const float* host_in, int n, int iters, float* ms)
+{
+    if (!c || !c->finalized || !host_in || !ms || n < 1 || n > c->max_batch || iters < 1) return -1;
+    FFCU_CHECK(cudaSetDevice(c->device));
+    FFCU_CHECK(cudaMemcpyAsync(c->d_in, host_in, (size_t)n * 37632 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    cudaEvent_t e0, e1;
+    FFCU_CHECK(cudaEventCreate(&e0));
+    FFCU_CHECK(cudaEventCreate(&e1));
+    FFCU_CHECK(cudaStreamSynchronize(c->stream));
+    FFCU_CHECK(cudaEventRecord(e0, c->stream));
+    int rc = 0;
+    for (int it = 0; it < iters && rc == 0; it++) rc = launch_forward(c, n);
+    FFCU_CHECK(cudaEventRecord(e1, c->stream));
+    int wrc = ffcu_wait(c);
+    if (rc == 0) rc = wrc;
+    if (rc == 0) FFCU_CHECK(cudaEventElapsedTime(ms, e0, e1));
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    return rc;
+}
+
+extern "C" int ffcu_layer_count(const ffcu_ctx* c) { return c ? (int)c->layers.size() : 0; }
+
+extern "C" int ffcu_layer_info(const ffcu_ctx* c, int k, ffcu_layer* out, int* uses_tc)
+{
+    if (!c || !out || k < 0 || k >= (int)c->layers.size()) return -1;
+    *out = c->layers[k].d;
+    if (uses_tc) *uses_tc = c->layers[k].tc ? 1 : 0;
+    return 0;
+}
+
+extern "C" int ffcu_bench_layers(ffcu_ctx* c, const float* host_in, int n, int iters, float* ms, int cap)
+{
+    if (!c || !c->finalized || !host_in || !ms || n < 1 || n > c->max_batch || iters < 1) return -1;
+    const int nl = (int)c->layers.size();
+    if (cap < nl) { ffcu_set_error("ffcu_bench_layers: ms[] too small"); return -1; }
+    FFCU_CHECK(cudaSetDevice(c->device));
+    FFCU_CHECK(cudaMemcpyAsync(c->d_in, host_in, (size_t)n * 37632 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    int rc = launch_forward(c, n);
+    if (rc != 0) return rc;
+    std::vector<cudaEvent_t> ev(2 * nl);
+    for (auto& e : ev) FFCU_CHECK(cudaEventCreate(&e));
+    for (int k = 0; k < nl && rc == 0; k++) {
+        FFCU_CHECK(cudaEventRecord(ev[2 * k], c->stream));
+        for (int it = 0; it < iters && rc == 0; it++) rc = launch_layer(c, k, n, nullptr);
+        FFCU_CHECK(cudaEventRecord(ev[2 * k + 1], c->stream));
+    }
+    int wrc = ffcu_wait(c);
+    if (rc == 0) rc = wrc;
+    for (int k = 0; k < nl && rc == 0; k++) FFCU_CHECK(cudaEventElapsedTime(&ms[k], ev[2 * k], ev[2 * k + 1]));
+    for (auto& e : ev) cudaEventDestroy(e);
+    return rc == 0 ? nl : rc;
+}
+
+// ---------------------------------------------------------------------------
+// one conv layer on caller-supplied host tensors (single-layer parity tests)
+// ---------------------------------------------------------------------------
+extern "C" int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mode, int impl,
+                              const int8_t* in, const int8_t* res, int32_t* acc_out, int8_t* out)
+{
+    if (!l || !in || batch < 1 || l->kind != FFCU_CONV) { ffcu_set_error("ffcu_conv_once: bad arguments"); return -1; }
+    FFCU_CHECK(cudaSetDevice(device));
+    size_t in_bytes = (size_t)batch * l->H * l->W * l->Cin_pad;
+    size_t out_elems = (size_t)batch * l->Ho * l->Wo * l->Cout;
+    int8_t *d_in = nullptr, *d_res = nullptr, *d_out = nullptr, *d_w = nullptr;
+    int32_t* d_acc = nullptr; int* d_err = nullptr;
+    float* tab[5] = {};
+    FFCU_CHECK(cudaMalloc(&d_in, in_bytes + 1024));
+    FFCU_CHECK(cudaMalloc(&d_out, out_elems + 1024));
+    FFCU_CHECK(cudaMalloc(&d_w, l->w_bytes + 1024));
+    FFCU_CHECK(cudaMalloc(&d_err, sizeof(int)));
+    FFCU_CHECK(cudaMemset(d_err, 0, sizeof(int)));
+    FFCU_CHECK(cudaMemset(d_w, 0, l->w_bytes + 1024));
+    FFCU_CHECK(cudaMemset(d_out, 0x55, out_elems + 1024));
+    if (acc_out) FFCU_CHECK(cudaMalloc(&d_acc, out_elems * 4));
+    if (res) { FFCU_CHECK(cudaMalloc(&d_res, out_elems)); FFCU_CHECK(cudaMemcpy(d_res, res, out_elems, cudaMemcpyHostToDevice)); }
+    FFCU_CHECK(cudaMemcpy(d_in, in, in_bytes, cudaMemcpyHostToDevice));
+    FFCU_CHECK(cudaMemcpy(d_w, l->w, l->w_bytes, cudaMemcpyHostToDevice));
+    const float* src[5] = {l->w_scale, l->bias, l->slope, l->res_scale, l->inv_out};
+    for (int k = 0; k < 5; k++) if (src[k]) tab[k] = upload_f32(src[k], l->Cout);
+    EpiTables t{tab[0], tab[1], tab[2], tab[3], tab[4]};
+    cudaStream_t s; FFCU_CHECK(cudaStreamCreate(&s));
+    int rc = 0;
+    if (impl == 0) {
+        TcPlan* p = ffcu_tc_plan(*l, batch, d_in, d_w, device);
+        if (!p) { ffcu_set_error("layer shape is not covered by the tensor-core kernel"); rc = -2; }
+        else { rc = ffcu_tc_launch(p, batch, mode, t, d_res, d_acc, d_out, d_err, s); }
+        if (rc == 0) { cudaStreamSynchronize(s); }
+        ffcu_tc_free(p);
+    } else {
+        rc = ffcu_launch_conv_simt(*l, batch, mode, d_in, d_w, t, d_res, d_acc, d_out, s);
+    }
+    if (rc == 0) {
+        cudaError_t e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess) { ffcu_set_error("kernel failed: %s", cudaGetErrorString(e)); rc = -100; }
+    }
+    if (rc == 0) {
+        int herr = 0;
+        cudaMemcpy(&herr, d_err, sizeof(int), cudaMemcpyDeviceToHost);
+        if (herr) { ffcu_set_error("device reported error word %d", herr); rc = 1000 + herr; }
+    }
+    if (rc == 0 && acc_out) cudaMemcpy(acc_out, d_acc, out_elems * 4, cudaMemcpyDeviceToHost);
+    if (rc == 0 && out) cudaMemcpy(out, d_out, out_elems, cudaMemcpyDeviceToHost);
+    cudaStreamDestroy(s);
+    cudaFree(d_in); cudaFree(d_res); cudaFree(d_out); cudaFree(d_w); cudaFree(d_acc); cudaFree(d_err);
+    for (float* q : tab) cudaFree(q);
+    return rc;
+}

@@ -1,0 +1,116 @@
+// ffcu_internal.cuh -- shared declarations of the CUDA side (sm_100a only).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <limits.h>
+
+#include "ff_cuda.h"
+
+#define FFCU_MAX_BUFS 8
+
+// Device error word values (first error wins).
+enum {
+    FFCU_ERR_NONE = 0,
+    FFCU_ERR_TMA_TIMEOUT = 1,    // a bounded wait on a TMA "full" barrier ran out
+    FFCU_ERR_MMA_TIMEOUT = 2,    // a bounded wait on an MMA-commit barrier ran out
+    FFCU_ERR_EMPTY_TIMEOUT = 3,  // a bounded wait on a pipeline "empty" barrier ran out
+    FFCU_ERR_EPI_TIMEOUT = 4,    // the epilogue's bounded wait on "accumulator ready" ran out
+    FFCU_ERR_TMEM_TIMEOUT = 5    // a bounded wait on "accumulator drained" ran out
+};
+
+void ffcu_set_error(const char* fmt, ...);
+
+#define FFCU_CHECK(expr)                                                                    \
+    do {                                                                                    \
+        cudaError_t _e = (expr);                                                            \
+        if (_e != cudaSuccess) {                                                            \
+            ffcu_set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+            return -100;                                                                    \
+        }                                                                                   \
+    } while (0)
+
+// Per-output-channel tables of one conv / FC epilogue (device pointers).
+struct EpiTables {
+    const float* w_scale;
+    const float* bias;
+    const float* slope;      // NULL: no PReLU
+    const float* res_scale;  // NULL: no residual
+    const float* inv_out;
+};
+
+// ---------------------------------------------------------------------------
+// The reference's fp32 arithmetic, one rounding per stated operation.
+// ---------------------------------------------------------------------------
+
+// Requantise: q = t * inv; r = q + copysign(0.5, q); truncate; clamp to [-128, 127]
+// (reference kernels/int8_epilogue.c:80-87).  x86 cvttps2dq returns INT_MIN for NaN
+// and for |r| >= 2^31, which the clamp turns into -128; reproduced here because
+// __float2int_rz saturates instead.
+__device__ __forceinline__ int ffcu_requant(float t, float inv)
+{
+    float q = __fmul_rn(t, inv);
+    float half = __int_as_float(0x3f000000 | (__float_as_int(q) & 0x80000000));
+    float r = __fadd_rn(q, half);
+    int i = __float2int_rz(r);
+    if (!(fabsf(r) < 2147483648.0f)) i = INT_MIN;
+    return max(-128, min(127, i));
+}
+
+// Conv epilogue value before requantisation (reference kernels/int8_epilogue.c:53-76).
+// CONTRACT selects the evaluation gcc produces for that source under the reference
+// Makefile's flags: the "* w_scale + bias" and "res * res_scale + t" pairs become fmas.
+template <bool CONTRACT>
+__device__ __forceinline__ float ffcu_conv_fp(int acc, float ws, float bias, bool has_res, int res,
+                                              float rs, bool has_slope, float slope)
+{
+    float t = __int2float_rn(acc);            // (float)acc, then * in_scale (1.0f): exact
+    if (CONTRACT) {
+        t = __fmaf_rn(t, ws, bias);
+        if (has_res) t = __fmaf_rn(__int2float_rn(res), rs, t);
+    } else {
+        t = __fadd_rn(__fmul_rn(t, ws), bias);
+        if (has_res) t = __fadd_rn(t, __fmul_rn(__int2float_rn(res), rs));
+    }
+    if (has_slope && t < 0.0f) t = __fmul_rn(t, slope);
+    return t;
+}
+
+// Standalone BN pass (reference kernels/int8_epilogue.c:272-303): explicit fma in the source.
+__device__ __forceinline__ int ffcu_bn_q(int a, float in_scale, float bn_scale, float bn_offset, float inv)
+{
+    float t = __fmul_rn(__int2float_rn(a), in_scale);
+    t = __fmaf_rn(t, bn_scale, bn_offset);
+    return ffcu_requant(t, inv);
+}
+
+// FC output (reference kernels/gemm_int8_matvec.c:78-79): bias + (float)dot * 1.0f * w_scale.
+template <bool CONTRACT>
+__device__ __forceinline__ float ffcu_fc_fp(int dot, float ws, float bias)
+{
+    float t = __int2float_rn(dot);
+    return CONTRACT ? __fmaf_rn(t, ws, bias) : __fadd_rn(bias, __fmul_rn(t, ws));
+}
+
+// ---------------------------------------------------------------------------
+// Kernel launchers (kernels_simt.cu)
+// ---------------------------------------------------------------------------
+int ffcu_launch_quant(const float* in, int n_pix, const float* inv3, int8_t* out4, cudaStream_t s);
+int ffcu_launch_conv_simt(const ffcu_layer& L, int batch, int mode, const int8_t* in, const int8_t* w,
+                          const EpiTables& t, const int8_t* res, int32_t* acc_out, int8_t* out,
+                          cudaStream_t s);
+int ffcu_launch_bn(const int8_t* in, int8_t* out, size_t n_pos, int C, const float* in_scale,
+                   const float* bn_scale, const float* bn_offset, const float* inv_out, cudaStream_t s);
+int ffcu_launch_fc_simt(const int8_t* act, const int8_t* w, const float* w_scale, const float* bias,
+                        int batch, int N, int K, int mode, float* out, cudaStream_t s);
+
+// ---------------------------------------------------------------------------
+// Tensor-core implicit GEMM (conv_tc.cu)
+// ---------------------------------------------------------------------------
+struct TcPlan;   // opaque: tile shape, TMA descriptors, launch geometry for one layer
+// NULL when the layer shape is not covered by the tensor-core kernel.
+TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, const int8_t* d_w, int device);
+void    ffcu_tc_free(TcPlan* p);
+int     ffcu_tc_launch(const TcPlan* p, int batch, int mode, const EpiTables& t, const int8_t* res,
+                       int32_t* acc_out, void* out, int* d_err, cudaStream_t s);

@@ -1,0 +1,233 @@
+// kernels_simt.cu -- CUDA-core kernels: input quantisation, the stem / generic
+// direct convolution (dp4a), the standalone BN pass and the small-batch FC.
+//
+// These are bandwidth- or latency-bound steps (or, for the generic conv, the
+// path for shapes the tensor-core kernel does not take: Cin = 3).
+
+#include "ffcu_internal.cuh"
+
+// ---------------------------------------------------------------------------
+// fp32 HWC input -> int8, per channel, ties-to-even
+// (reference kernels/int8_epilogue.c:231-247: lrintf(x * inv[c]) then clamp).
+// Output pixels are stored as 4 bytes (c0,c1,c2,0) so a pixel is one word.
+// ---------------------------------------------------------------------------
+__global__ void quant_input_kernel(const float* __restrict__ in, long n_pix,
+                                   const float* __restrict__ inv3, int* __restrict__ out)
+{
+    long p = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= n_pix) return;
+    float i0 = __ldg(inv3), i1 = __ldg(inv3 + 1), i2 = __ldg(inv3 + 2);
+    const float* x = in + p * 3;
+    int q0 = max(-128, min(127, __float2int_rn(__fmul_rn(x[0], i0))));
+    int q1 = max(-128, min(127, __float2int_rn(__fmul_rn(x[1], i1))));
+    int q2 = max(-128, min(127, __float2int_rn(__fmul_rn(x[2], i2))));
+    out[p] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16);
+}
+
+int ffcu_launch_quant(const float* in, int n_pix, const float* inv3, int8_t* out4, cudaStream_t s)
+{
+    int threads = 256;
+    long blocks = ((long)n_pix + threads - 1) / threads;
+    quant_input_kernel<<<(unsigned)blocks, threads, 0, s>>>(in, n_pix, inv3, (int*)out4);
+    FFCU_CHECK(cudaGetLastError());
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Direct convolution on CUDA cores: exact int8 x int8 -> int32 (dp4a), then the
+// fused epilogue.  One thread = one output pixel x 4 consecutive output channels.
+//   in  [B][H][W][Cp]   (Cp = Cin rounded up to 4, pad channels are zero)
+//   w   [Cout][Kh][Kw][Cp]
+//   out [B][Ho][Wo][Cout]
+// Takes over fastface_conv2d_i8_nhwc_batched + fused_epilogue_int8
+// (reference kernels/conv2d_nhwc.c:179-220, kernels/int8_epilogue.c:25-112).
+// ---------------------------------------------------------------------------
+template <bool CONTRACT>
+__global__ void conv_simt_kernel(const int8_t* __restrict__ in, const int8_t* __restrict__ w,
+                                 EpiTables t, const int8_t* __restrict__ res,
+                                 int32_t* __restrict__ acc_out, int8_t* __restrict__ out,
+                                 int B, int H, int W, int Cp, int Cout, int Kh, int Kw,
+                                 int stride, int pad, int Ho, int Wo)
+{
+    const int cg_per_pix = Cout >> 2;
+    long gid = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    long total = (long)B * Ho * Wo * cg_per_pix;
+    if (gid >= total) return;
+    int cg = (int)(gid % cg_per_pix);
+    long pix = gid / cg_per_pix;
+    int ow = (int)(pix % Wo);
+    int oh = (int)((pix / Wo) % Ho);
+    int b = (int)(pix / ((long)Wo * Ho));
+    const int co = cg * 4;
+    const int c4n = Cp >> 2;
+    const int krow = Kh * Kw * c4n;                 // words per output channel
+    const int* w0 = (const int*)w + (long)co * krow;
+    int a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+    for (int kh = 0; kh < Kh; kh++) {
+        int ih = oh * stride - pad + kh;
+        if (ih < 0 || ih >= H) continue;
+        for (int kw = 0; kw < Kw; kw++) {
+            int iw = ow * stride - pad + kw;
+            if (iw < 0 || iw >= W) continue;
+            const int* ip = (const int*)in + (((long)b * H + ih) * W + iw) * c4n;
+            const int* wp = w0 + (kh * Kw + kw) * c4n;
+            for (int c = 0; c < c4n; c++) {
+                int a = __ldg(ip + c);
+                a0 = __dp4a(a, __ldg(wp + c), a0);
+                a1 = __dp4a(a, __ldg(wp + krow + c), a1);
+                a2 = __dp4a(a, __ldg(wp + 2 * krow + c), a2);
+                a3 = __dp4a(a, __ldg(wp + 3 * krow + c), a3);
+            }
+        }
+    }
+    long o = pix * Cout + co;
+    if (acc_out) *(int4*)(acc_out + o) = make_int4(a0, a1, a2, a3);
+    if (!out) return;
+    int acc[4] = {a0, a1, a2, a3};
+    int rw = 0;
+    const bool has_res = (res != nullptr) && (t.res_scale != nullptr);
+    if (has_res) rw = *(const int*)(res + o);
+    unsigned packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        int c = co + j;
+        int r = (int)(int8_t)((rw >> (8 * j)) & 0xff);
+        float v = ffcu_conv_fp<CONTRACT>(acc[j], __ldg(t.w_scale + c), __ldg(t.bias + c), has_res, r,
+                                         has_res ? __ldg(t.res_scale + c) : 0.0f,
+                                         t.slope != nullptr, t.slope ? __ldg(t.slope + c) : 0.0f);
+        int q = ffcu_requant(v, __ldg(t.inv_out + c));
+        packed |= (unsigned)(q & 0xff) << (8 * j);
+    }
+    *(unsigned*)(out + o) = packed;
+}
+
+int ffcu_launch_conv_simt(const ffcu_layer& L, int batch, int mode, const int8_t* in, const int8_t* w,
+                          const EpiTables& t, const int8_t* res, int32_t* acc_out, int8_t* out,
+                          cudaStream_t s)
+{
+    long total = (long)batch * L.Ho * L.Wo * (L.Cout / 4);
+    int threads = 256;
+    long blocks = (total + threads - 1) / threads;
+    if (mode)
+        conv_simt_kernel<true><<<(unsigned)blocks, threads, 0, s>>>(in, w, t, res, acc_out, out, batch, L.H, L.W,
+            L.Cin_pad, L.Cout, L.Kh, L.Kw, L.stride, L.pad, L.Ho, L.Wo);
+    else
+        conv_simt_kernel<false><<<(unsigned)blocks, threads, 0, s>>>(in, w, t, res, acc_out, out, batch, L.H, L.W,
+            L.Cin_pad, L.Cout, L.Kh, L.Kw, L.stride, L.pad, L.Ho, L.Wo);
+    FFCU_CHECK(cudaGetLastError());
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Standalone BN + requant (reference kernels/int8_epilogue.c:253-318).
+// One thread = 16 consecutive channels of one position (C is a multiple of 16).
+// ---------------------------------------------------------------------------
+__global__ void bn_kernel(const int4* __restrict__ in, int4* __restrict__ out, long n_vec, int c16,
+                          const float* __restrict__ in_scale, const float* __restrict__ bn_scale,
+                          const float* __restrict__ bn_offset, const float* __restrict__ inv_out)
+{
+    long v = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= n_vec) return;
+    int c0 = (int)(v % c16) * 16;
+    int4 x = in[v];
+    int xs[4] = {x.x, x.y, x.z, x.w};
+    int ys[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        unsigned packed = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int c = c0 + k * 4 + j;
+            int a = (int)(int8_t)((xs[k] >> (8 * j)) & 0xff);
+            int q = ffcu_bn_q(a, __ldg(in_scale + c), __ldg(bn_scale + c), __ldg(bn_offset + c), __ldg(inv_out + c));
+            packed |= (unsigned)(q & 0xff) << (8 * j);
+        }
+        ys[k] = (int)packed;
+    }
+    out[v] = make_int4(ys[0], ys[1], ys[2], ys[3]);
+}
+
+int ffcu_launch_bn(const int8_t* in, int8_t* out, size_t n_pos, int C, const float* in_scale,
+                   const float* bn_scale, const float* bn_offset, const float* inv_out, cudaStream_t s)
+{
+    if (C % 16 != 0) { ffcu_set_error("BN kernel needs C %% 16 == 0 (C=%d)", C); return -1; }
+    long n_vec = (long)n_pos * (C / 16);
+    int threads = 256;
+    long blocks = (n_vec + threads - 1) / threads;
+    bn_kernel<<<(unsigned)blocks, threads, 0, s>>>((const int4*)in, (int4*)out, n_vec, C / 16,
+                                                   in_scale, bn_scale, bn_offset, inv_out);
+    FFCU_CHECK(cudaGetLastError());
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// FC on CUDA cores: out[b][n] = bias[n] + (float)dot(act[b], w[n]) * w_scale[n]
+// (reference kernels/gemm_int8_matvec.c:33-81).  A block owns 8 outputs x 8 faces;
+// its 256 threads split K in 16-byte steps, then reduce.
+// ---------------------------------------------------------------------------
+#define FC_TN 8
+#define FC_TB 8
+template <bool CONTRACT>
+__global__ void __launch_bounds__(256) fc_simt_kernel(const int8_t* __restrict__ act, const int8_t* __restrict__ w,
+                                                      const float* __restrict__ w_scale, const float* __restrict__ bias,
+                                                      int B, int N, int K, float* __restrict__ out)
+{
+    __shared__ int red[8][FC_TB * FC_TN];
+    const int n0 = blockIdx.x * FC_TN;
+    const int b0 = blockIdx.y * FC_TB;
+    int acc[FC_TB][FC_TN];
+#pragma unroll
+    for (int i = 0; i < FC_TB; i++)
+#pragma unroll
+        for (int j = 0; j < FC_TN; j++) acc[i][j] = 0;
+    const int kv = K >> 4;
+    for (int k = threadIdx.x; k < kv; k += blockDim.x) {
+        int4 a[FC_TB], ww[FC_TN];
+#pragma unroll
+        for (int i = 0; i < FC_TB; i++) {
+            int b = min(b0 + i, B - 1);
+            a[i] = __ldg((const int4*)(act + (size_t)b * K) + k);
+        }
+#pragma unroll
+        for (int j = 0; j < FC_TN; j++) ww[j] = __ldg((const int4*)(w + (size_t)(n0 + j) * K) + k);
+#pragma unroll
+        for (int i = 0; i < FC_TB; i++)
+#pragma unroll
+            for (int j = 0; j < FC_TN; j++) {
+                int s = acc[i][j];
+                s = __dp4a(a[i].x, ww[j].x, s); s = __dp4a(a[i].y, ww[j].y, s);
+                s = __dp4a(a[i].z, ww[j].z, s); s = __dp4a(a[i].w, ww[j].w, s);
+                acc[i][j] = s;
+            }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int i = 0; i < FC_TB; i++)
+#pragma unroll
+        for (int j = 0; j < FC_TN; j++) {
+            int s = acc[i][j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (lane == 0) red[warp][i * FC_TN + j] = s;
+        }
+    __syncthreads();
+    if (threadIdx.x < FC_TB * FC_TN) {
+        int s = 0;
+#pragma unroll
+        for (int wv = 0; wv < 8; wv++) s += red[wv][threadIdx.x];
+        int i = threadIdx.x / FC_TN, j = threadIdx.x % FC_TN;
+        int b = b0 + i, n = n0 + j;
+        if (b < B) out[(size_t)b * N + n] = ffcu_fc_fp<CONTRACT>(s, __ldg(w_scale + n), __ldg(bias + n));
+    }
+}
+
+int ffcu_launch_fc_simt(const int8_t* act, const int8_t* w, const float* w_scale, const float* bias,
+                        int batch, int N, int K, int mode, float* out, cudaStream_t s)
+{
+    if (N % FC_TN != 0 || K % 16 != 0) { ffcu_set_error("FC kernel needs N %% 8 == 0 and K %% 16 == 0"); return -1; }
+    dim3 grid(N / FC_TN, (batch + FC_TB - 1) / FC_TB);
+    if (mode) fc_simt_kernel<true><<<grid, 256, 0, s>>>(act, w, w_scale, bias, batch, N, K, out);
+    else      fc_simt_kernel<false><<<grid, 256, 0, s>>>(act, w, w_scale, bias, batch, N, K, out);
+    FFCU_CHECK(cudaGetLastError());
+    return 0;
+}

@@ -1,0 +1,108 @@
+/* ff_cuda.h -- C-ABI shim between the C99 host code and the CUDA (sm_100a) side.
+ *
+ * Plain pointers and sizes only.  The C99 host parses the model files, resolves
+ * every scale the reference's driver loop (libfastface.c:349-466) would pick at
+ * run time into per-channel arrays, assigns activation buffers, and hands the
+ * resulting static layer list to the device context through these calls.  Each
+ * entry names the reference function whose work it takes over.
+ */
+#ifndef FF_CUDA_H
+#define FF_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ffcu_ctx ffcu_ctx;
+
+enum { FFCU_QUANT = 0, FFCU_CONV = 1, FFCU_BN = 2, FFCU_FC = 3 };
+
+/* One step of the static layer plan.  All arrays are host pointers that
+ * ffcu_add_layer copies to the device; they need not outlive the call. */
+typedef struct {
+    int kind;            /* FFCU_*                                                   */
+    int op_index;        /* FFW4 op index (dump-point id)                            */
+    int src_buf;         /* activation buffer ids; FFCU_QUANT reads the fp32 input   */
+    int dst_buf;         /* FFCU_FC writes the f32 embedding buffer                  */
+    int res_buf;         /* residual operand of a fused ADD, or -1                   */
+    int Cin, Cout, Kh, Kw, stride, pad;
+    int H, W, Ho, Wo;    /* per-face input / output extent                           */
+    /* FFCU_CONV: int8 weights repacked [Cout][Kh][Kw][Cin_pad] (Cin_pad = Cin rounded
+     * up to 4); FFCU_FC: [N][K] with K in (h,w,c) order.                             */
+    const int8_t* w;
+    size_t w_bytes;
+    int Cin_pad;
+    /* per-output-channel fp32 tables, each [Cout] (or [C] for BN); NULL = unused   */
+    const float* w_scale;    /* conv/FC dequant scale                                */
+    const float* bias;       /* conv/FC bias                                         */
+    const float* slope;      /* fused PReLU                                          */
+    const float* res_scale;  /* scale of the residual operand                        */
+    const float* inv_out;    /* requant multiplier 1/(s+1e-9f) (conv, BN, input)     */
+    const float* in_scale;   /* BN: scale of the int8 input                          */
+    const float* bn_scale;   /* BN                                                   */
+    const float* bn_offset;  /* BN                                                   */
+} ffcu_layer;
+
+/* Devices visible to the process; <0 on a CUDA error. */
+int ffcu_device_count(void);
+
+/* Device context: n_bufs int8 activation buffers of max_batch*bytes_per_face each,
+ * an fp32 input and an f32 output buffer for max_batch faces, streams, pinned
+ * staging.  Takes over the buffer allocation of libfastface.c:301-308. */
+ffcu_ctx* ffcu_create(int device, int max_batch, int n_bufs, size_t bytes_per_face);
+void      ffcu_destroy(ffcu_ctx* c);
+
+/* Append one layer (uploads its weights and tables).  Returns the layer id, <0 on error.
+ * Takes over pack_conv_weight_nhwc's device-side half (kernels/conv2d_nhwc.c:79-100). */
+int ffcu_add_layer(ffcu_ctx* c, const ffcu_layer* l);
+
+/* Fix the plan: picks kernels/tiles per layer, encodes TMA descriptors. */
+int ffcu_finalize(ffcu_ctx* c);
+
+/* mode: 0 strict, 1 contract (fp32 evaluation order of the conv/FC epilogue). */
+int ffcu_set_mode(ffcu_ctx* c, int mode);
+
+/* Forward n <= max_batch faces: host fp32 in -> host f32 out, copies included.
+ * Asynchronous on the context's stream; ffcu_wait blocks until it is done and
+ * returns 0 or the device error word.  Takes over the op loop of
+ * arcface_forward_int8_batched.c:339-516. */
+int ffcu_submit(ffcu_ctx* c, const float* host_in, int n, float* host_out);
+int ffcu_wait(ffcu_ctx* c);
+
+/* Same forward with dump points; fn is called on the host after each layer. */
+typedef void (*ffcu_trace_fn)(void* user, int op_index, int kind,
+                              const void* data, unsigned long long n_elems);
+int ffcu_trace(ffcu_ctx* c, const float* host_in, int n, float* host_out,
+               ffcu_trace_fn fn, void* user);
+
+/* iters forwards over n faces already on the device; CUDA-event milliseconds. */
+int ffcu_bench_resident(ffcu_ctx* c, const float* host_in, int n, int iters, float* ms);
+
+int ffcu_launches_per_forward(const ffcu_ctx* c);
+
+/* Per-layer timing: after one full forward over n resident faces, each layer is
+ * launched `iters` times back to back between two CUDA events on the compute stream;
+ * ms[k] receives the total for layer k.  Returns the layer count (<0 on error). */
+int ffcu_bench_layers(ffcu_ctx* c, const float* host_in, int n, int iters, float* ms, int cap);
+
+/* Layer count and description of layer k (pointer members are NULL in *out);
+ * *uses_tc = 1 when the tensor-core implicit-GEMM kernel runs it. */
+int ffcu_layer_count(const ffcu_ctx* c);
+int ffcu_layer_info(const ffcu_ctx* c, int k, ffcu_layer* out, int* uses_tc);
+
+/* Standalone kernels on raw device-independent host buffers, for the single-layer
+ * parity tests: runs one conv layer (int8 NHWC in, optional residual) and returns
+ * int32 accumulators and/or the int8 epilogue output. impl: 0 = tensor-core
+ * implicit GEMM, 1 = SIMT reference kernel. */
+int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mode, int impl,
+                   const int8_t* in, const int8_t* res, int32_t* acc_out, int8_t* out);
+
+const char* ffcu_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FF_CUDA_H */
