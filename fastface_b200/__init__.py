@@ -38,7 +38,9 @@ class FfcuLayer(C.Structure):
                 ("Wo", C.c_int), ("w", C.c_void_p), ("w_bytes", C.c_size_t), ("Cin_pad", C.c_int),
                 ("w_scale", C.c_void_p), ("bias", C.c_void_p), ("slope", C.c_void_p),
                 ("res_scale", C.c_void_p), ("inv_out", C.c_void_p), ("in_scale", C.c_void_p),
-                ("bn_scale", C.c_void_p), ("bn_offset", C.c_void_p)]
+                ("bn_scale", C.c_void_p), ("bn_offset", C.c_void_p),
+                ("bn2_dst_buf", C.c_int), ("bn2_op_index", C.c_int), ("bn2_in_scale", C.c_void_p),
+                ("bn2_scale", C.c_void_p), ("bn2_offset", C.c_void_p), ("bn2_inv_out", C.c_void_p)]
 
 
 def load_library() -> C.CDLL:
@@ -79,7 +81,7 @@ def load_library() -> C.CDLL:
     L.ffcu_device_count.restype = C.c_int
     L.ffcu_conv_once.restype = C.c_int
     L.ffcu_conv_once.argtypes = [C.c_int, C.POINTER(FfcuLayer), C.c_int, C.c_int, C.c_int,
-                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.ffcu_last_error.restype = C.c_char_p
     _lib = L
     return L
@@ -227,7 +229,8 @@ class FastFace:
 def conv_once(x: np.ndarray, w_oihw: np.ndarray, w_scale: np.ndarray, bias: np.ndarray,
               inv_out: np.ndarray, stride: int = 1, pad: int = 1, slope: Optional[np.ndarray] = None,
               res: Optional[np.ndarray] = None, res_scale: Optional[np.ndarray] = None,
-              mode: int = EPILOGUE_CONTRACT, impl: str = "tc", device: int = 0) -> Tuple[np.ndarray, np.ndarray]:
+              mode: int = EPILOGUE_CONTRACT, impl: str = "tc", device: int = 0,
+              bn2: Optional[Tuple[np.ndarray, np.ndarray, np.ndarray, np.ndarray]] = None):
     """One conv layer through the C-ABI (ffcu_conv_once): x int8 [B,H,W,Cin],
     w int8 [Cout,Cin,Kh,Kw] -> (int32 accumulators, int8 output), both [B,Ho,Wo,Cout]."""
     lib = load_library()
@@ -246,10 +249,19 @@ def conv_once(x: np.ndarray, w_oihw: np.ndarray, w_scale: np.ndarray, bias: np.n
     L.H, L.W, L.Ho, L.Wo = H, W, Ho, Wo
     L.w = wp.ctypes.data; L.w_bytes = wp.size; L.Cin_pad = Cp
     L.w_scale, L.bias, L.slope, L.res_scale, L.inv_out = [None if a is None else a.ctypes.data for a in keep]
+    L.bn2_dst_buf = -1
+    out2 = None
+    if bn2 is not None:
+        keep2 = [np.ascontiguousarray(a, dtype=np.float32) for a in bn2]
+        L.bn2_dst_buf = 3
+        L.bn2_in_scale, L.bn2_scale, L.bn2_offset, L.bn2_inv_out = [a.ctypes.data for a in keep2]
+        out2 = np.empty((B, Ho, Wo, Cout), np.int8)
     acc = np.empty((B, Ho, Wo, Cout), np.int32)
     out = np.empty((B, Ho, Wo, Cout), np.int8)
     r = None if res is None else np.ascontiguousarray(res, dtype=np.int8)
-    rc = lib.ffcu_conv_once(device, C.byref(L), B, mode, 0 if impl == "tc" else 1, _ptr(xp), _ptr(r), _ptr(acc), _ptr(out))
+    rc = lib.ffcu_conv_once(device, C.byref(L), B, mode, 0 if impl == "tc" else 1, _ptr(xp), _ptr(r), _ptr(acc), _ptr(out), _ptr(out2))
     if rc != 0:
         raise RuntimeError(f"ffcu_conv_once rc={rc}: " + lib.ffcu_last_error().decode())
+    if bn2 is not None:
+        return acc, out, out2
     return acc, out

@@ -151,6 +151,7 @@ struct TcParams {
     const int8_t* res;
     int32_t* acc_out;
     void* out;
+    int8_t* out2;            // fused BN second output (NULL: none)
     int* err;
     int batch, Ho, Wo, Cout;
     int taps, Kw, cin_blocks, Cp;
@@ -161,6 +162,7 @@ struct TcParams {
 };
 
 #define TC_MAX_STAGES 8
+#define TC_NTAB 9          // w_scale, bias, slope, res_scale, inv_out, bn_in, bn_scale, bn_offset, bn_inv
 
 struct TcShared {                 // lives after the stage ring and the tables
     uint64_t full[TC_MAX_STAGES];
@@ -184,8 +186,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;    // 128 / 256 / 512: powers of two
     constexpr uint32_t IDESC = idesc_i8(BN);
 
-    float* tab = (float*)(smem + (size_t)p.stages * STAGE_BYTES);       // [5][Cout]
-    TcShared* sh = (TcShared*)(tab + 5 * TC_MAX_COUT);
+    float* tab = (float*)(smem + (size_t)p.stages * STAGE_BYTES);       // [TC_NTAB][TC_MAX_COUT]
+    TcShared* sh = (TcShared*)(tab + TC_NTAB * TC_MAX_COUT);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -205,6 +207,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         tab[2 * TC_MAX_COUT + i] = p.t.slope ? p.t.slope[i] : 0.0f;
         tab[3 * TC_MAX_COUT + i] = p.t.res_scale ? p.t.res_scale[i] : 0.0f;
         tab[4 * TC_MAX_COUT + i] = p.t.inv_out ? p.t.inv_out[i] : 0.0f;
+        if (p.out2) {
+            tab[5 * TC_MAX_COUT + i] = p.t.bn_in[i];
+            tab[6 * TC_MAX_COUT + i] = p.t.bn_scale[i];
+            tab[7 * TC_MAX_COUT + i] = p.t.bn_offset[i];
+            tab[8 * TC_MAX_COUT + i] = p.t.bn_inv[i];
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -286,6 +294,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         const int ib = row / (p.TW * p.TH);
         const bool has_res = (p.res != nullptr) && (p.t.res_scale != nullptr);
         const bool has_slope = p.t.slope != nullptr;
+        const bool has_bn2 = p.out2 != nullptr;
         int local = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, local++) {
@@ -337,7 +346,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         rw[0] = r0.x; rw[1] = r0.y; rw[2] = r0.z; rw[3] = r0.w;
                         rw[4] = r1.x; rw[5] = r1.y; rw[6] = r1.z; rw[7] = r1.w;
                     }
-                    int ow_[8];
+                    int ow_[8], ow2_[8];
 #pragma unroll
                     for (int g = 0; g < 8; g++) {
                         const float4 ws = *(const float4*)&tab[0 * TC_MAX_COUT + cb + 4 * g];
@@ -353,10 +362,24 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         int q0 = ffcu_requant(f0, iv.x), q1 = ffcu_requant(f1, iv.y);
                         int q2 = ffcu_requant(f2, iv.z), q3 = ffcu_requant(f3, iv.w);
                         ow_[g] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
+                        if (has_bn2) {
+                            const float4 bi_ = *(const float4*)&tab[5 * TC_MAX_COUT + cb + 4 * g];
+                            const float4 bs_ = *(const float4*)&tab[6 * TC_MAX_COUT + cb + 4 * g];
+                            const float4 bo_ = *(const float4*)&tab[7 * TC_MAX_COUT + cb + 4 * g];
+                            const float4 bv_ = *(const float4*)&tab[8 * TC_MAX_COUT + cb + 4 * g];
+                            int b0 = ffcu_bn_q(q0, bi_.x, bs_.x, bo_.x, bv_.x), b1 = ffcu_bn_q(q1, bi_.y, bs_.y, bo_.y, bv_.y);
+                            int b2 = ffcu_bn_q(q2, bi_.z, bs_.z, bo_.z, bv_.z), b3 = ffcu_bn_q(q3, bi_.w, bs_.w, bo_.w, bv_.w);
+                            ow2_[g] = (b0 & 0xff) | ((b1 & 0xff) << 8) | ((b2 & 0xff) << 16) | ((b3 & 0xff) << 24);
+                        }
                     }
                     int4* dst = (int4*)((int8_t*)p.out + o);
                     dst[0] = make_int4(ow_[0], ow_[1], ow_[2], ow_[3]);
                     dst[1] = make_int4(ow_[4], ow_[5], ow_[6], ow_[7]);
+                    if (has_bn2) {
+                        int4* dst2 = (int4*)(p.out2 + o);
+                        dst2[0] = make_int4(ow2_[0], ow2_[1], ow2_[2], ow2_[3]);
+                        dst2[1] = make_int4(ow2_[4], ow2_[5], ow2_[6], ow2_[7]);
+                    }
                 }
             }
             // all of this warp's TMEM reads are complete (tcgen05.wait::ld inside tmem_ld32)
@@ -468,7 +491,7 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
     const char* bn_env = getenv("FF_TC_BN");
     if (bn_env) { int v = atoi(bn_env); if ((v == 64 || v == 128 || v == 256) && L.Cout % v == 0) p->BN = v; }
     const int stage_bytes = (TC_TILE_M + p->BN) * p->KC;
-    const int fixed = 5 * TC_MAX_COUT * 4 + (int)sizeof(TcShared) + 1024;
+    const int fixed = TC_NTAB * TC_MAX_COUT * 4 + (int)sizeof(TcShared) + 1024;
     int stages = (232448 - fixed) / stage_bytes;
     if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
     if (stages < 2) { delete p; return nullptr; }
@@ -508,7 +531,7 @@ static int launch_variant(const TcPlan* p, const TcGeom* g, const TcParams& prm,
 }
 
 int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, const int8_t* res,
-                   int32_t* acc_out, void* out, int* d_err, cudaStream_t s)
+                   int32_t* acc_out, void* out, int8_t* out_bn2, int* d_err, cudaStream_t s)
 {
     TcPlan* p = const_cast<TcPlan*>(cp);
     if (batch < 1 || batch > p->max_batch) { ffcu_set_error("tc launch: batch out of range"); return -1; }
@@ -527,6 +550,7 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
     }
     TcParams prm;
     prm.t = t; prm.res = res; prm.acc_out = acc_out; prm.out = out; prm.err = d_err;
+    prm.out2 = (out_bn2 && t.bn_in) ? out_bn2 : nullptr;
     prm.batch = batch; prm.Ho = d.Ho; prm.Wo = d.Wo; prm.Cout = d.Cout;
     prm.taps = d.Kh * d.Kw; prm.Kw = d.Kw; prm.Cp = d.Cin_pad; prm.cin_blocks = d.Cin_pad / p->KC;
     prm.stride = d.stride; prm.pad = d.pad;

@@ -24,9 +24,11 @@ extern "C" const char* ffcu_last_error(void) { return g_cu_err; }
 struct DevLayer {
     ffcu_layer d;          // host-side description; pointer members are NOT valid on the device
     int8_t* w = nullptr;
-    float* tab[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    float* tab[12] = {};   // w_scale,bias,slope,res_scale,inv_out | in_scale,bn_scale,bn_offset | bn2 in,scale,offset,inv
     EpiTables epi{};
     TcPlan* tc = nullptr;  // non-NULL: tensor-core implicit GEMM takes this layer
+    bool fused_stem = false;   // conv that also does the input quantisation (reads the fp32 input)
+    bool skip = false;         // quantise layer absorbed by the fused stem
 };
 
 struct ffcu_ctx {
@@ -125,8 +127,12 @@ extern "C" int ffcu_add_layer(ffcu_ctx* c, const ffcu_layer* l)
         cudaMemset(L.w, 0, l->w_bytes + 1024);
         cudaMemcpy(L.w, l->w, l->w_bytes, cudaMemcpyHostToDevice);
     }
-    const float* src[8] = {l->w_scale, l->bias, l->slope, l->res_scale, l->inv_out, l->in_scale, l->bn_scale, l->bn_offset};
-    for (int k = 0; k < 8; k++) {
+    const float* src[12] = {l->w_scale, l->bias, l->slope, l->res_scale, l->inv_out, l->in_scale, l->bn_scale, l->bn_offset,
+                            l->bn2_in_scale, l->bn2_scale, l->bn2_offset, l->bn2_inv_out};
+    if (l->bn2_dst_buf >= 0 && !(l->bn2_in_scale && l->bn2_scale && l->bn2_offset && l->bn2_inv_out)) {
+        ffcu_set_error("fused BN output without its tables"); return -1;
+    }
+    for (int k = 0; k < 12; k++) {
         int n = (l->kind == FFCU_QUANT) ? 3 : C;
         if (src[k]) {
             L.tab[k] = upload_f32(src[k], n);
@@ -135,6 +141,8 @@ extern "C" int ffcu_add_layer(ffcu_ctx* c, const ffcu_layer* l)
     }
     L.epi.w_scale = L.tab[0]; L.epi.bias = L.tab[1]; L.epi.slope = L.tab[2];
     L.epi.res_scale = L.tab[3]; L.epi.inv_out = L.tab[4];
+    L.epi.bn_in = L.tab[8]; L.epi.bn_scale = L.tab[9]; L.epi.bn_offset = L.tab[10]; L.epi.bn_inv = L.tab[11];
+    L.d.bn2_in_scale = L.d.bn2_scale = L.d.bn2_offset = L.d.bn2_inv_out = nullptr;
     L.d.w = nullptr;
     L.d.w_scale = L.d.bias = L.d.slope = L.d.res_scale = L.d.inv_out = nullptr;
     L.d.in_scale = L.d.bn_scale = L.d.bn_offset = nullptr;
@@ -153,6 +161,18 @@ extern "C" int ffcu_finalize(ffcu_ctx* c)
             L.tc = ffcu_tc_plan(L.d, c->max_batch, c->bufs[L.d.src_buf], L.w, c->device);
         }
     }
+    // [quantise, conv3x3 3->64 s1 p1 at 112x112] -> one fused stem kernel
+    const char* fs = getenv("FF_FUSE_STEM");
+    if (!c->force_simt && !(fs && fs[0] == '0') && c->layers.size() >= 2) {
+        DevLayer& q = c->layers[0]; DevLayer& s = c->layers[1];
+        if (q.d.kind == FFCU_QUANT && s.d.kind == FFCU_CONV && !s.tc && s.d.src_buf == q.d.dst_buf && s.d.Cin == 3 &&
+            s.d.Cin_pad == 4 && s.d.Cout == 64 && s.d.Kh == 3 && s.d.Kw == 3 && s.d.stride == 1 && s.d.pad == 1 &&
+            s.d.H == 112 && s.d.W == 112 && s.d.res_buf < 0) {
+            s.fused_stem = true; q.skip = true;
+        }
+    }
+    c->launches = 0;
+    for (auto& L : c->layers) if (!L.skip) c->launches++;
     c->finalized = true;
     return 0;
 }
@@ -170,25 +190,30 @@ extern "C" int ffcu_launches_per_forward(const ffcu_ctx* c) { return c ? c->laun
 // forward
 // ---------------------------------------------------------------------------
 
-// Launch layer k for n faces.  acc_dbg (optional) receives the conv's int32 accumulators.
-static int launch_layer(ffcu_ctx* c, size_t k, int n, int32_t* acc_dbg)
+// Launch layer k for n faces.  acc_dbg (optional) receives the conv's int32 accumulators;
+// unfused = dump-point mode: the stem runs as separate quantise + conv launches.
+static int launch_layer(ffcu_ctx* c, size_t k, int n, int32_t* acc_dbg, bool unfused = false)
 {
     DevLayer& L = c->layers[k];
     const ffcu_layer& d = L.d;
     cudaStream_t s = c->stream;
+    int8_t* out2 = d.bn2_dst_buf >= 0 ? c->bufs[d.bn2_dst_buf] : nullptr;
     switch (d.kind) {
     case FFCU_QUANT:
+        if (L.skip && !unfused) return 0;
         return ffcu_launch_quant(c->d_in, n * d.H * d.W, L.tab[4], c->bufs[d.dst_buf], s);
     case FFCU_CONV: {
         const int8_t* res = d.res_buf >= 0 ? c->bufs[d.res_buf] : nullptr;
-        if (L.tc) return ffcu_tc_launch(L.tc, n, c->mode, L.epi, res, acc_dbg, c->bufs[d.dst_buf], c->d_err, s);
-        return ffcu_launch_conv_simt(d, n, c->mode, c->bufs[d.src_buf], L.w, L.epi, res, acc_dbg, c->bufs[d.dst_buf], s);
+        if (L.fused_stem && !unfused)
+            return ffcu_launch_stem(c->d_in, c->layers[0].tab[4], L.w, L.epi, n, c->mode, c->bufs[d.dst_buf], out2, nullptr, s);
+        if (L.tc) return ffcu_tc_launch(L.tc, n, c->mode, L.epi, res, acc_dbg, c->bufs[d.dst_buf], out2, c->d_err, s);
+        return ffcu_launch_conv_simt(d, n, c->mode, c->bufs[d.src_buf], L.w, L.epi, res, acc_dbg, c->bufs[d.dst_buf], out2, s);
     }
     case FFCU_BN:
         return ffcu_launch_bn(c->bufs[d.src_buf], c->bufs[d.dst_buf], (size_t)n * d.H * d.W, d.Cout,
                               L.tab[5], L.tab[6], L.tab[7], L.tab[4], s);
     case FFCU_FC:
-        if (L.tc) return ffcu_tc_launch(L.tc, n, c->mode, L.epi, nullptr, nullptr, c->d_out, c->d_err, s);
+        if (L.tc) return ffcu_tc_launch(L.tc, n, c->mode, L.epi, nullptr, nullptr, c->d_out, nullptr, c->d_err, s);
         return ffcu_launch_fc_simt(c->bufs[d.src_buf], L.w, L.epi.w_scale, L.epi.bias, n, d.Cout, d.Cin,
                                    c->mode, c->d_out, s);
     }
@@ -202,7 +227,6 @@ static int launch_forward(ffcu_ctx* c, int n)
         int rc = launch_layer(c, k, n, nullptr);
         if (rc != 0) return rc;
     }
-    c->launches = (int)c->layers.size();
     return 0;
 }
 
@@ -248,7 +272,7 @@ extern "C" int ffcu_trace(ffcu_ctx* c, const float* host_in, int n, float* host_
     int rc = 0;
     for (size_t k = 0; k < c->layers.size() && rc == 0; k++) {
         const ffcu_layer& d = c->layers[k].d;
-        rc = launch_layer(c, k, n, d.kind == FFCU_CONV ? d_acc : nullptr);
+        rc = launch_layer(c, k, n, d.kind == FFCU_CONV ? d_acc : nullptr, true);
         if (rc != 0) break;
         rc = ffcu_wait(c);
         if (rc != 0 || !fn) continue;
@@ -265,6 +289,10 @@ extern "C" int ffcu_trace(ffcu_ctx* c, const float* host_in, int n, float* host_
             fn(user, d.op_index, 'A', host.data(), ne);
             cudaMemcpy(host.data(), c->bufs[d.dst_buf], ne, cudaMemcpyDeviceToHost);
             fn(user, d.op_index, 'O', host.data(), ne);
+            if (d.bn2_dst_buf >= 0) {       // BN fused as the conv's second output
+                cudaMemcpy(host.data(), c->bufs[d.bn2_dst_buf], ne, cudaMemcpyDeviceToHost);
+                fn(user, d.bn2_op_index, 'B', host.data(), ne);
+            }
         } else if (d.kind == FFCU_BN) {
             size_t ne = (size_t)n * d.H * d.W * d.Cout;
             cudaMemcpy(host.data(), c->bufs[d.dst_buf], ne, cudaMemcpyDeviceToHost);
@@ -339,15 +367,17 @@ extern "C" int ffcu_bench_layers(ffcu_ctx* c, const float* host_in, int n, int i
 // one conv layer on caller-supplied host tensors (single-layer parity tests)
 // ---------------------------------------------------------------------------
 extern "C" int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mode, int impl,
-                              const int8_t* in, const int8_t* res, int32_t* acc_out, int8_t* out)
+                              const int8_t* in, const int8_t* res, int32_t* acc_out, int8_t* out, int8_t* out_bn2)
 {
     if (!l || !in || batch < 1 || l->kind != FFCU_CONV) { ffcu_set_error("ffcu_conv_once: bad arguments"); return -1; }
     FFCU_CHECK(cudaSetDevice(device));
     size_t in_bytes = (size_t)batch * l->H * l->W * l->Cin_pad;
     size_t out_elems = (size_t)batch * l->Ho * l->Wo * l->Cout;
-    int8_t *d_in = nullptr, *d_res = nullptr, *d_out = nullptr, *d_w = nullptr;
+    int8_t *d_in = nullptr, *d_res = nullptr, *d_out = nullptr, *d_w = nullptr, *d_out2 = nullptr;
     int32_t* d_acc = nullptr; int* d_err = nullptr;
-    float* tab[5] = {};
+    float* tab[9] = {};
+    const bool bn2 = out_bn2 && l->bn2_in_scale && l->bn2_scale && l->bn2_offset && l->bn2_inv_out;
+    if (bn2) FFCU_CHECK(cudaMalloc(&d_out2, out_elems + 1024));
     FFCU_CHECK(cudaMalloc(&d_in, in_bytes + 1024));
     FFCU_CHECK(cudaMalloc(&d_out, out_elems + 1024));
     FFCU_CHECK(cudaMalloc(&d_w, l->w_bytes + 1024));
@@ -359,19 +389,21 @@ extern "C" int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mo
     if (res) { FFCU_CHECK(cudaMalloc(&d_res, out_elems)); FFCU_CHECK(cudaMemcpy(d_res, res, out_elems, cudaMemcpyHostToDevice)); }
     FFCU_CHECK(cudaMemcpy(d_in, in, in_bytes, cudaMemcpyHostToDevice));
     FFCU_CHECK(cudaMemcpy(d_w, l->w, l->w_bytes, cudaMemcpyHostToDevice));
-    const float* src[5] = {l->w_scale, l->bias, l->slope, l->res_scale, l->inv_out};
-    for (int k = 0; k < 5; k++) if (src[k]) tab[k] = upload_f32(src[k], l->Cout);
-    EpiTables t{tab[0], tab[1], tab[2], tab[3], tab[4]};
+    const float* src[9] = {l->w_scale, l->bias, l->slope, l->res_scale, l->inv_out,
+                           bn2 ? l->bn2_in_scale : nullptr, bn2 ? l->bn2_scale : nullptr,
+                           bn2 ? l->bn2_offset : nullptr, bn2 ? l->bn2_inv_out : nullptr};
+    for (int k = 0; k < 9; k++) if (src[k]) tab[k] = upload_f32(src[k], l->Cout);
+    EpiTables t{tab[0], tab[1], tab[2], tab[3], tab[4], tab[5], tab[6], tab[7], tab[8]};
     cudaStream_t s; FFCU_CHECK(cudaStreamCreate(&s));
     int rc = 0;
     if (impl == 0) {
         TcPlan* p = ffcu_tc_plan(*l, batch, d_in, d_w, device);
         if (!p) { ffcu_set_error("layer shape is not covered by the tensor-core kernel"); rc = -2; }
-        else { rc = ffcu_tc_launch(p, batch, mode, t, d_res, d_acc, d_out, d_err, s); }
+        else { rc = ffcu_tc_launch(p, batch, mode, t, d_res, d_acc, d_out, d_out2, d_err, s); }
         if (rc == 0) { cudaStreamSynchronize(s); }
         ffcu_tc_free(p);
     } else {
-        rc = ffcu_launch_conv_simt(*l, batch, mode, d_in, d_w, t, d_res, d_acc, d_out, s);
+        rc = ffcu_launch_conv_simt(*l, batch, mode, d_in, d_w, t, d_res, d_acc, d_out, d_out2, s);
     }
     if (rc == 0) {
         cudaError_t e = cudaStreamSynchronize(s);
@@ -384,8 +416,9 @@ extern "C" int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mo
     }
     if (rc == 0 && acc_out) cudaMemcpy(acc_out, d_acc, out_elems * 4, cudaMemcpyDeviceToHost);
     if (rc == 0 && out) cudaMemcpy(out, d_out, out_elems, cudaMemcpyDeviceToHost);
+    if (rc == 0 && bn2) cudaMemcpy(out_bn2, d_out2, out_elems, cudaMemcpyDeviceToHost);
     cudaStreamDestroy(s);
-    cudaFree(d_in); cudaFree(d_res); cudaFree(d_out); cudaFree(d_w); cudaFree(d_acc); cudaFree(d_err);
+    cudaFree(d_in); cudaFree(d_res); cudaFree(d_out); cudaFree(d_out2); cudaFree(d_w); cudaFree(d_acc); cudaFree(d_err);
     for (float* q : tab) cudaFree(q);
     return rc;
 }

@@ -38,6 +38,11 @@ struct EpiTables {
     const float* slope;      // NULL: no PReLU
     const float* res_scale;  // NULL: no residual
     const float* inv_out;
+    // fused BN second output (all NULL when the layer has none)
+    const float* bn_in;      // scale of the int8 value just produced
+    const float* bn_scale;
+    const float* bn_offset;
+    const float* bn_inv;
 };
 
 // ---------------------------------------------------------------------------
@@ -99,7 +104,11 @@ __device__ __forceinline__ float ffcu_fc_fp(int dot, float ws, float bias)
 int ffcu_launch_quant(const float* in, int n_pix, const float* inv3, int8_t* out4, cudaStream_t s);
 int ffcu_launch_conv_simt(const ffcu_layer& L, int batch, int mode, const int8_t* in, const int8_t* w,
                           const EpiTables& t, const int8_t* res, int32_t* acc_out, int8_t* out,
-                          cudaStream_t s);
+                          int8_t* out_bn2, cudaStream_t s);
+// Fused stem: fp32 input -> per-channel int8 quantise -> conv3x3 3->64 -> epilogue (+BN second output).
+// q_out (optional) receives the quantised input as 4-byte pixels.
+int ffcu_launch_stem(const float* in_f32, const float* inv3, const int8_t* w, const EpiTables& t, int batch,
+                     int mode, int8_t* out, int8_t* out_bn2, int8_t* q_out, cudaStream_t s);
 int ffcu_launch_bn(const int8_t* in, int8_t* out, size_t n_pos, int C, const float* in_scale,
                    const float* bn_scale, const float* bn_offset, const float* inv_out, cudaStream_t s);
 int ffcu_launch_fc_simt(const int8_t* act, const int8_t* w, const float* w_scale, const float* bias,
@@ -113,4 +122,4 @@ struct TcPlan;   // opaque: tile shape, TMA descriptors, launch geometry for one
 TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, const int8_t* d_w, int device);
 void    ffcu_tc_free(TcPlan* p);
 int     ffcu_tc_launch(const TcPlan* p, int batch, int mode, const EpiTables& t, const int8_t* res,
-                       int32_t* acc_out, void* out, int* d_err, cudaStream_t s);
+                       int32_t* acc_out, void* out, int8_t* out_bn2, int* d_err, cudaStream_t s);

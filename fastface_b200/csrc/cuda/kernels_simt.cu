@@ -46,6 +46,7 @@ template <bool CONTRACT>
 __global__ void conv_simt_kernel(const int8_t* __restrict__ in, const int8_t* __restrict__ w,
                                  EpiTables t, const int8_t* __restrict__ res,
                                  int32_t* __restrict__ acc_out, int8_t* __restrict__ out,
+                                 int8_t* __restrict__ out_bn2,
                                  int B, int H, int W, int Cp, int Cout, int Kh, int Kw,
                                  int stride, int pad, int Ho, int Wo)
 {
@@ -87,7 +88,8 @@ __global__ void conv_simt_kernel(const int8_t* __restrict__ in, const int8_t* __
     int rw = 0;
     const bool has_res = (res != nullptr) && (t.res_scale != nullptr);
     if (has_res) rw = *(const int*)(res + o);
-    unsigned packed = 0;
+    unsigned packed = 0, packed2 = 0;
+    const bool has_bn2 = (out_bn2 != nullptr) && (t.bn_in != nullptr);
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         int c = co + j;
@@ -97,22 +99,27 @@ __global__ void conv_simt_kernel(const int8_t* __restrict__ in, const int8_t* __
                                          t.slope != nullptr, t.slope ? __ldg(t.slope + c) : 0.0f);
         int q = ffcu_requant(v, __ldg(t.inv_out + c));
         packed |= (unsigned)(q & 0xff) << (8 * j);
+        if (has_bn2) {
+            int q2 = ffcu_bn_q(q, __ldg(t.bn_in + c), __ldg(t.bn_scale + c), __ldg(t.bn_offset + c), __ldg(t.bn_inv + c));
+            packed2 |= (unsigned)(q2 & 0xff) << (8 * j);
+        }
     }
     *(unsigned*)(out + o) = packed;
+    if (has_bn2) *(unsigned*)(out_bn2 + o) = packed2;
 }
 
 int ffcu_launch_conv_simt(const ffcu_layer& L, int batch, int mode, const int8_t* in, const int8_t* w,
                           const EpiTables& t, const int8_t* res, int32_t* acc_out, int8_t* out,
-                          cudaStream_t s)
+                          int8_t* out_bn2, cudaStream_t s)
 {
     long total = (long)batch * L.Ho * L.Wo * (L.Cout / 4);
     int threads = 256;
     long blocks = (total + threads - 1) / threads;
     if (mode)
-        conv_simt_kernel<true><<<(unsigned)blocks, threads, 0, s>>>(in, w, t, res, acc_out, out, batch, L.H, L.W,
+        conv_simt_kernel<true><<<(unsigned)blocks, threads, 0, s>>>(in, w, t, res, acc_out, out, out_bn2, batch, L.H, L.W,
             L.Cin_pad, L.Cout, L.Kh, L.Kw, L.stride, L.pad, L.Ho, L.Wo);
     else
-        conv_simt_kernel<false><<<(unsigned)blocks, threads, 0, s>>>(in, w, t, res, acc_out, out, batch, L.H, L.W,
+        conv_simt_kernel<false><<<(unsigned)blocks, threads, 0, s>>>(in, w, t, res, acc_out, out, out_bn2, batch, L.H, L.W,
             L.Cin_pad, L.Cout, L.Kh, L.Kw, L.stride, L.pad, L.Ho, L.Wo);
     FFCU_CHECK(cudaGetLastError());
     return 0;
@@ -228,6 +235,115 @@ int ffcu_launch_fc_simt(const int8_t* act, const int8_t* w, const float* w_scale
     dim3 grid(N / FC_TN, (batch + FC_TB - 1) / FC_TB);
     if (mode) fc_simt_kernel<true><<<grid, 256, 0, s>>>(act, w, w_scale, bias, batch, N, K, out);
     else      fc_simt_kernel<false><<<grid, 256, 0, s>>>(act, w, w_scale, bias, batch, N, K, out);
+    FFCU_CHECK(cudaGetLastError());
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Fused stem: fp32 HWC input -> per-channel int8 quantise (ties-to-even) ->
+// conv3x3 s1 p1, 3 -> 64 channels (dp4a over (c0,c1,c2,0) words) -> PReLU epilogue
+// -> int8 NHWC, plus the following BN pass as a second output.
+// Takes over quantize_fp32_nhwc_to_int8_per_channel + the first conv + its epilogue
+// + the first BN (reference kernels/int8_epilogue.c:231-247, kernels/conv2d_nhwc.c:179-220,
+// kernels/int8_epilogue.c:25-112 and :253-318) in one pass over the image:
+// 150 528 B read and 2 x 802 816 B written per face.
+// A block owns a 16x16 output tile: the 18x18 input patch is quantised once into
+// shared memory, weights ([tap][co] words) and the per-channel tables sit there too.
+// ---------------------------------------------------------------------------
+#define STEM_T 16
+template <bool CONTRACT>
+__global__ void __launch_bounds__(256) stem_kernel(const float* __restrict__ in, const float* __restrict__ inv3,
+                                                   const int8_t* __restrict__ w, EpiTables t,
+                                                   int8_t* __restrict__ out, int8_t* __restrict__ out2,
+                                                   int* __restrict__ q_out)
+{
+    constexpr int H = 112, W = 112, C = 64, P = STEM_T + 2;
+    __shared__ int s_in[P * P];
+    __shared__ __align__(16) int s_w[9 * C];          // [tap][co]
+    __shared__ __align__(16) float s_tab[8 * C];      // w_scale, bias, slope, inv_out, bn_in, bn_scale, bn_offset, bn_inv
+    const int b = blockIdx.z;
+    const int x0 = blockIdx.x * STEM_T, y0 = blockIdx.y * STEM_T;
+    const float i0 = __ldg(inv3), i1 = __ldg(inv3 + 1), i2 = __ldg(inv3 + 2);
+    const bool has_bn2 = (out2 != nullptr) && (t.bn_in != nullptr);
+    for (int i = threadIdx.x; i < P * P; i += 256) {
+        int py = y0 - 1 + i / P, px = x0 - 1 + i % P;
+        int v = 0;
+        if (py >= 0 && py < H && px >= 0 && px < W) {
+            const float* x = in + (((size_t)b * H + py) * W + px) * 3;
+            int q0 = max(-128, min(127, __float2int_rn(__fmul_rn(__ldg(x), i0))));
+            int q1 = max(-128, min(127, __float2int_rn(__fmul_rn(__ldg(x + 1), i1))));
+            int q2 = max(-128, min(127, __float2int_rn(__fmul_rn(__ldg(x + 2), i2))));
+            v = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16);
+        }
+        s_in[i] = v;
+    }
+    for (int i = threadIdx.x; i < 9 * C; i += 256) {
+        int tap = i / C, co = i % C;
+        s_w[i] = __ldg((const int*)w + co * 9 + tap);     // global layout [co][tap] words
+    }
+    for (int i = threadIdx.x; i < C; i += 256) {
+        s_tab[0 * C + i] = t.w_scale[i]; s_tab[1 * C + i] = t.bias[i];
+        s_tab[2 * C + i] = t.slope ? t.slope[i] : 0.0f; s_tab[3 * C + i] = t.inv_out[i];
+        if (has_bn2) {
+            s_tab[4 * C + i] = t.bn_in[i]; s_tab[5 * C + i] = t.bn_scale[i];
+            s_tab[6 * C + i] = t.bn_offset[i]; s_tab[7 * C + i] = t.bn_inv[i];
+        }
+    }
+    __syncthreads();
+    const int tx = threadIdx.x % STEM_T, ty = threadIdx.x / STEM_T;
+    int a[9];
+#pragma unroll
+    for (int kh = 0; kh < 3; kh++)
+#pragma unroll
+        for (int kw = 0; kw < 3; kw++) a[kh * 3 + kw] = s_in[(ty + kh) * P + tx + kw];
+    const size_t pix = ((size_t)b * H + (y0 + ty)) * W + (x0 + tx);
+    if (q_out) q_out[pix] = a[4];
+    const bool has_slope = t.slope != nullptr;
+    int4* dst = (int4*)(out + pix * C);
+    int4* dst2 = (int4*)(out2 + pix * C);
+#pragma unroll 1
+    for (int g16 = 0; g16 < C / 16; g16++) {          // 16 channels -> one 16-byte store
+        int wo[4], wo2[4];
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            const int co = g16 * 16 + g * 4;
+            int acc0 = 0, acc1 = 0, acc2 = 0, acc3 = 0;
+#pragma unroll
+            for (int tap = 0; tap < 9; tap++) {
+                const int4 ww = *(const int4*)&s_w[tap * C + co];
+                acc0 = __dp4a(a[tap], ww.x, acc0); acc1 = __dp4a(a[tap], ww.y, acc1);
+                acc2 = __dp4a(a[tap], ww.z, acc2); acc3 = __dp4a(a[tap], ww.w, acc3);
+            }
+            const float4 ws = *(const float4*)&s_tab[0 * C + co];
+            const float4 bi = *(const float4*)&s_tab[1 * C + co];
+            const float4 sl = *(const float4*)&s_tab[2 * C + co];
+            const float4 iv = *(const float4*)&s_tab[3 * C + co];
+            int q0 = ffcu_requant(ffcu_conv_fp<CONTRACT>(acc0, ws.x, bi.x, false, 0, 0.0f, has_slope, sl.x), iv.x);
+            int q1 = ffcu_requant(ffcu_conv_fp<CONTRACT>(acc1, ws.y, bi.y, false, 0, 0.0f, has_slope, sl.y), iv.y);
+            int q2 = ffcu_requant(ffcu_conv_fp<CONTRACT>(acc2, ws.z, bi.z, false, 0, 0.0f, has_slope, sl.z), iv.z);
+            int q3 = ffcu_requant(ffcu_conv_fp<CONTRACT>(acc3, ws.w, bi.w, false, 0, 0.0f, has_slope, sl.w), iv.w);
+            wo[g] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
+            if (has_bn2) {
+                const float4 b_i = *(const float4*)&s_tab[4 * C + co];
+                const float4 b_s = *(const float4*)&s_tab[5 * C + co];
+                const float4 b_o = *(const float4*)&s_tab[6 * C + co];
+                const float4 b_v = *(const float4*)&s_tab[7 * C + co];
+                int r0 = ffcu_bn_q(q0, b_i.x, b_s.x, b_o.x, b_v.x), r1 = ffcu_bn_q(q1, b_i.y, b_s.y, b_o.y, b_v.y);
+                int r2 = ffcu_bn_q(q2, b_i.z, b_s.z, b_o.z, b_v.z), r3 = ffcu_bn_q(q3, b_i.w, b_s.w, b_o.w, b_v.w);
+                wo2[g] = (r0 & 0xff) | ((r1 & 0xff) << 8) | ((r2 & 0xff) << 16) | ((r3 & 0xff) << 24);
+            }
+        }
+        dst[g16] = make_int4(wo[0], wo[1], wo[2], wo[3]);
+        if (has_bn2) dst2[g16] = make_int4(wo2[0], wo2[1], wo2[2], wo2[3]);
+    }
+}
+
+int ffcu_launch_stem(const float* in_f32, const float* inv3, const int8_t* w, const EpiTables& t, int batch,
+                     int mode, int8_t* out, int8_t* out_bn2, int8_t* q_out, cudaStream_t s)
+{
+    dim3 grid(112 / STEM_T, 112 / STEM_T, batch);
+    if (mode) stem_kernel<true><<<grid, 256, 0, s>>>(in_f32, inv3, w, t, out, out_bn2, (int*)q_out);
+    else      stem_kernel<false><<<grid, 256, 0, s>>>(in_f32, inv3, w, t, out, out_bn2, (int*)q_out);
     FFCU_CHECK(cudaGetLastError());
     return 0;
 }

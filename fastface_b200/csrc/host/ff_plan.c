@@ -60,6 +60,13 @@ static int buf_get(bufset* b)
         if (b->ref[i] == 0) { b->ref[i] = 1; if (i + 1 > b->used) b->used = i + 1; return i; }
     return -1;
 }
+/* a free buffer other than x and y (the operands of the launch that will also write it) */
+static int buf_get_not(bufset* b, int x, int y)
+{
+    for (int i = 0; i < FF_MAX_BUFS; i++)
+        if (b->ref[i] == 0 && i != x && i != y) { b->ref[i] = 1; if (i + 1 > b->used) b->used = i + 1; return i; }
+    return -1;
+}
 static void buf_hold(bufset* b, int i) { if (i >= 0) b->ref[i]++; }
 static void buf_drop(bufset* b, int i) { if (i >= 0 && b->ref[i] > 0) b->ref[i]--; }
 
@@ -72,6 +79,7 @@ static ffcu_layer* push_layer(ff_plan* p, int* cap)
     ffcu_layer* l = &p->layers[p->n_layers++];
     memset(l, 0, sizeof *l);
     l->src_buf = l->dst_buf = l->res_buf = -1;
+    l->bn2_dst_buf = -1; l->bn2_op_index = -1;
     return l;
 }
 
@@ -81,6 +89,8 @@ int ff_plan_build(ff_plan* p, const ff_model* m)
     int cap = 0;
     bufset bs; memset(&bs, 0, sizeof bs);
     const int n_ops = m->n_ops;
+    const char* fb = getenv("FF_FUSE_BN");
+    const int fuse_bn = !(fb && fb[0] == '0');
 
     /* scale state carried by the reference loop */
     float A_scale = m->input_scale;
@@ -192,20 +202,35 @@ int ff_plan_build(ff_plan* p, const ff_model* m)
         case FF_OP_BN: {
             int C = cur.C;
             if (op->n != C) { ff_set_error("op %d: BN size %d != %d channels", i, op->n, C); return -2; }
-            ffcu_layer* l = push_layer(p, &cap);
-            l->kind = FFCU_BN; l->op_index = i;
-            l->src_buf = cur_buf;
-            l->Cin = l->Cout = C; l->H = l->Ho = cur.H; l->W = l->Wo = cur.W;
             const float* in_pc = (m->has_pc && A_pc) ? A_pc : NULL;
             if (in_pc && A_pc_len < C) { ff_set_error("op %d: input scale length %d < %d", i, A_pc_len, C); return -2; }
-            l->in_scale = per_channel(p, in_pc, A_scale, C);
-            l->bn_scale = copy_f32(p, op->bn_scale, C);
-            l->bn_offset = copy_f32(p, op->bn_offset, C);
             const float* inv_pc = (m->has_pc && m->pc_inv[i] && (int)m->pc_len[i] == C) ? m->pc_inv[i] : NULL;
-            l->inv_out = per_channel(p, inv_pc, 1.0f / (next_scale + 1e-9f), C);
-            int dst = buf_get(&bs);
+            ffcu_layer* prev = p->n_layers ? &p->layers[p->n_layers - 1] : NULL;
+            const int can_fuse = fuse_bn && prev && prev->kind == FFCU_CONV && prev->dst_buf == cur_buf
+                                 && prev->bn2_dst_buf < 0 && prev->Cout == C;
+            /* a fused second output must not land in a buffer the same launch still reads */
+            int dst = can_fuse ? buf_get_not(&bs, prev->src_buf, prev->res_buf) : buf_get(&bs);
             if (dst < 0) { ff_set_error("activation buffer pool exhausted"); return -2; }
-            l->dst_buf = dst;
+            /* The BN input is always the tensor the previous launch wrote; BN is a pure
+             * per-element function of that int8 value, so it rides along as a second output of
+             * the producing conv's epilogue (saves one read of the tensor and one launch). */
+            if (can_fuse) {
+                prev->bn2_dst_buf = dst; prev->bn2_op_index = i;
+                prev->bn2_in_scale = per_channel(p, in_pc, A_scale, C);
+                prev->bn2_scale = copy_f32(p, op->bn_scale, C);
+                prev->bn2_offset = copy_f32(p, op->bn_offset, C);
+                prev->bn2_inv_out = per_channel(p, inv_pc, 1.0f / (next_scale + 1e-9f), C);
+            } else {
+                ffcu_layer* l = push_layer(p, &cap);
+                l->kind = FFCU_BN; l->op_index = i;
+                l->src_buf = cur_buf;
+                l->Cin = l->Cout = C; l->H = l->Ho = cur.H; l->W = l->Wo = cur.W;
+                l->in_scale = per_channel(p, in_pc, A_scale, C);
+                l->bn_scale = copy_f32(p, op->bn_scale, C);
+                l->bn_offset = copy_f32(p, op->bn_offset, C);
+                l->inv_out = per_channel(p, inv_pc, 1.0f / (next_scale + 1e-9f), C);
+                l->dst_buf = dst;
+            }
             buf_drop(&bs, cur_buf); cur_buf = dst;
             A_scale = next_scale;
             if (m->has_pc && m->pc_scale[i]) { A_pc = m->pc_scale[i]; A_pc_len = (int)m->pc_len[i]; }

@@ -44,6 +44,15 @@ typedef struct {
     const float* in_scale;   /* BN: scale of the int8 input                          */
     const float* bn_scale;   /* BN                                                   */
     const float* bn_offset;  /* BN                                                   */
+    /* FFCU_CONV only: a BN pass fused as a SECOND output of the epilogue.  The int8 result q
+     * is stored to dst_buf as usual and BN(q) (same arithmetic as a FFCU_BN layer reading
+     * dst_buf) is stored to bn2_dst_buf.  bn2_dst_buf < 0: none.                            */
+    int bn2_dst_buf;
+    int bn2_op_index;          /* FFW4 op index of the fused BN (dump-point id)             */
+    const float* bn2_in_scale;
+    const float* bn2_scale;
+    const float* bn2_offset;
+    const float* bn2_inv_out;
 } ffcu_layer;
 
 /* Devices visible to the process; <0 on a CUDA error. */
@@ -98,7 +107,7 @@ int ffcu_layer_info(const ffcu_ctx* c, int k, ffcu_layer* out, int* uses_tc);
  * int32 accumulators and/or the int8 epilogue output. impl: 0 = tensor-core
  * implicit GEMM, 1 = SIMT reference kernel. */
 int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mode, int impl,
-                   const int8_t* in, const int8_t* res, int32_t* acc_out, int8_t* out);
+                   const int8_t* in, const int8_t* res, int32_t* acc_out, int8_t* out, int8_t* out_bn2);
 
 const char* ffcu_last_error(void);
 

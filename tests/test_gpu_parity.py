@@ -110,6 +110,50 @@ def test_single_layer_vs_oracle(built_lib, case, impl):
         assert not msg, msg
 
 
+@pytest.mark.parametrize("case", [LAYER_CASES[0], LAYER_CASES[3], LAYER_CASES[5], LAYER_CASES[7], LAYER_CASES[13]],
+                         ids=lambda c: c[0])
+@pytest.mark.parametrize("impl", ["tc", "simt"])
+def test_fused_bn_second_output(built_lib, case, impl):
+    """The BN pass that follows a conv rides along as a second epilogue output; it must equal
+    bn_prelu_requant_int8 (kernels/int8_epilogue.c:253-318) applied to the conv's int8 output."""
+    name, B, H, Cin, Cout, k, stride, sl, rs = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()) + 1)
+    L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
+    in_scale = (np.float32(1) / L["inv"]).astype(np.float32)
+    bn_s = rng.uniform(0.5, 1.5, Cout).astype(np.float32)
+    bn_o = (rng.standard_normal(Cout) * 0.1).astype(np.float32)
+    bn_inv = (np.float32(1) / (rng.uniform(0.005, 0.05, Cout).astype(np.float32) + np.float32(1e-9))).astype(np.float32)
+    acc, out, out2 = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
+                                  slope=L["slope"], res=L["res"], res_scale=L["rs"], impl=impl,
+                                  bn2=(in_scale, bn_s, bn_o, bn_inv))
+    acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
+                               L["res"], L["rs"], ffo.CONTRACT)
+    lib = _libffo()
+    want2 = np.zeros_like(out_o)
+    lib.ffo_bn_requant.argtypes = [C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                   C.c_float, C.c_void_p, C.c_int, C.c_int]
+    lib.ffo_bn_requant(out_o.ctypes.data, 1.0, in_scale.ctypes.data, bn_s.ctypes.data, bn_o.ctypes.data, None,
+                       bn_inv.ctypes.data, 1.0, want2.ctypes.data, out_o.size // Cout, Cout)
+    assert np.array_equal(out, out_o)
+    msg = describe_mismatch("fused BN output", out2, want2)
+    assert not msg, msg
+
+
+def test_unfused_plan_agrees(built_lib, model_root, ffw4, oracle, monkeypatch):
+    """FF_FUSE_BN=0 / FF_FUSE_STEM=0 (separate BN passes, separate quantise + stem conv) give
+    the same bytes as the fused default."""
+    faces = synth.faces(3, seed=41)
+    want = oracle.forward(faces, ffo.CONTRACT)
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=3) as e:
+        n_fused = e.launches_per_forward
+        assert np.array_equal(e.embed_batch(faces), want)
+    monkeypatch.setenv("FF_FUSE_BN", "0")
+    monkeypatch.setenv("FF_FUSE_STEM", "0")
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=3) as e:
+        assert e.launches_per_forward == 80 and n_fused == 54
+        assert np.array_equal(e.embed_batch(faces), want)
+
+
 def test_stem_conv_simt_vs_oracle(built_lib):
     """Cin=3 stem (K=27): CUDA-core dp4a kernel."""
     rng = np.random.default_rng(3)
