@@ -17,7 +17,7 @@
 //   accumulators double-buffered in TMEM so the epilogue of tile i overlaps the
 //   MMAs of tile i+1.
 // * Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (+TMEM alloc),
-//   warps 2..5 = epilogue (tcgen05.ld -> exact fp32 chain -> int8 NHWC stores).
+//   warps 2..9 = epilogue (tcgen05.ld -> exact fp32 chain -> int8 NHWC stores).
 // * Every wait is bounded; on expiry the kernel records an error word, drains
 //   and frees its TMEM, and returns.  No cluster launch, no multicast.
 
@@ -26,7 +26,6 @@
 #include <stdio.h>
 #include <string.h>
 
-#define TC_THREADS 192
 #define TC_TILE_M 128
 #define TC_MAX_COUT 512
 #define TC_WAIT_NS 2000000000ull   // 2 s per wait
@@ -144,7 +143,7 @@ __host__ __device__ constexpr uint32_t idesc_i8(int bn)
 }
 
 // ---------------------------------------------------------------------------
-// kernel
+// kernel parameters, shared state, epilogue
 // ---------------------------------------------------------------------------
 struct TcParams {
     EpiTables t;
@@ -163,44 +162,21 @@ struct TcParams {
 
 #define TC_MAX_STAGES 8
 #define TC_NTAB 9          // w_scale, bias, slope, res_scale, inv_out, bn_in, bn_scale, bn_offset, bn_inv
+#define TC_EPI_WARPS 8     // warps 2..9: two per TMEM lane quarter, each takes half the columns
+#define TC_THREADS (32 * (2 + TC_EPI_WARPS))
 
 struct TcShared {                 // lives after the stage ring and the tables
     uint64_t full[TC_MAX_STAGES];
     uint64_t empty[TC_MAX_STAGES];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
+    uint64_t w_full;              // weight-stationary kernel: weights have landed
     uint32_t tmem_base;
     int abort_flag;
 };
 
-template <int BN, int KC, bool CONTRACT, bool OUT_F32>
-__global__ void __launch_bounds__(TC_THREADS, 1)
-conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
+__device__ __forceinline__ void tc_load_tables(float* tab, const TcParams& p)
 {
-    extern __shared__ uint8_t smem_raw[];
-    // stage ring must start on a 1024-byte boundary (swizzle atoms)
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    constexpr int A_BYTES = TC_TILE_M * KC;
-    constexpr int B_BYTES = BN * KC;
-    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;    // 128 / 256 / 512: powers of two
-    constexpr uint32_t IDESC = idesc_i8(BN);
-
-    float* tab = (float*)(smem + (size_t)p.stages * STAGE_BYTES);       // [TC_NTAB][TC_MAX_COUT]
-    TcShared* sh = (TcShared*)(tab + TC_NTAB * TC_MAX_COUT);
-
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    const int kblocks = p.taps * p.cin_blocks;
-
-    // ---- set-up -----------------------------------------------------------
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; s++) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), 1); }
-        for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&sh->acc_full[a]), 1); mbar_init(smem_u32(&sh->acc_empty[a]), 4); }
-        sh->abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
     for (int i = threadIdx.x; i < p.Cout; i += TC_THREADS) {
         tab[0 * TC_MAX_COUT + i] = p.t.w_scale[i];
         tab[1 * TC_MAX_COUT + i] = p.t.bias[i];
@@ -214,18 +190,194 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             tab[8 * TC_MAX_COUT + i] = p.t.bn_inv[i];
         }
     }
+}
+
+// One 32-column chunk of one accumulator row: v[32] int32 -> outputs at element offset o
+// (= pixel * Cout + first channel cb).  Replaces fused_epilogue_int8 for those 32 values
+// (reference kernels/int8_epilogue.c:25-112), optionally followed by the next BN pass
+// (:253-318) as a second output.
+template <bool CONTRACT, bool OUT_F32>
+__device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float* tab, const int (&v)[32],
+                                                  int cb, size_t o, bool has_res, bool has_slope, bool has_bn2)
+{
+    if (p.acc_out) {
+        int4* dst = (int4*)(p.acc_out + o);
+#pragma unroll
+        for (int g = 0; g < 8; g++) dst[g] = make_int4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+    }
+    if (OUT_F32) {
+        float4* dst = (float4*)((float*)p.out + o);
+#pragma unroll
+        for (int g = 0; g < 8; g++) {
+            const float4 ws = *(const float4*)&tab[0 * TC_MAX_COUT + cb + 4 * g];
+            const float4 bi = *(const float4*)&tab[1 * TC_MAX_COUT + cb + 4 * g];
+            float4 r;
+            r.x = ffcu_fc_fp<CONTRACT>(v[4 * g + 0], ws.x, bi.x);
+            r.y = ffcu_fc_fp<CONTRACT>(v[4 * g + 1], ws.y, bi.y);
+            r.z = ffcu_fc_fp<CONTRACT>(v[4 * g + 2], ws.z, bi.z);
+            r.w = ffcu_fc_fp<CONTRACT>(v[4 * g + 3], ws.w, bi.w);
+            dst[g] = r;
+        }
+        return;
+    }
+    int rw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (has_res) {
+        const int4* rp = (const int4*)(p.res + o);
+        int4 r0 = rp[0], r1 = rp[1];
+        rw[0] = r0.x; rw[1] = r0.y; rw[2] = r0.z; rw[3] = r0.w;
+        rw[4] = r1.x; rw[5] = r1.y; rw[6] = r1.z; rw[7] = r1.w;
+    }
+    int ow_[8], ow2_[8];
+#pragma unroll
+    for (int g = 0; g < 8; g++) {
+        const float4 ws = *(const float4*)&tab[0 * TC_MAX_COUT + cb + 4 * g];
+        const float4 bi = *(const float4*)&tab[1 * TC_MAX_COUT + cb + 4 * g];
+        const float4 sl = *(const float4*)&tab[2 * TC_MAX_COUT + cb + 4 * g];
+        const float4 rs = *(const float4*)&tab[3 * TC_MAX_COUT + cb + 4 * g];
+        const float4 iv = *(const float4*)&tab[4 * TC_MAX_COUT + cb + 4 * g];
+        const int r = rw[g];
+        float f0 = ffcu_conv_fp<CONTRACT>(v[4 * g + 0], ws.x, bi.x, has_res, (int)(int8_t)(r & 0xff), rs.x, has_slope, sl.x);
+        float f1 = ffcu_conv_fp<CONTRACT>(v[4 * g + 1], ws.y, bi.y, has_res, (int)(int8_t)((r >> 8) & 0xff), rs.y, has_slope, sl.y);
+        float f2 = ffcu_conv_fp<CONTRACT>(v[4 * g + 2], ws.z, bi.z, has_res, (int)(int8_t)((r >> 16) & 0xff), rs.z, has_slope, sl.z);
+        float f3 = ffcu_conv_fp<CONTRACT>(v[4 * g + 3], ws.w, bi.w, has_res, (int)(int8_t)((r >> 24) & 0xff), rs.w, has_slope, sl.w);
+        int q0 = ffcu_requant(f0, iv.x), q1 = ffcu_requant(f1, iv.y);
+        int q2 = ffcu_requant(f2, iv.z), q3 = ffcu_requant(f3, iv.w);
+        ow_[g] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
+        if (has_bn2) {
+            const float4 bi_ = *(const float4*)&tab[5 * TC_MAX_COUT + cb + 4 * g];
+            const float4 bs_ = *(const float4*)&tab[6 * TC_MAX_COUT + cb + 4 * g];
+            const float4 bo_ = *(const float4*)&tab[7 * TC_MAX_COUT + cb + 4 * g];
+            const float4 bv_ = *(const float4*)&tab[8 * TC_MAX_COUT + cb + 4 * g];
+            int b0 = ffcu_bn_q(q0, bi_.x, bs_.x, bo_.x, bv_.x), b1 = ffcu_bn_q(q1, bi_.y, bs_.y, bo_.y, bv_.y);
+            int b2 = ffcu_bn_q(q2, bi_.z, bs_.z, bo_.z, bv_.z), b3 = ffcu_bn_q(q3, bi_.w, bs_.w, bo_.w, bv_.w);
+            ow2_[g] = (b0 & 0xff) | ((b1 & 0xff) << 8) | ((b2 & 0xff) << 16) | ((b3 & 0xff) << 24);
+        }
+    }
+    int4* dst = (int4*)((int8_t*)p.out + o);
+    dst[0] = make_int4(ow_[0], ow_[1], ow_[2], ow_[3]);
+    dst[1] = make_int4(ow_[4], ow_[5], ow_[6], ow_[7]);
+    if (has_bn2) {
+        int4* dst2 = (int4*)(p.out2 + o);
+        dst2[0] = make_int4(ow2_[0], ow2_[1], ow2_[2], ow2_[3]);
+        dst2[1] = make_int4(ow2_[4], ow2_[5], ow2_[6], ow2_[7]);
+    }
+}
+
+// Epilogue role shared by both kernels.  Warps 2..9: warp w reads TMEM lanes
+// [32*(w%4), +32) (the hardware's per-warp lane window) and the column half (w-2)/4.
+template <int BN, bool CONTRACT, bool OUT_F32>
+__device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float* tab, TcShared* sh,
+                                                 uint32_t tmem_base, volatile int* abort_flag, int warp, int lane)
+{
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int CHUNKS = BN / 32;                       // 2, 4 or 8
+    constexpr int PER = CHUNKS / 2;
+    const int row = q * 32 + lane;
+    const int iw = row % p.TW;
+    const int ih = (row / p.TW) % p.TH;
+    const int ib = row / (p.TW * p.TH);
+    const bool has_res = (p.res != nullptr) && (p.t.res_scale != nullptr);
+    const bool has_slope = p.t.slope != nullptr;
+    const bool has_bn2 = p.out2 != nullptr;
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, local++) {
+        const int tn = tile % p.tiles_n;
+        int m = tile / p.tiles_n;
+        const int tw = m % p.tiles_w; m /= p.tiles_w;
+        const int th = m % p.tiles_h;
+        const int tb = m / p.tiles_h;
+        const int ow = tw * p.TW + iw, oh = th * p.TH + ih, b = tb * p.TB + ib;
+        const bool valid = (ow < p.Wo) && (oh < p.Ho) && (b < p.batch);
+        const size_t pix = ((size_t)b * p.Ho + oh) * p.Wo + ow;
+        const int n0 = tn * BN;
+        const int a = local & 1;
+        const uint32_t aphase = (uint32_t)(local >> 1) & 1;
+        ok = mbar_wait(smem_u32(&sh->acc_full[a]), aphase, abort_flag, p.err, FFCU_ERR_EPI_TIMEOUT);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (uint32_t)(a * BN) + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+        for (int jj = 0; jj < PER; jj++) {
+            const int j = half * PER + jj;
+            int v[32];
+            tmem_ld32(taddr + (uint32_t)(j * 32), v);
+            if (!valid) continue;
+            const int cb = n0 + j * 32;
+            tc_epilogue_chunk<CONTRACT, OUT_F32>(p, tab, v, cb, pix * p.Cout + cb, has_res, has_slope, has_bn2);
+        }
+        // this warp's TMEM reads are complete (tcgen05.wait::ld inside tmem_ld32)
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[a]));
+    }
+}
+
+__device__ __forceinline__ void tc_setup(TcShared* sh, int stages, uint32_t tmem_cols, int warp)
+{
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; s++) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&sh->acc_full[a]), 1); mbar_init(smem_u32(&sh->acc_empty[a]), TC_EPI_WARPS); }
+        mbar_init(smem_u32(&sh->w_full), 1);
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&sh->tmem_base)), "r"((uint32_t)TMEM_COLS) : "memory");
+                     ::"r"(smem_u32(&sh->tmem_base)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+}
+
+__device__ __forceinline__ void tc_teardown(volatile int* abort_flag, uint32_t tmem_base, uint32_t tmem_cols, int warp)
+{
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        // a wait ran out: give bulk copies still in flight time to land before the
+        // shared memory is handed back (bounded: about 1 ms)
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// generic kernel: one TMA box per filter tap and channel slice
+// ---------------------------------------------------------------------------
+template <int BN, int KC, bool CONTRACT, bool OUT_F32>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    // stage ring must start on a 1024-byte boundary (swizzle atoms)
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int A_BYTES = TC_TILE_M * KC;
+    constexpr int B_BYTES = BN * KC;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;    // 128 / 256 / 512: powers of two
+    constexpr uint32_t IDESC = idesc_i8(BN);
+
+    float* tab = (float*)(smem + (size_t)p.stages * STAGE_BYTES);       // [TC_NTAB][TC_MAX_COUT]
+    TcShared* sh = (TcShared*)(tab + TC_NTAB * TC_MAX_COUT);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int kblocks = p.taps * p.cin_blocks;
+
+    tc_load_tables(tab, p);
+    tc_setup(sh, p.stages, TMEM_COLS, warp);
     const uint32_t tmem_base = sh->tmem_base;
     volatile int* abort_flag = &sh->abort_flag;
 
-    // ---- roles ------------------------------------------------------------
     if (warp == 0) {
         if (lane == 0) {
             // TMA producer
@@ -286,122 +438,113 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             }
         }
     } else {
-        // epilogue: warp w may only touch TMEM lanes [32*(w%4), 32*(w%4)+32)
-        const int q = warp & 3;
-        const int row = q * 32 + lane;
-        const int iw = row % p.TW;
-        const int ih = (row / p.TW) % p.TH;
-        const int ib = row / (p.TW * p.TH);
-        const bool has_res = (p.res != nullptr) && (p.t.res_scale != nullptr);
-        const bool has_slope = p.t.slope != nullptr;
-        const bool has_bn2 = p.out2 != nullptr;
-        int local = 0;
-        bool ok = true;
-        for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, local++) {
-            const int tn = tile % p.tiles_n;
-            int m = tile / p.tiles_n;
-            const int tw = m % p.tiles_w; m /= p.tiles_w;
-            const int th = m % p.tiles_h;
-            const int tb = m / p.tiles_h;
-            const int ow = tw * p.TW + iw, oh = th * p.TH + ih, b = tb * p.TB + ib;
-            const bool valid = (ow < p.Wo) && (oh < p.Ho) && (b < p.batch);
-            const size_t pix = ((size_t)b * p.Ho + oh) * p.Wo + ow;
-            const int n0 = tn * BN;
-            const int a = local & 1;
-            const uint32_t aphase = (uint32_t)(local >> 1) & 1;
-            ok = mbar_wait(smem_u32(&sh->acc_full[a]), aphase, abort_flag, p.err, FFCU_ERR_EPI_TIMEOUT);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t taddr = tmem_base + (uint32_t)(a * BN) + ((uint32_t)(q * 32) << 16);
-#pragma unroll 1
-            for (int j = 0; j < BN / 32; j++) {
-                int v[32];
-                tmem_ld32(taddr + (uint32_t)(j * 32), v);
-                if (!valid) continue;
-                const int cb = n0 + j * 32;
-                const size_t o = pix * p.Cout + cb;
-                if (p.acc_out) {
-                    int4* dst = (int4*)(p.acc_out + o);
-#pragma unroll
-                    for (int g = 0; g < 8; g++) dst[g] = make_int4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
-                }
-                if (OUT_F32) {
-                    float4* dst = (float4*)((float*)p.out + o);
-#pragma unroll
-                    for (int g = 0; g < 8; g++) {
-                        const float4 ws = *(const float4*)&tab[0 * TC_MAX_COUT + cb + 4 * g];
-                        const float4 bi = *(const float4*)&tab[1 * TC_MAX_COUT + cb + 4 * g];
-                        float4 r;
-                        r.x = ffcu_fc_fp<CONTRACT>(v[4 * g + 0], ws.x, bi.x);
-                        r.y = ffcu_fc_fp<CONTRACT>(v[4 * g + 1], ws.y, bi.y);
-                        r.z = ffcu_fc_fp<CONTRACT>(v[4 * g + 2], ws.z, bi.z);
-                        r.w = ffcu_fc_fp<CONTRACT>(v[4 * g + 3], ws.w, bi.w);
-                        dst[g] = r;
-                    }
-                } else {
-                    int rw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                    if (has_res) {
-                        const int4* rp = (const int4*)(p.res + o);
-                        int4 r0 = rp[0], r1 = rp[1];
-                        rw[0] = r0.x; rw[1] = r0.y; rw[2] = r0.z; rw[3] = r0.w;
-                        rw[4] = r1.x; rw[5] = r1.y; rw[6] = r1.z; rw[7] = r1.w;
-                    }
-                    int ow_[8], ow2_[8];
-#pragma unroll
-                    for (int g = 0; g < 8; g++) {
-                        const float4 ws = *(const float4*)&tab[0 * TC_MAX_COUT + cb + 4 * g];
-                        const float4 bi = *(const float4*)&tab[1 * TC_MAX_COUT + cb + 4 * g];
-                        const float4 sl = *(const float4*)&tab[2 * TC_MAX_COUT + cb + 4 * g];
-                        const float4 rs = *(const float4*)&tab[3 * TC_MAX_COUT + cb + 4 * g];
-                        const float4 iv = *(const float4*)&tab[4 * TC_MAX_COUT + cb + 4 * g];
-                        const int r = rw[g];
-                        float f0 = ffcu_conv_fp<CONTRACT>(v[4 * g + 0], ws.x, bi.x, has_res, (int)(int8_t)(r & 0xff), rs.x, has_slope, sl.x);
-                        float f1 = ffcu_conv_fp<CONTRACT>(v[4 * g + 1], ws.y, bi.y, has_res, (int)(int8_t)((r >> 8) & 0xff), rs.y, has_slope, sl.y);
-                        float f2 = ffcu_conv_fp<CONTRACT>(v[4 * g + 2], ws.z, bi.z, has_res, (int)(int8_t)((r >> 16) & 0xff), rs.z, has_slope, sl.z);
-                        float f3 = ffcu_conv_fp<CONTRACT>(v[4 * g + 3], ws.w, bi.w, has_res, (int)(int8_t)((r >> 24) & 0xff), rs.w, has_slope, sl.w);
-                        int q0 = ffcu_requant(f0, iv.x), q1 = ffcu_requant(f1, iv.y);
-                        int q2 = ffcu_requant(f2, iv.z), q3 = ffcu_requant(f3, iv.w);
-                        ow_[g] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
-                        if (has_bn2) {
-                            const float4 bi_ = *(const float4*)&tab[5 * TC_MAX_COUT + cb + 4 * g];
-                            const float4 bs_ = *(const float4*)&tab[6 * TC_MAX_COUT + cb + 4 * g];
-                            const float4 bo_ = *(const float4*)&tab[7 * TC_MAX_COUT + cb + 4 * g];
-                            const float4 bv_ = *(const float4*)&tab[8 * TC_MAX_COUT + cb + 4 * g];
-                            int b0 = ffcu_bn_q(q0, bi_.x, bs_.x, bo_.x, bv_.x), b1 = ffcu_bn_q(q1, bi_.y, bs_.y, bo_.y, bv_.y);
-                            int b2 = ffcu_bn_q(q2, bi_.z, bs_.z, bo_.z, bv_.z), b3 = ffcu_bn_q(q3, bi_.w, bs_.w, bo_.w, bv_.w);
-                            ow2_[g] = (b0 & 0xff) | ((b1 & 0xff) << 8) | ((b2 & 0xff) << 16) | ((b3 & 0xff) << 24);
-                        }
-                    }
-                    int4* dst = (int4*)((int8_t*)p.out + o);
-                    dst[0] = make_int4(ow_[0], ow_[1], ow_[2], ow_[3]);
-                    dst[1] = make_int4(ow_[4], ow_[5], ow_[6], ow_[7]);
-                    if (has_bn2) {
-                        int4* dst2 = (int4*)(p.out2 + o);
-                        dst2[0] = make_int4(ow2_[0], ow2_[1], ow2_[2], ow2_[3]);
-                        dst2[1] = make_int4(ow2_[4], ow2_[5], ow2_[6], ow2_[7]);
-                    }
-                }
-            }
-            // all of this warp's TMEM reads are complete (tcgen05.wait::ld inside tmem_ld32)
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[a]));
-        }
+        tc_epilogue_role<BN, CONTRACT, OUT_F32>(p, tab, sh, tmem_base, abort_flag, warp, lane);
     }
+    tc_teardown(abort_flag, tmem_base, TMEM_COLS, warp);
+}
 
-    // ---- teardown -----------------------------------------------------------
-    tc_fence_before();
-    __syncthreads();
-    if (*abort_flag && threadIdx.x == 0) {
-        // a wait ran out: give bulk copies still in flight time to land before the
-        // shared memory is handed back (bounded: about 1 ms)
-        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+// ---------------------------------------------------------------------------
+// weight-stationary kernel for the 64-input-channel 3x3 stride-1 layers
+// (112x112 and 56x56 maps: 20% of the network's MACs but, tap by tap, its largest
+// shared-memory fill traffic).
+//   * all 9 weight taps ([tap][BN rows][64 B], 36 KB or 72 KB) are loaded once per CTA
+//     and stay in shared memory for every tile the CTA processes;
+//   * output tile = 8 wide x 16 high pixels of one image.  Per tile three boxes
+//     {64 B, 8, 18, 1} are loaded, one per kw, each holding rows y0-1 .. y0+16: an 8-row
+//     swizzle group is one image row of the box, so the three kh taps are the same box
+//     read at group offsets 0, 1, 2 (descriptor start + kh * 512 B).  Activation bytes
+//     fetched per tile drop from 9 x 128 to 3 x 144 rows.
+// ---------------------------------------------------------------------------
+#define WS_TW 8
+#define WS_TH 16
+#define WS_BOX_ROWS (WS_TW * (WS_TH + 2))          // 144 rows of 64 B per kw box
+#define WS_A_BYTES (3 * WS_BOX_ROWS * 64)          // 27 648 B per tile
+
+template <int BN, bool CONTRACT>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int KC = 64;
+    constexpr int W_TAP_BYTES = BN * KC;
+    constexpr int W_BYTES = 9 * W_TAP_BYTES;
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+    constexpr uint32_t IDESC = idesc_i8(BN);
+
+    uint8_t* s_w = smem;                                        // [9][BN][64]
+    uint8_t* s_a = smem + W_BYTES;                              // [stages][3][144][64]
+    float* tab = (float*)(s_a + (size_t)p.stages * WS_A_BYTES);
+    TcShared* sh = (TcShared*)(tab + TC_NTAB * TC_MAX_COUT);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    tc_load_tables(tab, p);
+    tc_setup(sh, p.stages, TMEM_COLS, warp);
+    const uint32_t tmem_base = sh->tmem_base;
+    volatile int* abort_flag = &sh->abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t wbar = smem_u32(&sh->w_full);
+            mbar_expect_tx(wbar, W_BYTES);
+            for (int tap = 0; tap < 9; tap++)
+                tma_load_2d(smem_u32(s_w + tap * W_TAP_BYTES), &mapB, wbar, tap * p.Cp, 0);
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+                int m = tile;
+                const int tw = m % p.tiles_w; m /= p.tiles_w;
+                const int th = m % p.tiles_h;
+                const int b = m / p.tiles_h;
+                ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, p.err, FFCU_ERR_EMPTY_TIMEOUT);
+                if (!ok) break;
+                const uint32_t bar = smem_u32(&sh->full[stage]);
+                const uint32_t sa = smem_u32(s_a + (size_t)stage * WS_A_BYTES);
+                mbar_expect_tx(bar, WS_A_BYTES);
+                for (int kw = 0; kw < 3; kw++)
+                    tma_load_4d(sa + kw * (WS_BOX_ROWS * 64), &mapA, bar, 0, tw * WS_TW + kw - 1, th * WS_TH - 1, b);
+                if (++stage == p.stages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = mbar_wait(smem_u32(&sh->w_full), 0, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
+            tc_fence_after();
+            int stage = 0; uint32_t phase = 0;
+            int local = 0;
+            const uint64_t dw = smem_desc<KC>(smem_u32(s_w));
+            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, local++) {
+                const int a = local & 1;
+                const uint32_t aphase = (uint32_t)(local >> 1) & 1;
+                ok = mbar_wait(smem_u32(&sh->acc_empty[a]), aphase ^ 1, abort_flag, p.err, FFCU_ERR_TMEM_TIMEOUT);
+                if (!ok) break;
+                ok = mbar_wait(smem_u32(&sh->full[stage]), phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
+                const uint64_t da0 = smem_desc<KC>(smem_u32(s_a + (size_t)stage * WS_A_BYTES));
+#pragma unroll
+                for (int kw = 0; kw < 3; kw++)
+#pragma unroll
+                    for (int kh = 0; kh < 3; kh++) {
+                        // box kw, image rows kh .. kh+15: start = kw * 9216 + kh * 512 bytes (>> 4)
+                        const uint64_t da = da0 + (uint64_t)((kw * WS_BOX_ROWS * 64 + kh * WS_TW * 64) >> 4);
+                        const uint64_t db = dw + (uint64_t)(((kh * 3 + kw) * W_TAP_BYTES) >> 4);
+#pragma unroll
+                        for (int k = 0; k < 2; k++)
+                            umma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, (kw | kh | k) ? 1u : 0u);
+                    }
+                umma_commit(smem_u32(&sh->empty[stage]));
+                umma_commit(smem_u32(&sh->acc_full[a]));
+                if (++stage == p.stages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else {
+        tc_epilogue_role<BN, CONTRACT, false>(p, tab, sh, tmem_base, abort_flag, warp, lane);
     }
-    __syncthreads();
-    if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
-    }
+    tc_teardown(abort_flag, tmem_base, TMEM_COLS, warp);
 }
 
 // ---------------------------------------------------------------------------
@@ -436,6 +579,9 @@ struct TcPlan {
     int n_sm;
     TcGeom geoms[8];
     int n_geoms;
+    bool ws;                 // weight-stationary kernel (64-channel 3x3 stride-1 layers)
+    CUtensorMap mapA_ws;     // box {64, 8, 18, 1}
+    int ws_stages, ws_smem_bytes;
 };
 
 // Output-tile shape {TW, TH, TB} with TW*TH*TB = 128 that wastes the fewest rows for this
@@ -509,6 +655,26 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
                      p->KC == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { ffcu_set_error("cuTensorMapEncodeTiled(B) failed: %d", (int)r); delete p; return nullptr; }
+    // weight-stationary variant
+    p->ws = false;
+    const char* ws_env = getenv("FF_TC_WS");
+    if (L.kind == FFCU_CONV && Cp == 64 && L.Kh == 3 && L.Kw == 3 && L.stride == 1 && L.pad == 1 &&
+        (L.Cout == 64 || L.Cout == 128) && p->BN == L.Cout && L.W % WS_TW == 0 && L.H >= WS_TH &&
+        !(ws_env && ws_env[0] == '0')) {
+        cuuint64_t adims[4] = {64, (cuuint64_t)L.W, (cuuint64_t)L.H, (cuuint64_t)max_batch};
+        cuuint64_t astr[3] = {64, (cuuint64_t)64 * L.W, (cuuint64_t)64 * L.W * L.H};
+        cuuint32_t abox[4] = {64, WS_TW, WS_TH + 2, 1};
+        cuuint32_t aes[4] = {1, 1, 1, 1};
+        r = enc(&p->mapA_ws, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d_in, adims, astr, abox, aes,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r == CUDA_SUCCESS) {
+            const int wbytes = 9 * p->BN * 64;
+            int st = (232448 - wbytes - fixed) / WS_A_BYTES;
+            if (st > TC_MAX_STAGES) st = TC_MAX_STAGES;
+            if (st >= 2) { p->ws = true; p->ws_stages = st; p->ws_smem_bytes = wbytes + st * WS_A_BYTES + fixed; }
+        }
+    }
     return p;
 }
 
@@ -536,6 +702,29 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
     TcPlan* p = const_cast<TcPlan*>(cp);
     if (batch < 1 || batch > p->max_batch) { ffcu_set_error("tc launch: batch out of range"); return -1; }
     const ffcu_layer& d = p->d;
+    if (p->ws) {
+        TcParams prm;
+        prm.t = t; prm.res = res; prm.acc_out = acc_out; prm.out = out; prm.err = d_err;
+        prm.out2 = (out_bn2 && t.bn_in) ? out_bn2 : nullptr;
+        prm.batch = batch; prm.Ho = d.Ho; prm.Wo = d.Wo; prm.Cout = d.Cout;
+        prm.taps = 9; prm.Kw = 3; prm.Cp = 64; prm.cin_blocks = 1; prm.stride = 1; prm.pad = 1;
+        prm.TW = WS_TW; prm.TH = WS_TH; prm.TB = 1;
+        prm.tiles_w = d.Wo / WS_TW; prm.tiles_h = (d.Ho + WS_TH - 1) / WS_TH; prm.tiles_b = batch; prm.tiles_n = 1;
+        prm.total_tiles = prm.tiles_w * prm.tiles_h * batch;
+        prm.stages = p->ws_stages;
+        int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
+#define WS_LAUNCH(BNV, CONTRACT)                                                                            \
+        do {                                                                                                \
+            auto kern = conv_ws_kernel<BNV, CONTRACT>;                                                      \
+            FFCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->ws_smem_bytes)); \
+            kern<<<grid, TC_THREADS, p->ws_smem_bytes, s>>>(p->mapA_ws, p->mapB, prm);                      \
+        } while (0)
+        if (p->BN == 64) { if (mode) WS_LAUNCH(64, true); else WS_LAUNCH(64, false); }
+        else             { if (mode) WS_LAUNCH(128, true); else WS_LAUNCH(128, false); }
+#undef WS_LAUNCH
+        FFCU_CHECK(cudaGetLastError());
+        return 0;
+    }
     int TW, TH, TB;
     pick_geometry(d.Wo, d.Ho, batch, &TW, &TH, &TB);
     TcGeom* g = nullptr;

@@ -76,6 +76,7 @@ LAYER_CASES = [
     # name, B, H, Cin, Cout, k, stride, slope, res
     ("s1_64_64_56_prelu", 2, 56, 64, 64, 3, 1, True, False),
     ("s1_64_64_112_oddB", 1, 112, 64, 64, 3, 1, True, False),
+    ("s1_64_64_56_add", 3, 56, 64, 64, 3, 1, False, True),
     ("s1_64_128_56_prelu", 3, 56, 64, 128, 3, 1, True, False),
     ("s1_128_128_28_add", 3, 28, 128, 128, 3, 1, False, True),
     ("s1_128_256_28_prelu", 2, 28, 128, 256, 3, 1, True, False),
@@ -110,7 +111,7 @@ def test_single_layer_vs_oracle(built_lib, case, impl):
         assert not msg, msg
 
 
-@pytest.mark.parametrize("case", [LAYER_CASES[0], LAYER_CASES[3], LAYER_CASES[5], LAYER_CASES[7], LAYER_CASES[13]],
+@pytest.mark.parametrize("case", [LAYER_CASES[0], LAYER_CASES[2], LAYER_CASES[4], LAYER_CASES[6], LAYER_CASES[8], LAYER_CASES[14]],
                          ids=lambda c: c[0])
 @pytest.mark.parametrize("impl", ["tc", "simt"])
 def test_fused_bn_second_output(built_lib, case, impl):
@@ -152,6 +153,21 @@ def test_unfused_plan_agrees(built_lib, model_root, ffw4, oracle, monkeypatch):
     with ff.FastFace(ffw4, cwd=model_root, max_batch=3) as e:
         assert e.launches_per_forward == 80 and n_fused == 54
         assert np.array_equal(e.embed_batch(faces), want)
+
+
+@pytest.mark.parametrize("case", LAYER_CASES[:4], ids=lambda c: c[0])
+def test_64ch_layers_on_the_per_tap_kernel(built_lib, case, monkeypatch):
+    """FF_TC_WS=0 routes the 64-input-channel layers through the generic per-tap kernel
+    instead of the weight-stationary one; both must give the same bytes."""
+    monkeypatch.setenv("FF_TC_WS", "0")
+    name, B, H, Cin, Cout, k, stride, sl, rs = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
+    acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
+                            slope=L["slope"], res=L["res"], res_scale=L["rs"], impl="tc")
+    acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
+                               L["res"], L["rs"], ffo.CONTRACT)
+    assert np.array_equal(acc, acc_o) and np.array_equal(out, out_o)
 
 
 def test_stem_conv_simt_vs_oracle(built_lib):
