@@ -198,7 +198,8 @@ __device__ __forceinline__ void tc_load_tables(float* tab, const TcParams& p)
 // (:253-318) as a second output.
 template <bool CONTRACT, bool OUT_F32>
 __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float* tab, const int (&v)[32],
-                                                  int cb, size_t o, bool has_res, bool has_slope, bool has_bn2)
+                                                  const int (&rw)[8], int cb, size_t o, bool has_res,
+                                                  bool has_slope, bool has_bn2)
 {
     if (p.acc_out) {
         int4* dst = (int4*)(p.acc_out + o);
@@ -220,13 +221,6 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
         }
         return;
     }
-    int rw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (has_res) {
-        const int4* rp = (const int4*)(p.res + o);
-        int4 r0 = rp[0], r1 = rp[1];
-        rw[0] = r0.x; rw[1] = r0.y; rw[2] = r0.z; rw[3] = r0.w;
-        rw[4] = r1.x; rw[5] = r1.y; rw[6] = r1.z; rw[7] = r1.w;
-    }
     int ow_[8], ow2_[8];
 #pragma unroll
     for (int g = 0; g < 8; g++) {
@@ -240,17 +234,19 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
         float f1 = ffcu_conv_fp<CONTRACT>(v[4 * g + 1], ws.y, bi.y, has_res, (int)(int8_t)((r >> 8) & 0xff), rs.y, has_slope, sl.y);
         float f2 = ffcu_conv_fp<CONTRACT>(v[4 * g + 2], ws.z, bi.z, has_res, (int)(int8_t)((r >> 16) & 0xff), rs.z, has_slope, sl.z);
         float f3 = ffcu_conv_fp<CONTRACT>(v[4 * g + 3], ws.w, bi.w, has_res, (int)(int8_t)((r >> 24) & 0xff), rs.w, has_slope, sl.w);
-        int q0 = ffcu_requant(f0, iv.x), q1 = ffcu_requant(f1, iv.y);
-        int q2 = ffcu_requant(f2, iv.z), q3 = ffcu_requant(f3, iv.w);
-        ow_[g] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
+        int q0 = ffcu_requant_nosat(f0, iv.x), q1 = ffcu_requant_nosat(f1, iv.y);
+        int q2 = ffcu_requant_nosat(f2, iv.z), q3 = ffcu_requant_nosat(f3, iv.w);
+        ow_[g] = ffcu_pack4(q0, q1, q2, q3);
         if (has_bn2) {
+            q0 = max(-128, min(127, q0)); q1 = max(-128, min(127, q1));
+            q2 = max(-128, min(127, q2)); q3 = max(-128, min(127, q3));
             const float4 bi_ = *(const float4*)&tab[5 * TC_MAX_COUT + cb + 4 * g];
             const float4 bs_ = *(const float4*)&tab[6 * TC_MAX_COUT + cb + 4 * g];
             const float4 bo_ = *(const float4*)&tab[7 * TC_MAX_COUT + cb + 4 * g];
             const float4 bv_ = *(const float4*)&tab[8 * TC_MAX_COUT + cb + 4 * g];
-            int b0 = ffcu_bn_q(q0, bi_.x, bs_.x, bo_.x, bv_.x), b1 = ffcu_bn_q(q1, bi_.y, bs_.y, bo_.y, bv_.y);
-            int b2 = ffcu_bn_q(q2, bi_.z, bs_.z, bo_.z, bv_.z), b3 = ffcu_bn_q(q3, bi_.w, bs_.w, bo_.w, bv_.w);
-            ow2_[g] = (b0 & 0xff) | ((b1 & 0xff) << 8) | ((b2 & 0xff) << 16) | ((b3 & 0xff) << 24);
+            int b0 = ffcu_bn_q_nosat(q0, bi_.x, bs_.x, bo_.x, bv_.x), b1 = ffcu_bn_q_nosat(q1, bi_.y, bs_.y, bo_.y, bv_.y);
+            int b2 = ffcu_bn_q_nosat(q2, bi_.z, bs_.z, bo_.z, bv_.z), b3 = ffcu_bn_q_nosat(q3, bi_.w, bs_.w, bo_.w, bv_.w);
+            ow2_[g] = ffcu_pack4(b0, b1, b2, b3);
         }
     }
     int4* dst = (int4*)((int8_t*)p.out + o);
@@ -294,6 +290,16 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
         const int n0 = tn * BN;
         const int a = local & 1;
         const uint32_t aphase = (uint32_t)(local >> 1) & 1;
+        // the residual operand does not depend on the accumulator: fetch the first chunk's
+        // 32 bytes before waiting for the MMAs, the next chunk's while computing this one
+        int rw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const size_t o0 = pix * p.Cout + n0 + half * PER * 32;
+        if (has_res && valid) {
+            const int4* rp = (const int4*)(p.res + o0);
+            int4 r0 = rp[0], r1 = rp[1];
+            rw[0] = r0.x; rw[1] = r0.y; rw[2] = r0.z; rw[3] = r0.w;
+            rw[4] = r1.x; rw[5] = r1.y; rw[6] = r1.z; rw[7] = r1.w;
+        }
         ok = mbar_wait(smem_u32(&sh->acc_full[a]), aphase, abort_flag, p.err, FFCU_ERR_EPI_TIMEOUT);
         if (!ok) break;
         tc_fence_after();
@@ -304,8 +310,17 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
             int v[32];
             tmem_ld32(taddr + (uint32_t)(j * 32), v);
             if (!valid) continue;
+            int rn[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (has_res && jj + 1 < PER) {
+                const int4* rp = (const int4*)(p.res + o0 + (size_t)(jj + 1) * 32);
+                int4 r0 = rp[0], r1 = rp[1];
+                rn[0] = r0.x; rn[1] = r0.y; rn[2] = r0.z; rn[3] = r0.w;
+                rn[4] = r1.x; rn[5] = r1.y; rn[6] = r1.z; rn[7] = r1.w;
+            }
             const int cb = n0 + j * 32;
-            tc_epilogue_chunk<CONTRACT, OUT_F32>(p, tab, v, cb, pix * p.Cout + cb, has_res, has_slope, has_bn2);
+            tc_epilogue_chunk<CONTRACT, OUT_F32>(p, tab, v, rw, cb, pix * p.Cout + cb, has_res, has_slope, has_bn2);
+#pragma unroll
+            for (int g = 0; g < 8; g++) rw[g] = rn[g];
         }
         // this warp's TMEM reads are complete (tcgen05.wait::ld inside tmem_ld32)
         tc_fence_before();

@@ -37,11 +37,18 @@ struct ffcu_ctx {
     int n_bufs = 0;
     size_t bytes_per_face = 0;
     int8_t* bufs[FFCU_MAX_BUFS] = {};
-    float* d_in = nullptr;       // [max_batch][112][112][3] f32
-    float* d_out = nullptr;      // [max_batch][512] f32
+    // Two input / output slots: the H2D copy of step k+1 and the D2H copy of step k-1
+    // overlap the kernels of step k (copy-in, compute and copy-out streams).
+    float* in_slot[2] = {};      // [max_batch][112][112][3] f32
+    float* out_slot[2] = {};     // [max_batch][512] f32
+    float* d_in = nullptr;       // slot the next launch_forward reads
+    float* d_out = nullptr;      // slot the next launch_forward writes
+    cudaEvent_t ev_in_ready[2] = {}, ev_compute_done[2] = {}, ev_out_copied[2] = {};
+    unsigned long long seq = 0;
     int* d_err = nullptr;        // device error word
     int* h_err = nullptr;        // pinned mirror
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;       // compute
+    cudaStream_t s_in = nullptr, s_out = nullptr;
     std::vector<DevLayer> layers;
     int mode = 1;
     int force_simt = 0;          // FF_CONV_IMPL=simt: every conv on the CUDA-core kernel
@@ -82,8 +89,16 @@ extern "C" ffcu_ctx* ffcu_create(int device, int max_batch, int n_bufs, size_t b
     // 1 KiB of slack after each tensor: TMA boxes of partial tiles stay inside the allocation
     size_t act = (size_t)max_batch * bytes_per_face + 1024;
     for (int i = 0; i < n_bufs && ok; i++) ok = cudaMalloc(&c->bufs[i], act) == cudaSuccess;
-    ok = ok && cudaMalloc(&c->d_in, (size_t)max_batch * 37632 * sizeof(float)) == cudaSuccess;
-    ok = ok && cudaMalloc(&c->d_out, (size_t)max_batch * 512 * sizeof(float)) == cudaSuccess;
+    for (int k = 0; k < 2; k++) {
+        ok = ok && cudaMalloc(&c->in_slot[k], (size_t)max_batch * 37632 * sizeof(float)) == cudaSuccess;
+        ok = ok && cudaMalloc(&c->out_slot[k], (size_t)max_batch * 512 * sizeof(float)) == cudaSuccess;
+        ok = ok && cudaEventCreateWithFlags(&c->ev_in_ready[k], cudaEventDisableTiming) == cudaSuccess;
+        ok = ok && cudaEventCreateWithFlags(&c->ev_compute_done[k], cudaEventDisableTiming) == cudaSuccess;
+        ok = ok && cudaEventCreateWithFlags(&c->ev_out_copied[k], cudaEventDisableTiming) == cudaSuccess;
+    }
+    c->d_in = c->in_slot[0]; c->d_out = c->out_slot[0];
+    ok = ok && cudaStreamCreateWithFlags(&c->s_in, cudaStreamNonBlocking) == cudaSuccess;
+    ok = ok && cudaStreamCreateWithFlags(&c->s_out, cudaStreamNonBlocking) == cudaSuccess;
     ok = ok && cudaMalloc(&c->d_err, sizeof(int)) == cudaSuccess;
     ok = ok && cudaHostAlloc(&c->h_err, sizeof(int), cudaHostAllocDefault) == cudaSuccess;
     ok = ok && cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess;
@@ -103,15 +118,25 @@ extern "C" void ffcu_destroy(ffcu_ctx* c)
     if (!c) return;
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
+    if (c->s_in) cudaStreamSynchronize(c->s_in);
+    if (c->s_out) cudaStreamSynchronize(c->s_out);
     for (auto& L : c->layers) {
         cudaFree(L.w);
         for (float* t : L.tab) cudaFree(t);
         ffcu_tc_free(L.tc);
     }
     for (int i = 0; i < FFCU_MAX_BUFS; i++) cudaFree(c->bufs[i]);
-    cudaFree(c->d_in); cudaFree(c->d_out); cudaFree(c->d_err);
+    for (int k = 0; k < 2; k++) {
+        cudaFree(c->in_slot[k]); cudaFree(c->out_slot[k]);
+        if (c->ev_in_ready[k]) cudaEventDestroy(c->ev_in_ready[k]);
+        if (c->ev_compute_done[k]) cudaEventDestroy(c->ev_compute_done[k]);
+        if (c->ev_out_copied[k]) cudaEventDestroy(c->ev_out_copied[k]);
+    }
+    cudaFree(c->d_err);
     if (c->h_err) cudaFreeHost(c->h_err);
     if (c->stream) cudaStreamDestroy(c->stream);
+    if (c->s_in) cudaStreamDestroy(c->s_in);
+    if (c->s_out) cudaStreamDestroy(c->s_out);
     delete c;
 }
 
@@ -237,10 +262,24 @@ extern "C" int ffcu_submit(ffcu_ctx* c, const float* host_in, int n, float* host
         return -1;
     }
     FFCU_CHECK(cudaSetDevice(c->device));
-    FFCU_CHECK(cudaMemcpyAsync(c->d_in, host_in, (size_t)n * 37632 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    const int slot = (int)(c->seq & 1);
+    const bool reused = c->seq >= 2;
+    // copy-in stream: the slot is free once the forward that last read it has finished
+    if (reused) FFCU_CHECK(cudaStreamWaitEvent(c->s_in, c->ev_compute_done[slot], 0));
+    FFCU_CHECK(cudaMemcpyAsync(c->in_slot[slot], host_in, (size_t)n * 37632 * sizeof(float), cudaMemcpyHostToDevice, c->s_in));
+    FFCU_CHECK(cudaEventRecord(c->ev_in_ready[slot], c->s_in));
+    // compute stream: needs the input, and the output slot drained by the copy-out of two steps ago
+    FFCU_CHECK(cudaStreamWaitEvent(c->stream, c->ev_in_ready[slot], 0));
+    if (reused) FFCU_CHECK(cudaStreamWaitEvent(c->stream, c->ev_out_copied[slot], 0));
+    c->d_in = c->in_slot[slot]; c->d_out = c->out_slot[slot];
     int rc = launch_forward(c, n);
     if (rc != 0) return rc;
-    FFCU_CHECK(cudaMemcpyAsync(host_out, c->d_out, (size_t)n * 512 * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+    FFCU_CHECK(cudaEventRecord(c->ev_compute_done[slot], c->stream));
+    // copy-out stream
+    FFCU_CHECK(cudaStreamWaitEvent(c->s_out, c->ev_compute_done[slot], 0));
+    FFCU_CHECK(cudaMemcpyAsync(host_out, c->out_slot[slot], (size_t)n * 512 * sizeof(float), cudaMemcpyDeviceToHost, c->s_out));
+    FFCU_CHECK(cudaEventRecord(c->ev_out_copied[slot], c->s_out));
+    c->seq++;
     return 0;
 }
 
@@ -248,8 +287,10 @@ extern "C" int ffcu_wait(ffcu_ctx* c)
 {
     if (!c) return -1;
     FFCU_CHECK(cudaSetDevice(c->device));
+    FFCU_CHECK(cudaStreamSynchronize(c->s_in));
     FFCU_CHECK(cudaMemcpyAsync(c->h_err, c->d_err, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
     FFCU_CHECK(cudaStreamSynchronize(c->stream));
+    FFCU_CHECK(cudaStreamSynchronize(c->s_out));
     if (*c->h_err != 0) {
         ffcu_set_error("device reported error word %d (a bounded wait inside a kernel ran out)", *c->h_err);
         int e = *c->h_err;

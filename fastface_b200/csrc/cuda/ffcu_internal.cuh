@@ -63,6 +63,34 @@ __device__ __forceinline__ int ffcu_requant(float t, float inv)
     return max(-128, min(127, i));
 }
 
+// Same rounding as ffcu_requant, but the clamp is left to the caller (ffcu_pack4 saturates).
+__device__ __forceinline__ int ffcu_requant_nosat(float t, float inv)
+{
+    float q = __fmul_rn(t, inv);
+    float half = __int_as_float(0x3f000000 | (__float_as_int(q) & 0x80000000));
+    float r = __fadd_rn(q, half);
+    int i = __float2int_rz(r);
+    if (!(fabsf(r) < 2147483648.0f)) i = INT_MIN;
+    return i;
+}
+
+// Four int32 -> four int8 with saturation to [-128, 127], packed little-endian (a = byte 0).
+__device__ __forceinline__ int ffcu_pack4(int a, int b, int c, int d)
+{
+    int hi, out;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(d), "r"(c));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(b), "r"(a), "r"(hi));
+    return out;
+}
+
+// BN of an already-clamped int8 value, unclamped result (see ffcu_bn_q).
+__device__ __forceinline__ int ffcu_bn_q_nosat(int a, float in_scale, float bn_scale, float bn_offset, float inv)
+{
+    float t = __fmul_rn(__int2float_rn(a), in_scale);
+    t = __fmaf_rn(t, bn_scale, bn_offset);
+    return ffcu_requant_nosat(t, inv);
+}
+
 // Conv epilogue value before requantisation (reference kernels/int8_epilogue.c:53-76).
 // CONTRACT selects the evaluation gcc produces for that source under the reference
 // Makefile's flags: the "* w_scale + bias" and "res * res_scale + t" pairs become fmas.

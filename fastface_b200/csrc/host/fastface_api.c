@@ -162,20 +162,29 @@ static void* dev_job_run(void* arg)
     return NULL;
 }
 
+int fastface_shard_plan(int n, int n_devices, int* starts, int* counts)
+{
+    if (n < 1 || n_devices < 1 || !starts || !counts) return 0;
+    int per = (n + n_devices - 1) / n_devices, used = 0, start = 0;
+    for (int d = 0; d < n_devices && start < n; d++) {
+        int cnt = n - start < per ? n - start : per;
+        starts[used] = start; counts[used] = cnt;
+        start += cnt; used++;
+    }
+    return used;
+}
+
 int fastface_embed_batch(FastFace* ff, const float* input_hwc, int n, float* out_emb)
 {
     if (!ff || !input_hwc || !out_emb || n < 1) return -1;
     g_api_err[0] = 0;
     dev_job jobs[FF_MAX_DEVICES];
     pthread_t th[FF_MAX_DEVICES];
-    int used = 0, start = 0;
-    int per = (n + ff->n_dev - 1) / ff->n_dev;
-    for (int d = 0; d < ff->n_dev && start < n; d++) {
-        int cnt = n - start < per ? n - start : per;
-        jobs[used] = (dev_job){ ff->dev[d], input_hwc + (size_t)start * FASTFACE_INPUT_N,
-                                out_emb + (size_t)start * FASTFACE_OUTPUT_N, cnt, ff->max_batch, 0 };
-        start += cnt; used++;
-    }
+    int starts[FF_MAX_DEVICES], counts[FF_MAX_DEVICES];
+    int used = fastface_shard_plan(n, ff->n_dev, starts, counts);
+    for (int d = 0; d < used; d++)
+        jobs[d] = (dev_job){ ff->dev[d], input_hwc + (size_t)starts[d] * FASTFACE_INPUT_N,
+                             out_emb + (size_t)starts[d] * FASTFACE_OUTPUT_N, counts[d], ff->max_batch, 0 };
     if (used == 1) {
         dev_job_run(&jobs[0]);
     } else {

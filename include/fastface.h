@@ -62,6 +62,11 @@ FastFace* fastface_create_ex(const char* ffw4_path, const int* device_ids, int n
  * and into steps of at most max_batch per device. */
 int fastface_embed_batch(FastFace* ff, const float* input_hwc, int n, float* out_emb);
 
+/* How fastface_embed_batch splits n faces over n_devices: contiguous chunks of
+ * ceil(n / n_devices) faces (the last may be shorter; devices beyond the data get none).
+ * Fills starts[] / counts[] and returns the number of devices used.  Pure host arithmetic. */
+int fastface_shard_plan(int n, int n_devices, int* starts, int* counts);
+
 /* Cosine similarity of two 512-d embeddings, float64 accumulation, 0 when a
  * norm is 0 (reference go/fastface/fastface.go:157-168). */
 float fastface_cos_sim(const float* a, const float* b);
