@@ -1,0 +1,187 @@
+// conv_tc_pair.cu -- CTA-pair (cta_group::2) implicit-GEMM kernel for >= 128 input channels.
+#include "conv_tc_common.cuh"
+
+// ---------------------------------------------------------------------------
+// CTA-pair kernel (cta_group::2) for the layers with >= 128 input channels.
+// Two CTAs on one TPC compute a 256-pixel x BN tile: each loads its own 128 pixel rows
+// of A and HALF of the weight tile (BN/2 rows), and one tcgen05.mma.cta_group::2 issued
+// by the leader CTA reads both halves from both shared memories.  Per CTA the bytes
+// fetched from L2 per MAC drop by a third (BN = 256: 16 KB + 16 KB instead of
+// 16 KB + 32 KB per 128 x 256 x 128 MACs), which is what bounds these layers.
+//   * every TMA load is issued by the CTA that owns the destination shared memory and
+//     counts its bytes on the LEADER's full barrier (no multicast);
+//   * the leader's commit arrives on the empty / accumulator-full barriers of both CTAs;
+//   * both CTAs' epilogue warps arrive on the leader's accumulator-empty barrier;
+//   * the pair synchronises (cluster barrier) after set-up and before teardown so neither
+//     CTA's shared memory or TMEM goes away while the other may still touch it.
+// ---------------------------------------------------------------------------
+template <int BN, bool CONTRACT, bool OUT_F32, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int KC = 128;
+    constexpr int A_BYTES = TC_TILE_M * KC;
+    constexpr int B_BYTES = (BN / 2) * KC;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+    constexpr uint32_t IDESC = idesc_i8(BN, 256);
+
+    float* tab = (float*)(smem + (size_t)p.stages * STAGE_BYTES);
+    TcShared* sh = (TcShared*)(tab + TC_NTAB * TC_MAX_COUT);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();            // 0 = leader
+    const int kblocks = p.taps * p.cin_blocks;
+    const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int m_tiles = p.tiles_w * p.tiles_h * p.tiles_b;
+    const int total = p.tiles_n * ((m_tiles + 1) >> 1);  // pair tiles
+
+    tc_load_tables(tab, p);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; s++) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&sh->acc_full[a]), 1); mbar_init(smem_u32(&sh->acc_empty[a]), 2 * TC_EPI_WARPS); }
+        mbar_init(smem_u32(&sh->w_full), 1);
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&sh->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                  // peer's barriers are initialised
+    tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+    volatile int* abort_flag = &sh->abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair_id; tile < total && ok; tile += n_pairs) {
+                const int tn = tile % p.tiles_n;
+                int m = (tile / p.tiles_n) * 2 + (int)rank;
+                const int tw = m % p.tiles_w; m /= p.tiles_w;
+                const int th = m % p.tiles_h;
+                const int tb = m / p.tiles_h;                   // may be past the batch: TMA zero-fills
+                const int x0 = tw * p.TW * p.stride - p.pad;
+                const int y0 = th * p.TH * p.stride - p.pad;
+                const int b0 = tb * p.TB;
+                const int n0 = tn * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < kblocks; kb++) {
+                    ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, p.err, FFCU_ERR_EMPTY_TIMEOUT);
+                    if (!ok) break;
+                    const int tap = kb / p.cin_blocks;
+                    const int c0 = (kb - tap * p.cin_blocks) * KC;
+                    const int kh = tap / p.Kw, kw = tap - kh * p.Kw;
+                    const uint32_t bar_local = smem_u32(&sh->full[stage]);
+                    const uint32_t bar_leader = map_to_cta(bar_local, 0);
+                    const uint32_t sa = smem_u32(smem + (size_t)stage * STAGE_BYTES);
+                    if (rank == 0) mbar_expect_tx(bar_local, 2 * STAGE_BYTES);
+                    tma2_load_4d(sa, &mapA, bar_leader, c0, x0 + kw, y0 + kh, b0);
+                    tma2_load_2d(sa + A_BYTES, &mapB, bar_leader, tap * p.Cp + c0, n0);
+                    if (++stage == p.stages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            int stage = 0; uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int tile = pair_id; tile < total && ok; tile += n_pairs, local++) {
+                const int a = local & 1;
+                const uint32_t aphase = (uint32_t)(local >> 1) & 1;
+                ok = mbar_wait_cluster(smem_u32(&sh->acc_empty[a]), aphase ^ 1, abort_flag, p.err, FFCU_ERR_TMEM_TIMEOUT);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
+                for (int kb = 0; kb < kblocks; kb++) {
+                    ok = mbar_wait_cluster(smem_u32(&sh->full[stage]), phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + (size_t)stage * STAGE_BYTES);
+                    const uint64_t da = smem_desc<KC>(sa);
+                    const uint64_t db = smem_desc<KC>(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < KC / 32; k++)
+                        umma2_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, (kb | k) ? 1u : 0u);
+                    umma2_commit_both(smem_u32(&sh->empty[stage]));
+                    if (++stage == p.stages) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma2_commit_both(smem_u32(&sh->acc_full[a]));
+            }
+        }
+    } else {
+        const uint32_t leader_acc_empty = map_to_cta(smem_u32(&sh->acc_empty[0]), 0);
+        tc_epilogue_role<BN, CONTRACT, OUT_F32, EPI>(p, tab, sh, tmem_base, abort_flag, warp, lane,
+                                                pair_id, n_pairs, total, 2, (int)rank, leader_acc_empty);
+    }
+
+    // ---- teardown: neither CTA may leave while its partner can still read its smem / TMEM ----
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+    }
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+
+template <int BN, bool CONTRACT, bool F32, int EPI>
+static int launch_p(int grid, int smem, cudaStream_t s, const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm)
+{
+    auto kern = conv_tc2_kernel<BN, CONTRACT, F32, EPI>;
+    static int smem_set[64] = {};      // per device: the attribute belongs to the device's copy of the function
+    int dev = 0;
+    FFCU_CHECK(cudaGetDevice(&dev));
+    if (smem_set[dev & 63] < smem) {
+        FFCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        smem_set[dev & 63] = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    FFCU_CHECK(cudaLaunchKernelEx(&cfg, kern, mapA, mapB, prm));
+    return 0;
+}
+
+template <int BN>
+static int launch_p_bn(int mode, int epi, bool f32, int grid, int smem, cudaStream_t s,
+                       const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm)
+{
+    if (f32) return mode ? launch_p<BN, true, true, EPI_PLAIN>(grid, smem, s, mapA, mapB, prm)
+                         : launch_p<BN, false, true, EPI_PLAIN>(grid, smem, s, mapA, mapB, prm);
+    if (!mode) return launch_p<BN, false, false, EPI_RUNTIME>(grid, smem, s, mapA, mapB, prm);
+    switch (epi) {
+    case EPI_PLAIN:  return launch_p<BN, true, false, EPI_PLAIN>(grid, smem, s, mapA, mapB, prm);
+    case EPI_SLOPE:  return launch_p<BN, true, false, EPI_SLOPE>(grid, smem, s, mapA, mapB, prm);
+    case EPI_RES_BN: return launch_p<BN, true, false, EPI_RES_BN>(grid, smem, s, mapA, mapB, prm);
+    case EPI_RES:    return launch_p<BN, true, false, EPI_RES>(grid, smem, s, mapA, mapB, prm);
+    default:         return launch_p<BN, true, false, EPI_RUNTIME>(grid, smem, s, mapA, mapB, prm);
+    }
+}
+
+int tc_launch_pair(int bn, int mode, int epi, bool f32, int grid, int smem, cudaStream_t s,
+                   const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm)
+{
+    if (bn == 256) return launch_p_bn<256>(mode, epi, f32, grid, smem, s, mapA, mapB, prm);
+    return launch_p_bn<128>(mode, epi, f32, grid, smem, s, mapA, mapB, prm);
+}

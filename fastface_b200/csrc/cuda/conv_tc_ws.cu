@@ -1,0 +1,142 @@
+// conv_tc_ws.cu -- weight-stationary implicit-GEMM kernel for the 64-input-channel layers.
+#include "conv_tc_common.cuh"
+
+// ---------------------------------------------------------------------------
+// weight-stationary kernel for the 64-input-channel 3x3 stride-1 layers
+// (112x112 and 56x56 maps: 20% of the network's MACs but, tap by tap, its largest
+// shared-memory fill traffic).
+//   * all 9 weight taps ([tap][BN rows][64 B], 36 KB or 72 KB) are loaded once per CTA
+//     and stay in shared memory for every tile the CTA processes;
+//   * output tile = 8 wide x 16 high pixels of one image.  Per tile three boxes
+//     {64 B, 8, 18, 1} are loaded, one per kw, each holding rows y0-1 .. y0+16: an 8-row
+//     swizzle group is one image row of the box, so the three kh taps are the same box
+//     read at group offsets 0, 1, 2 (descriptor start + kh * 512 B).  Activation bytes
+//     fetched per tile drop from 9 x 128 to 3 x 144 rows.
+// ---------------------------------------------------------------------------
+
+template <int BN, bool CONTRACT, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int KC = 64;
+    constexpr int W_TAP_BYTES = BN * KC;
+    constexpr int W_BYTES = 9 * W_TAP_BYTES;
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+    constexpr uint32_t IDESC = idesc_i8(BN);
+
+    uint8_t* s_w = smem;                                        // [9][BN][64]
+    uint8_t* s_a = smem + W_BYTES;                              // [stages][3][144][64]
+    float* tab = (float*)(s_a + (size_t)p.stages * WS_A_BYTES);
+    TcShared* sh = (TcShared*)(tab + TC_NTAB * TC_MAX_COUT);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    tc_load_tables(tab, p);
+    tc_setup(sh, p.stages, TMEM_COLS, warp);
+    const uint32_t tmem_base = sh->tmem_base;
+    volatile int* abort_flag = &sh->abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t wbar = smem_u32(&sh->w_full);
+            mbar_expect_tx(wbar, W_BYTES);
+            for (int tap = 0; tap < 9; tap++)
+                tma_load_2d(smem_u32(s_w + tap * W_TAP_BYTES), &mapB, wbar, tap * p.Cp, 0);
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+                int m = tile;
+                const int tw = m % p.tiles_w; m /= p.tiles_w;
+                const int th = m % p.tiles_h;
+                const int b = m / p.tiles_h;
+                ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, p.err, FFCU_ERR_EMPTY_TIMEOUT);
+                if (!ok) break;
+                const uint32_t bar = smem_u32(&sh->full[stage]);
+                const uint32_t sa = smem_u32(s_a + (size_t)stage * WS_A_BYTES);
+                mbar_expect_tx(bar, WS_A_BYTES);
+                for (int kw = 0; kw < 3; kw++)
+                    tma_load_4d(sa + kw * (WS_BOX_ROWS * 64), &mapA, bar, 0, tw * WS_TW + kw - 1, th * WS_TH - 1, b);
+                if (++stage == p.stages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = mbar_wait(smem_u32(&sh->w_full), 0, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
+            tc_fence_after();
+            int stage = 0; uint32_t phase = 0;
+            int local = 0;
+            const uint64_t dw = smem_desc<KC>(smem_u32(s_w));
+            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, local++) {
+                const int a = local & 1;
+                const uint32_t aphase = (uint32_t)(local >> 1) & 1;
+                ok = mbar_wait(smem_u32(&sh->acc_empty[a]), aphase ^ 1, abort_flag, p.err, FFCU_ERR_TMEM_TIMEOUT);
+                if (!ok) break;
+                ok = mbar_wait(smem_u32(&sh->full[stage]), phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
+                const uint64_t da0 = smem_desc<KC>(smem_u32(s_a + (size_t)stage * WS_A_BYTES));
+#pragma unroll
+                for (int kw = 0; kw < 3; kw++)
+#pragma unroll
+                    for (int kh = 0; kh < 3; kh++) {
+                        // box kw, image rows kh .. kh+15: start = kw * 9216 + kh * 512 bytes (>> 4)
+                        const uint64_t da = da0 + (uint64_t)((kw * WS_BOX_ROWS * 64 + kh * WS_TW * 64) >> 4);
+                        const uint64_t db = dw + (uint64_t)(((kh * 3 + kw) * W_TAP_BYTES) >> 4);
+#pragma unroll
+                        for (int k = 0; k < 2; k++)
+                            umma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, (kw | kh | k) ? 1u : 0u);
+                    }
+                umma_commit(smem_u32(&sh->empty[stage]));
+                umma_commit(smem_u32(&sh->acc_full[a]));
+                if (++stage == p.stages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else {
+        tc_epilogue_role<BN, CONTRACT, false, EPI>(p, tab, sh, tmem_base, abort_flag, warp, lane,
+                                             blockIdx.x, gridDim.x, p.total_tiles, 1, 0, 0u);
+    }
+    tc_teardown(abort_flag, tmem_base, TMEM_COLS, warp);
+}
+
+
+
+template <int BN, bool CONTRACT, int EPI>
+static int launch_w(int grid, int smem, cudaStream_t s, const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm)
+{
+    auto kern = conv_ws_kernel<BN, CONTRACT, EPI>;
+    static int smem_set[64] = {};      // per device: the attribute belongs to the device's copy of the function
+    int dev = 0;
+    FFCU_CHECK(cudaGetDevice(&dev));
+    if (smem_set[dev & 63] < smem) {
+        FFCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        smem_set[dev & 63] = smem;
+    }
+    kern<<<grid, TC_THREADS, smem, s>>>(mapA, mapB, prm);
+    FFCU_CHECK(cudaGetLastError());
+    return 0;
+}
+
+template <int BN>
+static int launch_w_bn(int mode, int epi, int grid, int smem, cudaStream_t s,
+                       const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm)
+{
+    if (!mode) return launch_w<BN, false, EPI_RUNTIME>(grid, smem, s, mapA, mapB, prm);
+    switch (epi) {
+    case EPI_PLAIN:  return launch_w<BN, true, EPI_PLAIN>(grid, smem, s, mapA, mapB, prm);
+    case EPI_SLOPE:  return launch_w<BN, true, EPI_SLOPE>(grid, smem, s, mapA, mapB, prm);
+    case EPI_RES_BN: return launch_w<BN, true, EPI_RES_BN>(grid, smem, s, mapA, mapB, prm);
+    case EPI_RES:    return launch_w<BN, true, EPI_RES>(grid, smem, s, mapA, mapB, prm);
+    default:         return launch_w<BN, true, EPI_RUNTIME>(grid, smem, s, mapA, mapB, prm);
+    }
+}
+
+int tc_launch_ws(int bn, int mode, int epi, int grid, int smem, cudaStream_t s,
+                 const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm)
+{
+    if (bn == 64) return launch_w_bn<64>(mode, epi, grid, smem, s, mapA, mapB, prm);
+    return launch_w_bn<128>(mode, epi, grid, smem, s, mapA, mapB, prm);
+}

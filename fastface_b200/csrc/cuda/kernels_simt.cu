@@ -251,7 +251,7 @@ int ffcu_launch_fc_simt(const int8_t* act, const int8_t* w, const float* w_scale
 // shared memory, weights ([tap][co] words) and the per-channel tables sit there too.
 // ---------------------------------------------------------------------------
 #define STEM_T 16
-template <bool CONTRACT>
+template <bool CONTRACT, bool HAS_SLOPE, bool HAS_BN2>
 __global__ void __launch_bounds__(256) stem_kernel(const float* __restrict__ in, const float* __restrict__ inv3,
                                                    const int8_t* __restrict__ w, EpiTables t,
                                                    int8_t* __restrict__ out, int8_t* __restrict__ out2,
@@ -264,7 +264,7 @@ __global__ void __launch_bounds__(256) stem_kernel(const float* __restrict__ in,
     const int b = blockIdx.z;
     const int x0 = blockIdx.x * STEM_T, y0 = blockIdx.y * STEM_T;
     const float i0 = __ldg(inv3), i1 = __ldg(inv3 + 1), i2 = __ldg(inv3 + 2);
-    const bool has_bn2 = (out2 != nullptr) && (t.bn_in != nullptr);
+    constexpr bool has_bn2 = HAS_BN2;     // compile-time: keeps the per-element code branch-free
     for (int i = threadIdx.x; i < P * P; i += 256) {
         int py = y0 - 1 + i / P, px = x0 - 1 + i % P;
         int v = 0;
@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(256) stem_kernel(const float* __restrict__ in,
         for (int kw = 0; kw < 3; kw++) a[kh * 3 + kw] = s_in[(ty + kh) * P + tx + kw];
     const size_t pix = ((size_t)b * H + (y0 + ty)) * W + (x0 + tx);
     if (q_out) q_out[pix] = a[4];
-    const bool has_slope = t.slope != nullptr;
+    constexpr bool has_slope = HAS_SLOPE;
     int4* dst = (int4*)(out + pix * C);
     int4* dst2 = (int4*)(out2 + pix * C);
 #pragma unroll 1
@@ -342,8 +342,16 @@ int ffcu_launch_stem(const float* in_f32, const float* inv3, const int8_t* w, co
                      int mode, int8_t* out, int8_t* out_bn2, int8_t* q_out, cudaStream_t s)
 {
     dim3 grid(112 / STEM_T, 112 / STEM_T, batch);
-    if (mode) stem_kernel<true><<<grid, 256, 0, s>>>(in_f32, inv3, w, t, out, out_bn2, (int*)q_out);
-    else      stem_kernel<false><<<grid, 256, 0, s>>>(in_f32, inv3, w, t, out, out_bn2, (int*)q_out);
+    const bool sl = t.slope != nullptr, bn = (out_bn2 != nullptr) && (t.bn_in != nullptr);
+#define STEM_GO(C_, S_, B_) stem_kernel<C_, S_, B_><<<grid, 256, 0, s>>>(in_f32, inv3, w, t, out, out_bn2, (int*)q_out)
+    if (mode) {
+        if (sl && bn) STEM_GO(true, true, true); else if (sl) STEM_GO(true, true, false);
+        else if (bn) STEM_GO(true, false, true); else STEM_GO(true, false, false);
+    } else {
+        if (sl && bn) STEM_GO(false, true, true); else if (sl) STEM_GO(false, true, false);
+        else if (bn) STEM_GO(false, false, true); else STEM_GO(false, false, false);
+    }
+#undef STEM_GO
     FFCU_CHECK(cudaGetLastError());
     return 0;
 }

@@ -170,6 +170,21 @@ def test_64ch_layers_on_the_per_tap_kernel(built_lib, case, monkeypatch):
     assert np.array_equal(acc, acc_o) and np.array_equal(out, out_o)
 
 
+@pytest.mark.parametrize("case", [c for c in LAYER_CASES if c[3] >= 128], ids=lambda c: c[0])
+def test_wide_layers_on_the_single_cta_kernel(built_lib, case, monkeypatch):
+    """FF_TC_PAIR=0 routes the >=128-input-channel layers through the one-CTA kernel instead of
+    the CTA-pair (cta_group::2) one; both must give the same bytes."""
+    monkeypatch.setenv("FF_TC_PAIR", "0")
+    name, B, H, Cin, Cout, k, stride, sl, rs = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
+    acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
+                            slope=L["slope"], res=L["res"], res_scale=L["rs"], impl="tc")
+    acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
+                               L["res"], L["rs"], ffo.CONTRACT)
+    assert np.array_equal(acc, acc_o) and np.array_equal(out, out_o)
+
+
 def test_stem_conv_simt_vs_oracle(built_lib):
     """Cin=3 stem (K=27): CUDA-core dp4a kernel."""
     rng = np.random.default_rng(3)
