@@ -32,6 +32,7 @@ struct TcPlan {
     const int8_t* d_in;
     CUtensorMap mapB;
     int n_sm;
+    int group, pair_group;   // K blocks per pipeline stage
     TcGeom geoms[8];
     int n_geoms;
     bool pair;               // CTA-pair kernel (cta_group::2) for >= 128 input channels
@@ -94,21 +95,44 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
     p->BN = L.Cout >= 256 ? 256 : L.Cout;
     const char* bn_env = getenv("FF_TC_BN");
     if (bn_env) { int v = atoi(bn_env); if ((v == 64 || v == 128 || v == 256) && L.Cout % v == 0) p->BN = v; }
-    const int stage_bytes = (TC_TILE_M + p->BN) * p->KC;
     const int fixed = TC_NTAB * TC_MAX_COUT * 4 + (int)sizeof(TcShared) + 1024;
-    int stages = (232448 - fixed) / stage_bytes;
-    if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
+    const int kblocks = L.Kh * L.Kw * (Cp / p->KC);
+    const char* genv = getenv("FF_TC_GROUP");
+    const int gmax = genv ? atoi(genv) : 8;
+    // K blocks per stage.  One barrier hand-shake costs the single-thread producer / issuer
+    // loops about 500 cycles whatever it moves, so a stage should hold >= ~768 cycles of MMA work
+    // (one block = 128 x BN x KC MACs at 8192 MACs/cycle); the group must divide the K loop and
+    // leave at least two stages.
+    const int blk_cycles = 2 * p->BN * p->KC / 128;
+    const int g_target = (768 + blk_cycles - 1) / blk_cycles;
+    auto pick_group = [&](int sub_bytes, int* stages_out) {
+        int best_g = 1;
+        for (int g = 2; g <= gmax && g <= 8; g++) {
+            if (kblocks % g) continue;
+            if ((232448 - fixed) / (g * sub_bytes) < 2) break;
+            best_g = g;
+            if (g >= g_target) break;
+        }
+        int st = (232448 - fixed) / (best_g * sub_bytes);
+        if (st > TC_MAX_STAGES) st = TC_MAX_STAGES;
+        *stages_out = st;
+        return best_g;
+    };
+    const int sub_bytes = (TC_TILE_M + p->BN) * p->KC;
+    int stages = 0;
+    p->group = pick_group(sub_bytes, &stages);
     if (stages < 2) { delete p; return nullptr; }
     p->stages = stages;
-    p->smem_bytes = stages * stage_bytes + fixed;
+    p->smem_bytes = stages * p->group * sub_bytes + fixed;
     cudaDeviceGetAttribute(&p->n_sm, cudaDevAttrMultiProcessorCount, device);
     // weights: [Cout][taps*Cp] K-major
     cuuint64_t Ktot = (cuuint64_t)L.Kh * L.Kw * Cp;
-    cuuint64_t dims[2] = {Ktot, (cuuint64_t)L.Cout};
-    cuuint64_t strides[1] = {Ktot};
-    cuuint32_t box[2] = {(cuuint32_t)p->KC, (cuuint32_t)p->BN};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(&p->mapB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)d_w, dims, strides, box, estr,
+    // 4-D like the activation map so one cp.async.bulk.tensor.4d instruction serves both operands
+    cuuint64_t dims[4] = {Ktot, (cuuint64_t)L.Cout, 1, 1};
+    cuuint64_t strides[3] = {Ktot, Ktot * L.Cout, Ktot * L.Cout};
+    cuuint32_t box[4] = {(cuuint32_t)p->KC, (cuuint32_t)p->BN, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(&p->mapB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d_w, dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE,
                      p->KC == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -117,15 +141,15 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
     p->pair = false;
     const char* pair_env = getenv("FF_TC_PAIR");
     if (p->KC == 128 && (p->BN == 128 || p->BN == 256) && !(pair_env && pair_env[0] == '0')) {
-        cuuint32_t hbox[2] = {128, (cuuint32_t)(p->BN / 2)};
-        r = enc(&p->mapB_half, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)d_w, dims, strides, hbox, estr,
+        cuuint32_t hbox[4] = {128, (cuuint32_t)(p->BN / 2), 1, 1};
+        r = enc(&p->mapB_half, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d_w, dims, strides, hbox, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r == CUDA_SUCCESS) {
             const int sb = (TC_TILE_M + p->BN / 2) * 128;
-            int st = (232448 - fixed) / sb;
-            if (st > TC_MAX_STAGES) st = TC_MAX_STAGES;
-            if (st >= 2) { p->pair = true; p->pair_stages = st; p->pair_smem_bytes = st * sb + fixed; }
+            int st = 0;
+            p->pair_group = pick_group(sb, &st);
+            if (st >= 2) { p->pair = true; p->pair_stages = st; p->pair_smem_bytes = st * p->pair_group * sb + fixed; }
         }
     }
     // weight-stationary variant
@@ -159,6 +183,8 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
     TcPlan* p = const_cast<TcPlan*>(cp);
     if (batch < 1 || batch > p->max_batch) { ffcu_set_error("tc launch: batch out of range"); return -1; }
     const ffcu_layer& d = p->d;
+    static int dbg = -1;
+    if (dbg < 0) { const char* e = getenv("FF_TC_DBG"); dbg = e ? atoi(e) : 0; }
     const bool has_res = res && t.res_scale, has_slope = t.slope != nullptr, has_bn2 = out_bn2 && t.bn_in;
     int epi = EPI_RUNTIME;
     if (p->out_f32 || (!has_res && !has_slope && !has_bn2)) epi = EPI_PLAIN;
@@ -174,7 +200,7 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
         prm.TW = WS_TW; prm.TH = WS_TH; prm.TB = 1;
         prm.tiles_w = d.Wo / WS_TW; prm.tiles_h = (d.Ho + WS_TH - 1) / WS_TH; prm.tiles_b = batch; prm.tiles_n = 1;
         prm.total_tiles = prm.tiles_w * prm.tiles_h * batch;
-        prm.stages = p->ws_stages;
+        prm.stages = p->ws_stages; prm.group = 1; prm.dbg = 0;
         int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
         return tc_launch_ws(p->BN, mode, epi, grid, p->ws_smem_bytes, s, p->mapA_ws, p->mapB, prm);
     }
@@ -200,12 +226,13 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
     prm.tiles_w = (d.Wo + TW - 1) / TW; prm.tiles_h = (d.Ho + TH - 1) / TH; prm.tiles_b = (batch + TB - 1) / TB;
     prm.tiles_n = d.Cout / p->BN;
     prm.total_tiles = prm.tiles_w * prm.tiles_h * prm.tiles_b * prm.tiles_n;
-    prm.stages = p->stages;
+    prm.stages = p->stages; prm.group = p->group; prm.dbg = dbg;
+    { const char* e = getenv("FF_TC_STAGES"); if (e && atoi(e) >= 2 && atoi(e) < prm.stages) prm.stages = atoi(e); }
     if (p->pair) {
         const int m_tiles = prm.tiles_w * prm.tiles_h * prm.tiles_b;
         const int pairs = prm.tiles_n * ((m_tiles + 1) / 2);
         const int max_pairs = p->n_sm / 2;
-        prm.stages = p->pair_stages;
+        prm.stages = p->pair_stages; prm.group = p->pair_group;
         const int pgrid = 2 * (pairs < max_pairs ? pairs : max_pairs);
         return tc_launch_pair(p->BN, mode, epi, p->out_f32, pgrid, p->pair_smem_bytes, s, g->mapA, p->mapB_half, prm);
     }

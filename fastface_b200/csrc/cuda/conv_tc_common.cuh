@@ -29,7 +29,6 @@
 
 #define TC_TILE_M 128
 #define TC_MAX_COUT 512
-#define TC_WAIT_NS 2000000000ull   // 2 s per wait
 
 // ---------------------------------------------------------------------------
 // PTX wrappers
@@ -63,17 +62,25 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity);
 // Bounded wait.  Returns false (and raises the CTA-wide abort flag + the global error
-// word) when the barrier did not flip within TC_WAIT_NS or another role already aborted.
-static __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code)
+// word) when the barrier did not flip within TC_WAIT_CYCLES SM cycles (about 2 s) or another
+// role already aborted.  The clock is only consulted after a burst of failed polls, so a
+// wait that succeeds quickly costs nothing but the polls.
+#define TC_WAIT_CYCLES 4000000000ll
+template <bool CLUSTER>
+__device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code)
 {
-    if (mbar_try(bar, parity)) return true;
-    uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+    for (int i = 0; i < 256; i++)
+        if (CLUSTER ? mbar_try_cluster(bar, parity) : mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+#pragma unroll 1
     for (uint32_t spin = 1;; spin++) {
-        if (mbar_try(bar, parity)) return true;
-        if ((spin & 63u) == 0) {
+        if (CLUSTER ? mbar_try_cluster(bar, parity) : mbar_try(bar, parity)) return true;
+        if ((spin & 255u) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > TC_WAIT_NS) {
+            if (clock64() - t0 > TC_WAIT_CYCLES) {
                 *abort_flag = 1;
                 atomicCAS(err, 0, code);
                 return false;
@@ -81,24 +88,15 @@ static __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, vol
         }
     }
 }
-
 __device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity);
-// Same, for a barrier that CTAs of the pair arrive on remotely (cluster-scope acquire).
-static __device__ __noinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code)
 {
-    if (mbar_try_cluster(bar, parity)) return true;
-    uint64_t t0 = globaltimer_ns();
-    for (uint32_t spin = 1;; spin++) {
-        if (mbar_try_cluster(bar, parity)) return true;
-        if ((spin & 63u) == 0) {
-            if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > TC_WAIT_NS) {
-                *abort_flag = 1;
-                atomicCAS(err, 0, code);
-                return false;
-            }
-        }
-    }
+    return mbar_wait_impl<false>(bar, parity, abort_flag, err, code);
+}
+// Same, for a barrier that CTAs of the pair arrive on remotely (cluster-scope acquire).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code)
+{
+    return mbar_wait_impl<true>(bar, parity, abort_flag, err, code);
 }
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
@@ -233,6 +231,8 @@ struct TcParams {
     int TW, TH, TB;
     int tiles_w, tiles_h, tiles_b, tiles_n, total_tiles;
     int stages;
+    int group;               // K blocks per pipeline stage (one barrier hand-shake per `group` blocks)
+    int dbg;                 // timing experiments only: bit 0 = skip the TMA loads, bit 1 = skip the MMAs
 };
 
 // Epilogue variants.  All but EPI_RUNTIME fix the presence of PReLU / residual / fused BN at
@@ -306,6 +306,10 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
         return;
     }
     int ow_[8], ow2_[8];
+    if (p.dbg & 8) {                                                                       // timing experiment: no math
+#pragma unroll
+        for (int g = 0; g < 8; g++) { ow_[g] = v[4 * g] ^ v[4 * g + 1] ^ v[4 * g + 2] ^ v[4 * g + 3]; ow2_[g] = ow_[g] + 1; }
+    } else
 #pragma unroll
     for (int g = 0; g < 8; g++) {
         const float4 ws = *(const float4*)&tab[0 * TC_MAX_COUT + cb + 4 * g];
@@ -333,6 +337,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
             ow2_[g] = ffcu_pack4(b0, b1, b2, b3);
         }
     }
+    if ((p.dbg & 4) && (ow_[0] ^ ow_[3] ^ ow_[5] ^ ow2_[1]) != 0x12345679) return;   // timing experiment: no stores
     int4* dst = (int4*)((int8_t*)p.out + o);
     dst[0] = make_int4(ow_[0], ow_[1], ow_[2], ow_[3]);
     dst[1] = make_int4(ow_[4], ow_[5], ow_[6], ow_[7]);
@@ -381,7 +386,7 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
         // 32 bytes before waiting for the MMAs, the next chunk's while computing this one
         int rw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         const size_t o0 = pix * p.Cout + n0 + half * PER * 32;
-        if (has_res && valid) {
+        if (has_res && valid && !(p.dbg & 4)) {
             const int4* rp = (const int4*)(p.res + o0);
             int4 r0 = rp[0], r1 = rp[1];
             rw[0] = r0.x; rw[1] = r0.y; rw[2] = r0.z; rw[3] = r0.w;
@@ -395,10 +400,14 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
         for (int jj = 0; jj < PER; jj++) {
             const int j = half * PER + jj;
             int v[32];
+            if (p.dbg & 16) {                       // timing experiment: no TMEM reads
+#pragma unroll
+                for (int i = 0; i < 32; i++) v[i] = i + j;
+            } else
             tmem_ld32(taddr + (uint32_t)(j * 32), v);
             if (!valid) continue;
             int rn[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            if (has_res && jj + 1 < PER) {
+            if (has_res && jj + 1 < PER && !(p.dbg & 4)) {
                 const int4* rp = (const int4*)(p.res + o0 + (size_t)(jj + 1) * 32);
                 int4 r0 = rp[0], r1 = rp[1];
                 rn[0] = r0.x; rn[1] = r0.y; rn[2] = r0.z; rn[3] = r0.w;

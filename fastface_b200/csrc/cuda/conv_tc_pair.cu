@@ -24,11 +24,11 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     constexpr int KC = 128;
     constexpr int A_BYTES = TC_TILE_M * KC;
     constexpr int B_BYTES = (BN / 2) * KC;
-    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int SUB_BYTES = A_BYTES + B_BYTES;          // one K block: [A 128 x 128 | B-half BN/2 x 128]
     constexpr uint32_t TMEM_COLS = 2 * BN;
     constexpr uint32_t IDESC = idesc_i8(BN, 256);
 
-    float* tab = (float*)(smem + (size_t)p.stages * STAGE_BYTES);
+    float* tab = (float*)(smem + (size_t)p.stages * p.group * SUB_BYTES);
     TcShared* sh = (TcShared*)(tab + TC_NTAB * TC_MAX_COUT);
 
     const int warp = threadIdx.x >> 5;
@@ -61,9 +61,23 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     volatile int* abort_flag = &sh->abort_flag;
 
     if (warp == 0) {
-        if (lane == 0) {
+        const int G = p.group;
+        if (lane < 2 * G) {
+            // TMA producer.  A pipeline stage holds G consecutive K blocks; lane 2g fetches the
+            // activation box of block g, lane 2g+1 its weight box, all in ONE instruction (both
+            // tensor maps are 4-D).  One barrier hand-shake per stage: the hand-shake, not the copy,
+            // is what a single-thread loop pays for, so it is amortised over G blocks.  Each lane
+            // carries its own (kh, kw, c0) forward by G blocks per step: no divisions in the loop.
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
+            const int g = lane >> 1;
+            const bool is_a = (lane & 1) == 0;
+            const CUtensorMap* map = is_a ? &mapA : &mapB;
+            const uint32_t smem0 = smem_u32(smem) + (uint32_t)(g * SUB_BYTES) + (is_a ? 0u : (uint32_t)A_BYTES);
+            const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
+            const uint32_t full0_leader = map_to_cta(full0, 0);
+            const int stage_bytes = G * SUB_BYTES;
+            const int n_steps = kblocks / G;
             for (int tile = pair_id; tile < total && ok; tile += n_pairs) {
                 const int tn = tile % p.tiles_n;
                 int m = (tile / p.tiles_n) * 2 + (int)rank;
@@ -72,29 +86,39 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                 const int tb = m / p.tiles_h;                   // may be past the batch: TMA zero-fills
                 const int x0 = tw * p.TW * p.stride - p.pad;
                 const int y0 = th * p.TH * p.stride - p.pad;
-                const int b0 = tb * p.TB;
-                const int n0 = tn * BN + (int)rank * (BN / 2);
-                for (int kb = 0; kb < kblocks; kb++) {
-                    ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, p.err, FFCU_ERR_EMPTY_TIMEOUT);
+                const int c3 = is_a ? tb * p.TB : 0;
+                // this lane's first block: kb = g
+                int c0 = g * KC, kw = 0, kh = 0;
+                while (c0 >= p.Cp) { c0 -= p.Cp; if (++kw == p.Kw) { kw = 0; kh++; } }
+                for (int it = 0; it < n_steps; it++) {
+                    ok = mbar_wait(empty0 + stage * 8, phase ^ 1, abort_flag, p.err, FFCU_ERR_EMPTY_TIMEOUT);
                     if (!ok) break;
-                    const int tap = kb / p.cin_blocks;
-                    const int c0 = (kb - tap * p.cin_blocks) * KC;
-                    const int kh = tap / p.Kw, kw = tap - kh * p.Kw;
-                    const uint32_t bar_local = smem_u32(&sh->full[stage]);
-                    const uint32_t bar_leader = map_to_cta(bar_local, 0);
-                    const uint32_t sa = smem_u32(smem + (size_t)stage * STAGE_BYTES);
-                    if (rank == 0) mbar_expect_tx(bar_local, 2 * STAGE_BYTES);
-                    tma2_load_4d(sa, &mapA, bar_leader, c0, x0 + kw, y0 + kh, b0);
-                    tma2_load_2d(sa + A_BYTES, &mapB, bar_leader, tap * p.Cp + c0, n0);
+                    if (p.dbg & 1) { if (rank == 0 && lane == 0) mbar_arrive(full0 + stage * 8); }
+                    else {
+                        if (rank == 0 && lane == 0) mbar_expect_tx(full0 + stage * 8, 2 * G * SUB_BYTES);
+                        __syncwarp((1u << (2 * G)) - 1u);       // the byte count is armed before any copy can land
+                        const int tapk = (kh * p.Kw + kw) * p.Cp + c0;
+                        tma2_load_4d(smem0 + stage * stage_bytes, map, full0_leader + stage * 8,
+                                    is_a ? c0 : tapk, is_a ? x0 + kw : tn * BN + (int)rank * (BN / 2), is_a ? y0 + kh : 0, c3);
+                    }
+                    c0 += G * KC;
+                    while (c0 >= p.Cp) { c0 -= p.Cp; if (++kw == p.Kw) { kw = 0; kh++; } }
                     if (++stage == p.stages) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
+            // MMA issuer
             int stage = 0; uint32_t phase = 0;
             int local = 0;
             bool ok = true;
+            const int G = p.group;
+            const int n_steps = kblocks / G;
+            const int stage_bytes = G * SUB_BYTES;
+            const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
+            const uint64_t da0 = smem_desc<KC>(smem_u32(smem));
+            const uint64_t db0 = smem_desc<KC>(smem_u32(smem) + A_BYTES);
             for (int tile = pair_id; tile < total && ok; tile += n_pairs, local++) {
                 const int a = local & 1;
                 const uint32_t aphase = (uint32_t)(local >> 1) & 1;
@@ -102,17 +126,18 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
-                for (int kb = 0; kb < kblocks; kb++) {
-                    ok = mbar_wait_cluster(smem_u32(&sh->full[stage]), phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
+                for (int it = 0; it < n_steps; it++) {
+                    ok = mbar_wait_cluster(full0 + stage * 8, phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + (size_t)stage * STAGE_BYTES);
-                    const uint64_t da = smem_desc<KC>(sa);
-                    const uint64_t db = smem_desc<KC>(sa + A_BYTES);
+                    uint64_t soff = (uint64_t)((stage * stage_bytes) >> 4);
+                    if (!(p.dbg & 2))
+                    for (int g = 0; g < G; g++, soff += (uint64_t)(SUB_BYTES >> 4)) {
 #pragma unroll
-                    for (int k = 0; k < KC / 32; k++)
-                        umma2_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, (kb | k) ? 1u : 0u);
-                    umma2_commit_both(smem_u32(&sh->empty[stage]));
+                        for (int k = 0; k < KC / 32; k++)
+                            umma2_i8(d_tmem, da0 + soff + (uint64_t)(2 * k), db0 + soff + (uint64_t)(2 * k), IDESC, (it | g | k) ? 1u : 0u);
+                    }
+                    umma2_commit_both(empty0 + stage * 8);   // frees the stage once these MMAs have read it
                     if (++stage == p.stages) { stage = 0; phase ^= 1; }
                 }
                 if (ok) umma2_commit_both(smem_u32(&sh->acc_full[a]));

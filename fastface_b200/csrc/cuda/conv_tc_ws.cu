@@ -44,7 +44,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             const uint32_t wbar = smem_u32(&sh->w_full);
             mbar_expect_tx(wbar, W_BYTES);
             for (int tap = 0; tap < 9; tap++)
-                tma_load_2d(smem_u32(s_w + tap * W_TAP_BYTES), &mapB, wbar, tap * p.Cp, 0);
+                tma_load_4d(smem_u32(s_w + tap * W_TAP_BYTES), &mapB, wbar, tap * p.Cp, 0, 0, 0);
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {

@@ -109,6 +109,11 @@ int ffcu_layer_info(const ffcu_ctx* c, int k, ffcu_layer* out, int* uses_tc);
 int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mode, int impl,
                    const int8_t* in, const int8_t* res, int32_t* acc_out, int8_t* out, int8_t* out_bn2);
 
+/* Dense INT8 tensor-core throughput (TOP/s, 2 ops per MAC) measured with operands already in
+ * shared memory: M=128, N=bn (64/128/256), all SMs busy, `iters` rounds of four K=32 MMAs.
+ * The practical ceiling the convolution kernels are compared against. */
+int ffcu_i8_mma_peak(int device, int bn, int iters, float* tops, float* ms);
+
 const char* ffcu_last_error(void);
 
 #ifdef __cplusplus
