@@ -230,7 +230,8 @@ def conv_once(x: np.ndarray, w_oihw: np.ndarray, w_scale: np.ndarray, bias: np.n
               inv_out: np.ndarray, stride: int = 1, pad: int = 1, slope: Optional[np.ndarray] = None,
               res: Optional[np.ndarray] = None, res_scale: Optional[np.ndarray] = None,
               mode: int = EPILOGUE_CONTRACT, impl: str = "tc", device: int = 0,
-              bn2: Optional[Tuple[np.ndarray, np.ndarray, np.ndarray, np.ndarray]] = None):
+              bn2: Optional[Tuple[np.ndarray, np.ndarray, np.ndarray, np.ndarray]] = None,
+              want_acc: bool = True):
     """One conv layer through the C-ABI (ffcu_conv_once): x int8 [B,H,W,Cin],
     w int8 [Cout,Cin,Kh,Kw] -> (int32 accumulators, int8 output), both [B,Ho,Wo,Cout]."""
     lib = load_library()
@@ -256,7 +257,7 @@ def conv_once(x: np.ndarray, w_oihw: np.ndarray, w_scale: np.ndarray, bias: np.n
         L.bn2_dst_buf = 3
         L.bn2_in_scale, L.bn2_scale, L.bn2_offset, L.bn2_inv_out = [a.ctypes.data for a in keep2]
         out2 = np.empty((B, Ho, Wo, Cout), np.int8)
-    acc = np.empty((B, Ho, Wo, Cout), np.int32)
+    acc = np.empty((B, Ho, Wo, Cout), np.int32) if want_acc else None
     out = np.empty((B, Ho, Wo, Cout), np.int8)
     r = None if res is None else np.ascontiguousarray(res, dtype=np.int8)
     rc = lib.ffcu_conv_once(device, C.byref(L), B, mode, 0 if impl == "tc" else 1, _ptr(xp), _ptr(r), _ptr(acc), _ptr(out), _ptr(out2))

@@ -273,6 +273,19 @@ __device__ __forceinline__ void tc_load_tables(float* tab, const TcParams& p)
     }
 }
 
+// 32-byte global accesses (sm_100 has 256-bit vector loads / stores): one full sector per
+// thread per instruction instead of two half-sector 16-byte accesses.
+__device__ __forceinline__ void st_global_32B(void* ptr, const int (&w)[8])
+{
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+}
+__device__ __forceinline__ void ld_global_32B(const void* ptr, int (&w)[8])
+{
+    asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "l"(ptr));
+}
+
 // One 32-column chunk of one accumulator row: v[32] int32 -> outputs at element offset o
 // (= pixel * Cout + first channel cb).  Replaces fused_epilogue_int8 for those 32 values
 // (reference kernels/int8_epilogue.c:25-112), optionally followed by the next BN pass
@@ -286,9 +299,11 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
     const bool has_slope = (EPI == EPI_RUNTIME) ? rt_slope : (EPI == EPI_SLOPE);
     const bool has_bn2 = (EPI == EPI_RUNTIME) ? rt_bn2 : (EPI == EPI_RES_BN);
     if (p.acc_out) {
-        int4* dst = (int4*)(p.acc_out + o);
 #pragma unroll
-        for (int g = 0; g < 8; g++) dst[g] = make_int4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+        for (int g = 0; g < 4; g++) {
+            const int w8[8] = {v[8 * g], v[8 * g + 1], v[8 * g + 2], v[8 * g + 3], v[8 * g + 4], v[8 * g + 5], v[8 * g + 6], v[8 * g + 7]};
+            st_global_32B(p.acc_out + o + 8 * g, w8);
+        }
     }
     if (OUT_F32) {
         float4* dst = (float4*)((float*)p.out + o);
@@ -338,14 +353,8 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
         }
     }
     if ((p.dbg & 4) && (ow_[0] ^ ow_[3] ^ ow_[5] ^ ow2_[1]) != 0x12345679) return;   // timing experiment: no stores
-    int4* dst = (int4*)((int8_t*)p.out + o);
-    dst[0] = make_int4(ow_[0], ow_[1], ow_[2], ow_[3]);
-    dst[1] = make_int4(ow_[4], ow_[5], ow_[6], ow_[7]);
-    if (has_bn2) {
-        int4* dst2 = (int4*)(p.out2 + o);
-        dst2[0] = make_int4(ow2_[0], ow2_[1], ow2_[2], ow2_[3]);
-        dst2[1] = make_int4(ow2_[4], ow2_[5], ow2_[6], ow2_[7]);
-    }
+    st_global_32B((int8_t*)p.out + o, ow_);
+    if (has_bn2) st_global_32B(p.out2 + o, ow2_);
 }
 
 // Epilogue role shared by both kernels.  Warps 2..9: warp w reads TMEM lanes
@@ -387,10 +396,7 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
         int rw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         const size_t o0 = pix * p.Cout + n0 + half * PER * 32;
         if (has_res && valid && !(p.dbg & 4)) {
-            const int4* rp = (const int4*)(p.res + o0);
-            int4 r0 = rp[0], r1 = rp[1];
-            rw[0] = r0.x; rw[1] = r0.y; rw[2] = r0.z; rw[3] = r0.w;
-            rw[4] = r1.x; rw[5] = r1.y; rw[6] = r1.z; rw[7] = r1.w;
+            ld_global_32B(p.res + o0, rw);
         }
         ok = mbar_wait(smem_u32(&sh->acc_full[a]), aphase, abort_flag, p.err, FFCU_ERR_EPI_TIMEOUT);
         if (!ok) break;
@@ -408,10 +414,7 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
             if (!valid) continue;
             int rn[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             if (has_res && jj + 1 < PER && !(p.dbg & 4)) {
-                const int4* rp = (const int4*)(p.res + o0 + (size_t)(jj + 1) * 32);
-                int4 r0 = rp[0], r1 = rp[1];
-                rn[0] = r0.x; rn[1] = r0.y; rn[2] = r0.z; rn[3] = r0.w;
-                rn[4] = r1.x; rn[5] = r1.y; rn[6] = r1.z; rn[7] = r1.w;
+                ld_global_32B(p.res + o0 + (size_t)(jj + 1) * 32, rn);
             }
             const int cb = n0 + j * 32;
             tc_epilogue_chunk<CONTRACT, OUT_F32, EPI>(p, tab, v, rw, cb, pix * p.Cout + cb, has_res, has_slope, has_bn2);

@@ -45,6 +45,7 @@ struct ffcu_ctx {
     float* d_out = nullptr;      // slot the next launch_forward writes
     cudaEvent_t ev_in_ready[2] = {}, ev_compute_done[2] = {}, ev_out_copied[2] = {};
     unsigned long long seq = 0;
+    int* d_fc_scratch = nullptr; // int32 [16][512] split-K accumulator of the small-batch FC (kept zero between calls)
     int* d_err = nullptr;        // device error word
     int* h_err = nullptr;        // pinned mirror
     cudaStream_t stream = nullptr;       // compute
@@ -52,6 +53,7 @@ struct ffcu_ctx {
     std::vector<DevLayer> layers;
     int mode = 1;
     int force_simt = 0;          // FF_CONV_IMPL=simt: every conv on the CUDA-core kernel
+    int no_fc_small = 0;         // FF_FC_SMALL=0: small batches take the large-batch FC path too
     int launches = 0;
     bool finalized = false;
 };
@@ -100,11 +102,14 @@ extern "C" ffcu_ctx* ffcu_create(int device, int max_batch, int n_bufs, size_t b
     ok = ok && cudaStreamCreateWithFlags(&c->s_in, cudaStreamNonBlocking) == cudaSuccess;
     ok = ok && cudaStreamCreateWithFlags(&c->s_out, cudaStreamNonBlocking) == cudaSuccess;
     ok = ok && cudaMalloc(&c->d_err, sizeof(int)) == cudaSuccess;
+    ok = ok && cudaMalloc(&c->d_fc_scratch, FFCU_FC_SMALL_MAX_BATCH * 512 * sizeof(int)) == cudaSuccess;
+    if (ok) cudaMemset(c->d_fc_scratch, 0, FFCU_FC_SMALL_MAX_BATCH * 512 * sizeof(int));
     ok = ok && cudaHostAlloc(&c->h_err, sizeof(int), cudaHostAllocDefault) == cudaSuccess;
     ok = ok && cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess;
     if (ok) { cudaMemset(c->d_err, 0, sizeof(int)); *c->h_err = 0; }
     const char* impl = getenv("FF_CONV_IMPL");
     c->force_simt = (impl && strcmp(impl, "simt") == 0) ? 1 : 0;
+    { const char* e = getenv("FF_FC_SMALL"); c->no_fc_small = (e && e[0] == '0') ? 1 : 0; }
     if (!ok) {
         ffcu_set_error("device allocation failed on device %d: %s", device, cudaGetErrorString(cudaGetLastError()));
         ffcu_destroy(c);
@@ -132,7 +137,7 @@ extern "C" void ffcu_destroy(ffcu_ctx* c)
         if (c->ev_compute_done[k]) cudaEventDestroy(c->ev_compute_done[k]);
         if (c->ev_out_copied[k]) cudaEventDestroy(c->ev_out_copied[k]);
     }
-    cudaFree(c->d_err);
+    cudaFree(c->d_err); cudaFree(c->d_fc_scratch);
     if (c->h_err) cudaFreeHost(c->h_err);
     if (c->stream) cudaStreamDestroy(c->stream);
     if (c->s_in) cudaStreamDestroy(c->s_in);
@@ -238,6 +243,9 @@ static int launch_layer(ffcu_ctx* c, size_t k, int n, int32_t* acc_dbg, bool unf
         return ffcu_launch_bn(c->bufs[d.src_buf], c->bufs[d.dst_buf], (size_t)n * d.H * d.W, d.Cout,
                               L.tab[5], L.tab[6], L.tab[7], L.tab[4], s);
     case FFCU_FC:
+        if (n <= FFCU_FC_SMALL_MAX_BATCH && d.Cout <= 512 && !c->no_fc_small)
+            return ffcu_launch_fc_small(c->bufs[d.src_buf], L.w, L.epi.w_scale, L.epi.bias, n, d.Cout, d.Cin, c->mode,
+                                        c->d_fc_scratch, c->d_out, s);
         if (L.tc) return ffcu_tc_launch(L.tc, n, c->mode, L.epi, nullptr, nullptr, c->d_out, nullptr, c->d_err, s);
         return ffcu_launch_fc_simt(c->bufs[d.src_buf], L.w, L.epi.w_scale, L.epi.bias, n, d.Cout, d.Cin,
                                    c->mode, c->d_out, s);
@@ -248,10 +256,15 @@ static int launch_layer(ffcu_ctx* c, size_t k, int n, int32_t* acc_dbg, bool unf
 
 static int launch_forward(ffcu_ctx* c, int n)
 {
+    int launches = 0;
     for (size_t k = 0; k < c->layers.size(); k++) {
         int rc = launch_layer(c, k, n, nullptr);
         if (rc != 0) return rc;
+        const DevLayer& L = c->layers[k];
+        if (!L.skip) launches++;
+        if (L.d.kind == FFCU_FC && n <= FFCU_FC_SMALL_MAX_BATCH && L.d.Cout <= 512 && !c->no_fc_small) launches++;
     }
+    c->launches = launches;
     return 0;
 }
 

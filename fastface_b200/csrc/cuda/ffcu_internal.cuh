@@ -142,6 +142,11 @@ int ffcu_launch_bn(const int8_t* in, int8_t* out, size_t n_pos, int C, const flo
 int ffcu_launch_fc_simt(const int8_t* act, const int8_t* w, const float* w_scale, const float* bias,
                         int batch, int N, int K, int mode, float* out, cudaStream_t s);
 
+// Small-batch (<= 16) split-K FC; scratch is an int32 [batch][N] accumulator, zero on entry and exit.
+#define FFCU_FC_SMALL_MAX_BATCH 16
+int ffcu_launch_fc_small(const int8_t* act, const int8_t* w, const float* w_scale, const float* bias,
+                         int batch, int N, int K, int mode, int* scratch, float* out, cudaStream_t s);
+
 // ---------------------------------------------------------------------------
 // Tensor-core implicit GEMM (conv_tc.cu)
 // ---------------------------------------------------------------------------

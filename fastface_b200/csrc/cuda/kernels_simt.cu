@@ -355,3 +355,97 @@ int ffcu_launch_stem(const float* in_f32, const float* inv3, const int8_t* w, co
     FFCU_CHECK(cudaGetLastError());
     return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Small-batch FC (batch <= 16): the 12.85 MB weight matrix is the whole cost, so the
+// K axis is split across blocks to put every SM on it.  Block (n-group, k-split) computes
+// 8 outputs x up to 16 faces over its K slice with dp4a, reduces across its 256 threads and
+// adds the int32 partial sums into a scratch accumulator [batch][N] (integer adds commute,
+// so the result is exact).  fc_finish_kernel then applies
+// out = bias + (float)dot * w_scale (reference kernels/gemm_int8_matvec.c:78-79) and
+// clears the scratch for the next call.
+// ---------------------------------------------------------------------------
+#define FCS_TN 8
+#define FCS_MAXB 16
+__global__ void __launch_bounds__(256) fc_splitk_kernel(const int8_t* __restrict__ act, const int8_t* __restrict__ w,
+                                                        int B, int N, int K, int k_per_split,
+                                                        int* __restrict__ scratch)
+{
+    __shared__ int red[8][FCS_MAXB * FCS_TN];
+    const int n0 = blockIdx.x * FCS_TN;
+    const int k0 = blockIdx.y * k_per_split;
+    const int kv = k_per_split >> 4;                       // 16-byte steps in this slice
+    int acc[FCS_MAXB][FCS_TN];
+#pragma unroll
+    for (int i = 0; i < FCS_MAXB; i++)
+#pragma unroll
+        for (int j = 0; j < FCS_TN; j++) acc[i][j] = 0;
+    for (int k = threadIdx.x; k < kv; k += blockDim.x) {
+        int4 ww[FCS_TN];
+#pragma unroll
+        for (int j = 0; j < FCS_TN; j++) ww[j] = __ldg((const int4*)(w + (size_t)(n0 + j) * K + k0) + k);
+#pragma unroll
+        for (int i = 0; i < FCS_MAXB; i++) {
+            if (i >= B) break;
+            const int4 a = __ldg((const int4*)(act + (size_t)i * K + k0) + k);
+#pragma unroll
+            for (int j = 0; j < FCS_TN; j++) {
+                int s = acc[i][j];
+                s = __dp4a(a.x, ww[j].x, s); s = __dp4a(a.y, ww[j].y, s);
+                s = __dp4a(a.z, ww[j].z, s); s = __dp4a(a.w, ww[j].w, s);
+                acc[i][j] = s;
+            }
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int i = 0; i < FCS_MAXB; i++) {
+        if (i >= B) break;
+#pragma unroll
+        for (int j = 0; j < FCS_TN; j++) {
+            int s = acc[i][j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (lane == 0) red[warp][i * FCS_TN + j] = s;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < B * FCS_TN) {
+        int s = 0;
+#pragma unroll
+        for (int wv = 0; wv < 8; wv++) s += red[wv][threadIdx.x];
+        const int i = threadIdx.x / FCS_TN, j = threadIdx.x % FCS_TN;
+        atomicAdd(scratch + (size_t)i * N + n0 + j, s);
+    }
+}
+
+template <bool CONTRACT>
+__global__ void fc_finish_kernel(int* __restrict__ scratch, const float* __restrict__ w_scale,
+                                 const float* __restrict__ bias, int total, int N, float* __restrict__ out)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int n = i % N;
+    const int dot = scratch[i];
+    scratch[i] = 0;                                        // leave the accumulator clean for the next call
+    out[i] = ffcu_fc_fp<CONTRACT>(dot, __ldg(w_scale + n), __ldg(bias + n));
+}
+
+// scratch: int32 [batch][N], all zero on entry (and again on exit).
+int ffcu_launch_fc_small(const int8_t* act, const int8_t* w, const float* w_scale, const float* bias,
+                         int batch, int N, int K, int mode, int* scratch, float* out, cudaStream_t s)
+{
+    if (batch < 1 || batch > FCS_MAXB || N % FCS_TN != 0 || K % 16 != 0) {
+        ffcu_set_error("small-batch FC needs 1 <= batch <= %d, N %% 8 == 0, K %% 16 == 0", FCS_MAXB);
+        return -1;
+    }
+    int splits = 16;
+    while (splits > 1 && (K % (splits * 16) != 0)) splits >>= 1;
+    dim3 grid(N / FCS_TN, splits);
+    fc_splitk_kernel<<<grid, 256, 0, s>>>(act, w, batch, N, K, K / splits, scratch);
+    const int total = batch * N;
+    if (mode) fc_finish_kernel<true><<<(total + 255) / 256, 256, 0, s>>>(scratch, w_scale, bias, total, N, out);
+    else      fc_finish_kernel<false><<<(total + 255) / 256, 256, 0, s>>>(scratch, w_scale, bias, total, N, out);
+    FFCU_CHECK(cudaGetLastError());
+    return 0;
+}

@@ -146,13 +146,13 @@ def test_unfused_plan_agrees(built_lib, model_root, ffw4, oracle, monkeypatch):
     faces = synth.faces(3, seed=41)
     want = oracle.forward(faces, ffo.CONTRACT)
     with ff.FastFace(ffw4, cwd=model_root, max_batch=3) as e:
-        n_fused = e.launches_per_forward
         assert np.array_equal(e.embed_batch(faces), want)
+        n_fused = e.launches_per_forward
     monkeypatch.setenv("FF_FUSE_BN", "0")
     monkeypatch.setenv("FF_FUSE_STEM", "0")
     with ff.FastFace(ffw4, cwd=model_root, max_batch=3) as e:
-        assert e.launches_per_forward == 80 and n_fused == 54
         assert np.array_equal(e.embed_batch(faces), want)
+        assert e.launches_per_forward == 81 and n_fused == 55   # + the FC finish kernel at batch <= 16
 
 
 @pytest.mark.parametrize("case", LAYER_CASES[:4], ids=lambda c: c[0])
@@ -279,6 +279,20 @@ def test_embed_and_embed_batch_agree_with_oracle(engine, oracle):
     # tolerance stated by the spec (met with margin, since the match is exact)
     assert np.abs(got - want).max() <= 1e-5
     assert ff.FastFace.cos_sim(got[0], want[0]) >= 0.99999
+
+
+def test_fc_paths(built_lib, model_root, ffw4, oracle, monkeypatch):
+    """The FC runs as a split-K CUDA-core kernel for batch <= 16 and on the tensor cores above;
+    both match the reference's matvec, and FF_FC_SMALL=0 sends a small batch down the large path."""
+    faces = synth.faces(20, seed=61)
+    want = oracle.forward(faces, ffo.CONTRACT)
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=20) as e:
+        assert np.array_equal(e.embed_batch(faces), want)            # tensor-core FC
+        assert np.array_equal(e.embed_batch(faces[:5]), want[:5])    # split-K FC
+        assert np.array_equal(e.embed_batch(faces[:5]), want[:5])    # scratch accumulator left clean
+    monkeypatch.setenv("FF_FC_SMALL", "0")
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=5) as e:
+        assert np.array_equal(e.embed_batch(faces[:5]), want[:5])
 
 
 def test_chunking_and_determinism(built_lib, model_root, ffw4, oracle):
