@@ -109,6 +109,20 @@ int ffcu_layer_info(const ffcu_ctx* c, int k, ffcu_layer* out, int* uses_tc);
 int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mode, int impl,
                    const int8_t* in, const int8_t* res, int32_t* acc_out, int8_t* out, int8_t* out_bn2);
 
+/* Small-batch FC (batch <= 16, N <= 512) that allocates nothing: no counterpart in the
+ * reference.  For callers that hold device buffers but cannot call cudaMalloc -- a serving loop
+ * that cannot afford an allocation's device-wide synchronisation, a plug-in given buffers but no
+ * allocator, a process with a fixed memory budget.  The split-K int32 accumulator the kernel
+ * needs is a fixed 32 KiB array inside the library's device image.  act int8 [batch][K],
+ * w int8 [N][K], w_scale / bias f32 [N], out f32 [batch][N]: all DEVICE pointers; stream is a
+ * cudaStream_t (NULL = default stream).  Sizes beyond the limit return -2 with a message.
+ * Every call on a device shares the one array (cleared at the start of each call): calls that
+ * can overlap on the GPU race.  The first call on a device resolves the array's address; make
+ * it outside any stream capture.  Computes out = bias + (float)dot * w_scale exactly as the FC
+ * of fastface_embed (reference kernels/gemm_int8_matvec.c:78-79). */
+int ffcu_fc_small_noalloc(const int8_t* act, const int8_t* w, const float* w_scale, const float* bias,
+                          int batch, int N, int K, int mode, float* out, void* stream);
+
 /* Dense INT8 tensor-core throughput (TOP/s, 2 ops per MAC) measured with operands already in
  * shared memory: M=128, N=bn (64/128/256), all SMs busy, `iters` rounds of four K=32 MMAs.
  * The practical ceiling the convolution kernels are compared against. */
