@@ -332,3 +332,16 @@ def test_against_live_reference_library(engine, model_root, ffw4):
     want = ref.embed(face)
     ref.close()
     assert np.array_equal(engine.embed(face), want)
+
+
+def test_multi_device_context_shards_the_batch(built_lib, model_root, ffw4, oracle):
+    """A context that owns two devices splits a batch into contiguous chunks (one host thread
+    per device, no exchange between devices); the result equals the single-device one."""
+    lib = ff.load_library()
+    if lib.ffcu_device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    faces = synth.faces(9, seed=123)
+    want = oracle.forward(faces, ffo.CONTRACT)
+    with ff.FastFace(ffw4, cwd=model_root, devices=[0, 1], max_batch=4) as e:
+        got = e.embed_batch(faces)          # 5 + 4 faces, in steps of at most 4 per device
+    assert np.array_equal(got, want)
