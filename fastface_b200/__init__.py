@@ -40,7 +40,8 @@ class FfcuLayer(C.Structure):
                 ("res_scale", C.c_void_p), ("inv_out", C.c_void_p), ("in_scale", C.c_void_p),
                 ("bn_scale", C.c_void_p), ("bn_offset", C.c_void_p),
                 ("bn2_dst_buf", C.c_int), ("bn2_op_index", C.c_int), ("bn2_in_scale", C.c_void_p),
-                ("bn2_scale", C.c_void_p), ("bn2_offset", C.c_void_p), ("bn2_inv_out", C.c_void_p)]
+                ("bn2_scale", C.c_void_p), ("bn2_offset", C.c_void_p), ("bn2_inv_out", C.c_void_p),
+                ("bn2_lut", C.c_void_p)]
 
 
 def load_library() -> C.CDLL:

@@ -33,6 +33,7 @@ struct TcPlan {
     CUtensorMap mapB;
     int n_sm;
     int group, pair_group;   // K blocks per pipeline stage
+    int lut_bytes;           // shared memory for the fused BN's byte table
     TcGeom geoms[8];
     int n_geoms;
     bool pair;               // CTA-pair kernel (cta_group::2) for >= 128 input channels
@@ -95,7 +96,9 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
     p->BN = L.Cout >= 256 ? 256 : L.Cout;
     const char* bn_env = getenv("FF_TC_BN");
     if (bn_env) { int v = atoi(bn_env); if ((v == 64 || v == 128 || v == 256) && L.Cout % v == 0) p->BN = v; }
-    const int fixed = TC_NTAB * TC_MAX_COUT * 4 + (int)sizeof(TcShared) + 1024;
+    const int lut_bytes = (L.kind == FFCU_CONV && L.bn2_dst_buf >= 0) ? p->BN * 256 : 0;
+    const int fixed = TC_NTAB * TC_MAX_COUT * 4 + (int)sizeof(TcShared) + 1024 + lut_bytes;
+    p->lut_bytes = lut_bytes;
     const int kblocks = L.Kh * L.Kw * (Cp / p->KC);
     const char* genv = getenv("FF_TC_GROUP");
     const int gmax = genv ? atoi(genv) : 8;
@@ -200,7 +203,7 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
         prm.TW = WS_TW; prm.TH = WS_TH; prm.TB = 1;
         prm.tiles_w = d.Wo / WS_TW; prm.tiles_h = (d.Ho + WS_TH - 1) / WS_TH; prm.tiles_b = batch; prm.tiles_n = 1;
         prm.total_tiles = prm.tiles_w * prm.tiles_h * batch;
-        prm.stages = p->ws_stages; prm.group = 1; prm.dbg = 0;
+        prm.stages = p->ws_stages; prm.group = 1; prm.dbg = 0; prm.lut_bytes = p->lut_bytes;
         int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
         return tc_launch_ws(p->BN, mode, epi, grid, p->ws_smem_bytes, s, p->mapA_ws, p->mapB, prm);
     }
@@ -226,16 +229,19 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
     prm.tiles_w = (d.Wo + TW - 1) / TW; prm.tiles_h = (d.Ho + TH - 1) / TH; prm.tiles_b = (batch + TB - 1) / TB;
     prm.tiles_n = d.Cout / p->BN;
     prm.total_tiles = prm.tiles_w * prm.tiles_h * prm.tiles_b * prm.tiles_n;
-    prm.stages = p->stages; prm.group = p->group; prm.dbg = dbg;
+    prm.stages = p->stages; prm.group = p->group; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes;
     { const char* e = getenv("FF_TC_STAGES"); if (e && atoi(e) >= 2 && atoi(e) < prm.stages) prm.stages = atoi(e); }
     if (p->pair) {
         const int m_tiles = prm.tiles_w * prm.tiles_h * prm.tiles_b;
         const int pairs = prm.tiles_n * ((m_tiles + 1) / 2);
         const int max_pairs = p->n_sm / 2;
         prm.stages = p->pair_stages; prm.group = p->pair_group;
-        const int pgrid = 2 * (pairs < max_pairs ? pairs : max_pairs);
+        int npairs = pairs < max_pairs ? pairs : max_pairs;
+        if (npairs > prm.tiles_n) npairs -= npairs % prm.tiles_n;      // a pair keeps one column tile (its BN table)
+        const int pgrid = 2 * npairs;
         return tc_launch_pair(p->BN, mode, epi, p->out_f32, pgrid, p->pair_smem_bytes, s, g->mapA, p->mapB_half, prm);
     }
     int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
+    if (grid > prm.tiles_n) grid -= grid % prm.tiles_n;                // a CTA keeps one column tile (its BN table)
     return tc_launch_generic(p->BN, p->KC, mode, epi, p->out_f32, grid, p->smem_bytes, s, g->mapA, p->mapB, prm);
 }

@@ -231,6 +231,7 @@ struct TcParams {
     int TW, TH, TB;
     int tiles_w, tiles_h, tiles_b, tiles_n, total_tiles;
     int stages;
+    int lut_bytes;           // shared-memory bytes of the fused BN's table (BN * 256, or 0)
     int group;               // K blocks per pipeline stage (one barrier hand-shake per `group` blocks)
     int dbg;                 // timing experiments only: bit 0 = skip the TMA loads, bit 1 = skip the MMAs
 };
@@ -242,7 +243,7 @@ struct TcParams {
 enum { EPI_RUNTIME = 0, EPI_PLAIN = 1, EPI_SLOPE = 2, EPI_RES_BN = 3, EPI_RES = 4 };
 
 #define TC_MAX_STAGES 8
-#define TC_NTAB 9          // w_scale, bias, slope, res_scale, inv_out, bn_in, bn_scale, bn_offset, bn_inv
+#define TC_NTAB 5          // w_scale, bias, slope, res_scale, inv_out (the fused BN is a byte table)
 #define TC_EPI_WARPS 8     // warps 2..9: two per TMEM lane quarter, each takes half the columns
 #define TC_THREADS (32 * (2 + TC_EPI_WARPS))
 
@@ -264,13 +265,17 @@ __device__ __forceinline__ void tc_load_tables(float* tab, const TcParams& p)
         tab[2 * TC_MAX_COUT + i] = p.t.slope ? p.t.slope[i] : 0.0f;
         tab[3 * TC_MAX_COUT + i] = p.t.res_scale ? p.t.res_scale[i] : 0.0f;
         tab[4 * TC_MAX_COUT + i] = p.t.inv_out ? p.t.inv_out[i] : 0.0f;
-        if (p.out2) {
-            tab[5 * TC_MAX_COUT + i] = p.t.bn_in[i];
-            tab[6 * TC_MAX_COUT + i] = p.t.bn_scale[i];
-            tab[7 * TC_MAX_COUT + i] = p.t.bn_offset[i];
-            tab[8 * TC_MAX_COUT + i] = p.t.bn_inv[i];
-        }
     }
+}
+
+// The fused BN pass as a byte table in shared memory: lut[c * 256 + (uint8_t)q] for the BN
+// channels [c0, c0 + bn) of this CTA's column tile (a CTA keeps one column tile for its lifetime).
+__device__ __forceinline__ void tc_load_lut(uint8_t* lut, const TcParams& p, int c0, int bn)
+{
+    if (!p.out2 || !p.lut_bytes) return;
+    const int4* src = (const int4*)(p.t.bn_lut + (size_t)c0 * 256);
+    int4* dst = (int4*)lut;
+    for (int i = threadIdx.x; i < bn * 16; i += TC_THREADS) dst[i] = __ldg(src + i);
 }
 
 // 32-byte global accesses (sm_100 has 256-bit vector loads / stores): one full sector per
@@ -291,9 +296,9 @@ __device__ __forceinline__ void ld_global_32B(const void* ptr, int (&w)[8])
 // (reference kernels/int8_epilogue.c:25-112), optionally followed by the next BN pass
 // (:253-318) as a second output.
 template <bool CONTRACT, bool OUT_F32, int EPI>
-__device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float* tab, const int (&v)[32],
-                                                  const int (&rw)[8], int cb, size_t o, bool rt_res,
-                                                  bool rt_slope, bool rt_bn2)
+__device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float* tab, const uint8_t* lut32,
+                                                  const int (&v)[32], const int (&rw)[8], int cb, size_t o,
+                                                  bool rt_res, bool rt_slope, bool rt_bn2)
 {
     const bool has_res = (EPI == EPI_RUNTIME) ? rt_res : (EPI == EPI_RES_BN || EPI == EPI_RES);
     const bool has_slope = (EPI == EPI_RUNTIME) ? rt_slope : (EPI == EPI_SLOPE);
@@ -341,15 +346,12 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
         int q2 = ffcu_requant_nosat(f2, iv.z), q3 = ffcu_requant_nosat(f3, iv.w);
         ow_[g] = ffcu_pack4(q0, q1, q2, q3);
         if (has_bn2) {
-            q0 = max(-128, min(127, q0)); q1 = max(-128, min(127, q1));
-            q2 = max(-128, min(127, q2)); q3 = max(-128, min(127, q3));
-            const float4 bi_ = *(const float4*)&tab[5 * TC_MAX_COUT + cb + 4 * g];
-            const float4 bs_ = *(const float4*)&tab[6 * TC_MAX_COUT + cb + 4 * g];
-            const float4 bo_ = *(const float4*)&tab[7 * TC_MAX_COUT + cb + 4 * g];
-            const float4 bv_ = *(const float4*)&tab[8 * TC_MAX_COUT + cb + 4 * g];
-            int b0 = ffcu_bn_q_nosat(q0, bi_.x, bs_.x, bo_.x, bv_.x), b1 = ffcu_bn_q_nosat(q1, bi_.y, bs_.y, bo_.y, bv_.y);
-            int b2 = ffcu_bn_q_nosat(q2, bi_.z, bs_.z, bo_.z, bv_.z), b3 = ffcu_bn_q_nosat(q3, bi_.w, bs_.w, bo_.w, bv_.w);
-            ow2_[g] = ffcu_pack4(b0, b1, b2, b3);
+            // BN of the four int8 results just packed: one table row per channel, indexed by the byte
+            const uint8_t* lc = lut32 + (4 * g) * 256;
+            const unsigned w = (unsigned)ow_[g];
+            const unsigned b0 = lc[w & 0xffu], b1 = lc[256 + ((w >> 8) & 0xffu)];
+            const unsigned b2 = lc[512 + ((w >> 16) & 0xffu)], b3 = lc[768 + (w >> 24)];
+            ow2_[g] = (int)(b0 | (b1 << 8) | (b2 << 16) | (b3 << 24));
         }
     }
     if ((p.dbg & 4) && (ow_[0] ^ ow_[3] ^ ow_[5] ^ ow2_[1]) != 0x12345679) return;   // timing experiment: no stores
@@ -360,7 +362,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
 // Epilogue role shared by both kernels.  Warps 2..9: warp w reads TMEM lanes
 // [32*(w%4), +32) (the hardware's per-warp lane window) and the column half (w-2)/4.
 template <int BN, bool CONTRACT, bool OUT_F32, int EPI>
-__device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float* tab, TcShared* sh,
+__device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float* tab, const uint8_t* lut, TcShared* sh,
                                                  uint32_t tmem_base, volatile int* abort_flag, int warp, int lane,
                                                  int first, int step, int total, int m_mul, int m_off,
                                                  uint32_t remote_acc_empty /* 0: local barrier */)
@@ -417,7 +419,7 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
                 ld_global_32B(p.res + o0 + (size_t)(jj + 1) * 32, rn);
             }
             const int cb = n0 + j * 32;
-            tc_epilogue_chunk<CONTRACT, OUT_F32, EPI>(p, tab, v, rw, cb, pix * p.Cout + cb, has_res, has_slope, has_bn2);
+            tc_epilogue_chunk<CONTRACT, OUT_F32, EPI>(p, tab, lut + (size_t)(j * 32) * 256, v, rw, cb, pix * p.Cout + cb, has_res, has_slope, has_bn2);
 #pragma unroll
             for (int g = 0; g < 8; g++) rw[g] = rn[g];
         }

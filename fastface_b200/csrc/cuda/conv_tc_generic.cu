@@ -18,13 +18,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     constexpr uint32_t IDESC = idesc_i8(BN);
 
     float* tab = (float*)(smem + (size_t)p.stages * p.group * SUB_BYTES);       // [TC_NTAB][TC_MAX_COUT]
-    TcShared* sh = (TcShared*)(tab + TC_NTAB * TC_MAX_COUT);
+    uint8_t* lut = (uint8_t*)(tab + TC_NTAB * TC_MAX_COUT);                  // [BN][256] fused-BN table (lut_bytes may be 0)
+    TcShared* sh = (TcShared*)(lut + p.lut_bytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int kblocks = p.taps * p.cin_blocks;
 
     tc_load_tables(tab, p);
+    tc_load_lut(lut, p, (int)(blockIdx.x % p.tiles_n) * BN, BN);
     tc_setup(sh, p.stages, TMEM_COLS, warp);
     const uint32_t tmem_base = sh->tmem_base;
     volatile int* abort_flag = &sh->abort_flag;
@@ -112,7 +114,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             }
         }
     } else {
-        tc_epilogue_role<BN, CONTRACT, OUT_F32, EPI>(p, tab, sh, tmem_base, abort_flag, warp, lane,
+        tc_epilogue_role<BN, CONTRACT, OUT_F32, EPI>(p, tab, lut, sh, tmem_base, abort_flag, warp, lane,
                                                 blockIdx.x, gridDim.x, p.total_tiles, 1, 0, 0u);
     }
     tc_teardown(abort_flag, tmem_base, TMEM_COLS, warp);

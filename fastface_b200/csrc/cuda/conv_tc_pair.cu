@@ -29,7 +29,8 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     constexpr uint32_t IDESC = idesc_i8(BN, 256);
 
     float* tab = (float*)(smem + (size_t)p.stages * p.group * SUB_BYTES);
-    TcShared* sh = (TcShared*)(tab + TC_NTAB * TC_MAX_COUT);
+    uint8_t* lut = (uint8_t*)(tab + TC_NTAB * TC_MAX_COUT);                  // [BN][256] fused-BN table (lut_bytes may be 0)
+    TcShared* sh = (TcShared*)(lut + p.lut_bytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -40,6 +41,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     const int total = p.tiles_n * ((m_tiles + 1) >> 1);  // pair tiles
 
     tc_load_tables(tab, p);
+    tc_load_lut(lut, p, (int)(pair_id % p.tiles_n) * BN, BN);
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; s++) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), 1); }
         for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&sh->acc_full[a]), 1); mbar_init(smem_u32(&sh->acc_empty[a]), 2 * TC_EPI_WARPS); }
@@ -145,7 +147,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         }
     } else {
         const uint32_t leader_acc_empty = map_to_cta(smem_u32(&sh->acc_empty[0]), 0);
-        tc_epilogue_role<BN, CONTRACT, OUT_F32, EPI>(p, tab, sh, tmem_base, abort_flag, warp, lane,
+        tc_epilogue_role<BN, CONTRACT, OUT_F32, EPI>(p, tab, lut, sh, tmem_base, abort_flag, warp, lane,
                                                 pair_id, n_pairs, total, 2, (int)rank, leader_acc_empty);
     }
 

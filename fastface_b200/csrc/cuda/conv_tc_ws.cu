@@ -29,12 +29,14 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     uint8_t* s_w = smem;                                        // [9][BN][64]
     uint8_t* s_a = smem + W_BYTES;                              // [stages][3][144][64]
     float* tab = (float*)(s_a + (size_t)p.stages * WS_A_BYTES);
-    TcShared* sh = (TcShared*)(tab + TC_NTAB * TC_MAX_COUT);
+    uint8_t* lut = (uint8_t*)(tab + TC_NTAB * TC_MAX_COUT);                  // [BN][256] fused-BN table (lut_bytes may be 0)
+    TcShared* sh = (TcShared*)(lut + p.lut_bytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
     tc_load_tables(tab, p);
+    tc_load_lut(lut, p, 0 * BN, BN);
     tc_setup(sh, p.stages, TMEM_COLS, warp);
     const uint32_t tmem_base = sh->tmem_base;
     volatile int* abort_flag = &sh->abort_flag;
@@ -96,7 +98,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             }
         }
     } else {
-        tc_epilogue_role<BN, CONTRACT, false, EPI>(p, tab, sh, tmem_base, abort_flag, warp, lane,
+        tc_epilogue_role<BN, CONTRACT, false, EPI>(p, tab, lut, sh, tmem_base, abort_flag, warp, lane,
                                              blockIdx.x, gridDim.x, p.total_tiles, 1, 0, 0u);
     }
     tc_teardown(abort_flag, tmem_base, TMEM_COLS, warp);

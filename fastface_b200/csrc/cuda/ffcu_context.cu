@@ -27,6 +27,7 @@ struct DevLayer {
     float* tab[12] = {};   // w_scale,bias,slope,res_scale,inv_out | in_scale,bn_scale,bn_offset | bn2 in,scale,offset,inv
     EpiTables epi{};
     TcPlan* tc = nullptr;  // non-NULL: tensor-core implicit GEMM takes this layer
+    int8_t* bn_lut = nullptr;  // device copy of the fused BN's table
     bool fused_stem = false;   // conv that also does the input quantisation (reads the fp32 input)
     bool skip = false;         // quantise layer absorbed by the fused stem
 };
@@ -126,7 +127,7 @@ extern "C" void ffcu_destroy(ffcu_ctx* c)
     if (c->s_in) cudaStreamSynchronize(c->s_in);
     if (c->s_out) cudaStreamSynchronize(c->s_out);
     for (auto& L : c->layers) {
-        cudaFree(L.w);
+        cudaFree(L.w); cudaFree(L.bn_lut);
         for (float* t : L.tab) cudaFree(t);
         ffcu_tc_free(L.tc);
     }
@@ -172,6 +173,15 @@ extern "C" int ffcu_add_layer(ffcu_ctx* c, const ffcu_layer* l)
     L.epi.w_scale = L.tab[0]; L.epi.bias = L.tab[1]; L.epi.slope = L.tab[2];
     L.epi.res_scale = L.tab[3]; L.epi.inv_out = L.tab[4];
     L.epi.bn_in = L.tab[8]; L.epi.bn_scale = L.tab[9]; L.epi.bn_offset = L.tab[10]; L.epi.bn_inv = L.tab[11];
+    if (l->bn2_dst_buf >= 0) {
+        std::vector<int8_t> lut((size_t)C * 256);
+        if (l->bn2_lut) memcpy(lut.data(), l->bn2_lut, lut.size());
+        else ff_bn_lut_build(l->bn2_in_scale, l->bn2_scale, l->bn2_offset, l->bn2_inv_out, C, lut.data());
+        if (cudaMalloc(&L.bn_lut, lut.size()) != cudaSuccess) { ffcu_set_error("BN table allocation failed"); return -1; }
+        cudaMemcpy(L.bn_lut, lut.data(), lut.size(), cudaMemcpyHostToDevice);
+    }
+    L.epi.bn_lut = L.bn_lut;
+    L.d.bn2_lut = nullptr;
     L.d.bn2_in_scale = L.d.bn2_scale = L.d.bn2_offset = L.d.bn2_inv_out = nullptr;
     L.d.w = nullptr;
     L.d.w_scale = L.d.bias = L.d.slope = L.d.res_scale = L.d.inv_out = nullptr;
@@ -447,7 +457,14 @@ extern "C" int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mo
                            bn2 ? l->bn2_in_scale : nullptr, bn2 ? l->bn2_scale : nullptr,
                            bn2 ? l->bn2_offset : nullptr, bn2 ? l->bn2_inv_out : nullptr};
     for (int k = 0; k < 9; k++) if (src[k]) tab[k] = upload_f32(src[k], l->Cout);
-    EpiTables t{tab[0], tab[1], tab[2], tab[3], tab[4], tab[5], tab[6], tab[7], tab[8]};
+    int8_t* d_lut = nullptr;
+    if (bn2) {
+        std::vector<int8_t> lut((size_t)l->Cout * 256);
+        ff_bn_lut_build(l->bn2_in_scale, l->bn2_scale, l->bn2_offset, l->bn2_inv_out, l->Cout, lut.data());
+        FFCU_CHECK(cudaMalloc(&d_lut, lut.size()));
+        FFCU_CHECK(cudaMemcpy(d_lut, lut.data(), lut.size(), cudaMemcpyHostToDevice));
+    }
+    EpiTables t{tab[0], tab[1], tab[2], tab[3], tab[4], tab[5], tab[6], tab[7], tab[8], d_lut};
     cudaStream_t s; FFCU_CHECK(cudaStreamCreate(&s));
     int rc = 0;
     if (impl == 0) {
@@ -472,7 +489,7 @@ extern "C" int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mo
     if (rc == 0 && out) cudaMemcpy(out, d_out, out_elems, cudaMemcpyDeviceToHost);
     if (rc == 0 && bn2) cudaMemcpy(out_bn2, d_out2, out_elems, cudaMemcpyDeviceToHost);
     cudaStreamDestroy(s);
-    cudaFree(d_in); cudaFree(d_res); cudaFree(d_out); cudaFree(d_out2); cudaFree(d_w); cudaFree(d_acc); cudaFree(d_err);
+    cudaFree(d_lut); cudaFree(d_in); cudaFree(d_res); cudaFree(d_out); cudaFree(d_out2); cudaFree(d_w); cudaFree(d_acc); cudaFree(d_err);
     for (float* q : tab) cudaFree(q);
     return rc;
 }

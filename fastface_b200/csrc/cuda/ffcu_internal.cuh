@@ -43,6 +43,7 @@ struct EpiTables {
     const float* bn_scale;
     const float* bn_offset;
     const float* bn_inv;
+    const int8_t* bn_lut;    // [Cout][256]: BN of every int8 value (ff_bn_lut_build), or NULL
 };
 
 // ---------------------------------------------------------------------------

@@ -260,7 +260,8 @@ __global__ void __launch_bounds__(256) stem_kernel(const float* __restrict__ in,
     constexpr int H = 112, W = 112, C = 64, P = STEM_T + 2;
     __shared__ int s_in[P * P];
     __shared__ __align__(16) int s_w[9 * C];          // [tap][co]
-    __shared__ __align__(16) float s_tab[8 * C];      // w_scale, bias, slope, inv_out, bn_in, bn_scale, bn_offset, bn_inv
+    __shared__ __align__(16) float s_tab[4 * C];      // w_scale, bias, slope, inv_out
+    __shared__ __align__(16) uint8_t s_lut[HAS_BN2 ? C * 256 : 16];   // the following BN pass as a byte table
     const int b = blockIdx.z;
     const int x0 = blockIdx.x * STEM_T, y0 = blockIdx.y * STEM_T;
     const float i0 = __ldg(inv3), i1 = __ldg(inv3 + 1), i2 = __ldg(inv3 + 2);
@@ -284,11 +285,9 @@ __global__ void __launch_bounds__(256) stem_kernel(const float* __restrict__ in,
     for (int i = threadIdx.x; i < C; i += 256) {
         s_tab[0 * C + i] = t.w_scale[i]; s_tab[1 * C + i] = t.bias[i];
         s_tab[2 * C + i] = t.slope ? t.slope[i] : 0.0f; s_tab[3 * C + i] = t.inv_out[i];
-        if (has_bn2) {
-            s_tab[4 * C + i] = t.bn_in[i]; s_tab[5 * C + i] = t.bn_scale[i];
-            s_tab[6 * C + i] = t.bn_offset[i]; s_tab[7 * C + i] = t.bn_inv[i];
-        }
     }
+    if (has_bn2)
+        for (int i = threadIdx.x; i < C * 16; i += 256) ((int4*)s_lut)[i] = __ldg((const int4*)t.bn_lut + i);
     __syncthreads();
     const int tx = threadIdx.x % STEM_T, ty = threadIdx.x / STEM_T;
     int a[9];
@@ -324,13 +323,11 @@ __global__ void __launch_bounds__(256) stem_kernel(const float* __restrict__ in,
             int q3 = ffcu_requant(ffcu_conv_fp<CONTRACT>(acc3, ws.w, bi.w, false, 0, 0.0f, has_slope, sl.w), iv.w);
             wo[g] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
             if (has_bn2) {
-                const float4 b_i = *(const float4*)&s_tab[4 * C + co];
-                const float4 b_s = *(const float4*)&s_tab[5 * C + co];
-                const float4 b_o = *(const float4*)&s_tab[6 * C + co];
-                const float4 b_v = *(const float4*)&s_tab[7 * C + co];
-                int r0 = ffcu_bn_q(q0, b_i.x, b_s.x, b_o.x, b_v.x), r1 = ffcu_bn_q(q1, b_i.y, b_s.y, b_o.y, b_v.y);
-                int r2 = ffcu_bn_q(q2, b_i.z, b_s.z, b_o.z, b_v.z), r3 = ffcu_bn_q(q3, b_i.w, b_s.w, b_o.w, b_v.w);
-                wo2[g] = (r0 & 0xff) | ((r1 & 0xff) << 8) | ((r2 & 0xff) << 16) | ((r3 & 0xff) << 24);
+                const uint8_t* lc = s_lut + co * 256;
+                const unsigned w4 = (unsigned)wo[g];
+                const unsigned r0 = lc[w4 & 0xffu], r1 = lc[256 + ((w4 >> 8) & 0xffu)];
+                const unsigned r2 = lc[512 + ((w4 >> 16) & 0xffu)], r3 = lc[768 + (w4 >> 24)];
+                wo2[g] = (int)(r0 | (r1 << 8) | (r2 << 16) | (r3 << 24));
             }
         }
         dst[g16] = make_int4(wo[0], wo[1], wo[2], wo[3]);
@@ -342,7 +339,7 @@ int ffcu_launch_stem(const float* in_f32, const float* inv3, const int8_t* w, co
                      int mode, int8_t* out, int8_t* out_bn2, int8_t* q_out, cudaStream_t s)
 {
     dim3 grid(112 / STEM_T, 112 / STEM_T, batch);
-    const bool sl = t.slope != nullptr, bn = (out_bn2 != nullptr) && (t.bn_in != nullptr);
+    const bool sl = t.slope != nullptr, bn = (out_bn2 != nullptr) && (t.bn_lut != nullptr);
 #define STEM_GO(C_, S_, B_) stem_kernel<C_, S_, B_><<<grid, 256, 0, s>>>(in_f32, inv3, w, t, out, out_bn2, (int*)q_out)
     if (mode) {
         if (sl && bn) STEM_GO(true, true, true); else if (sl) STEM_GO(true, true, false);

@@ -14,6 +14,8 @@
 #define _POSIX_C_SOURCE 200809L
 #include "ff_plan.h"
 
+#include <limits.h>
+#include <math.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -45,6 +47,30 @@ static const float* copy_f32(ff_plan* p, const float* src, int n)
     float* a = (float*)pool_alloc(p, (size_t)n * sizeof(float));
     memcpy(a, src, (size_t)n * sizeof(float));
     return a;
+}
+
+/* kernels/int8_epilogue.c:272-303 evaluated for all 256 int8 inputs of each channel.  Built
+ * with -ffp-contract=off: every line below is one IEEE operation, as in the CUDA kernels. */
+void ff_bn_lut_build(const float* in_scale, const float* bn_scale, const float* bn_offset,
+                     const float* inv_out, int C, int8_t* lut)
+{
+    for (int c = 0; c < C; c++)
+        for (int ub = 0; ub < 256; ub++) {
+            const int q = (int)(int8_t)(uint8_t)ub;
+            float t = (float)q * in_scale[c];
+            t = fmaf(t, bn_scale[c], bn_offset[c]);
+            const float qq = t * inv_out[c];
+            uint32_t bits; memcpy(&bits, &qq, 4);
+            const uint32_t hb = 0x3f000000u | (bits & 0x80000000u);
+            float half; memcpy(&half, &hb, 4);
+            const float r = qq + half;
+            int i;
+            if (!(fabsf(r) < 2147483648.0f)) i = INT_MIN;      /* cvttps2dq on overflow / NaN */
+            else i = (int)r;
+            if (i < -128) i = -128;
+            if (i > 127) i = 127;
+            lut[c * 256 + ub] = (int8_t)i;
+        }
 }
 
 typedef struct { int C, H, W; } shape3;
@@ -220,6 +246,9 @@ int ff_plan_build(ff_plan* p, const ff_model* m)
                 prev->bn2_scale = copy_f32(p, op->bn_scale, C);
                 prev->bn2_offset = copy_f32(p, op->bn_offset, C);
                 prev->bn2_inv_out = per_channel(p, inv_pc, 1.0f / (next_scale + 1e-9f), C);
+                int8_t* lut = (int8_t*)pool_alloc(p, (size_t)C * 256);
+                ff_bn_lut_build(prev->bn2_in_scale, prev->bn2_scale, prev->bn2_offset, prev->bn2_inv_out, C, lut);
+                prev->bn2_lut = lut;
             } else {
                 ffcu_layer* l = push_layer(p, &cap);
                 l->kind = FFCU_BN; l->op_index = i;

@@ -53,7 +53,16 @@ typedef struct {
     const float* bn2_scale;
     const float* bn2_offset;
     const float* bn2_inv_out;
+    /* Optional: the same BN as a table, [Cout][256] int8 indexed by the int8 value's byte
+     * (two's complement, 0..255); ff_bn_lut_build fills it.  NULL: the kernels compute BN. */
+    const int8_t* bn2_lut;
 } ffcu_layer;
+
+/* BN + requantisation of every int8 input value, per channel: lut[c*256 + (uint8_t)q] =
+ * bn_prelu_requant_int8 (reference kernels/int8_epilogue.c:253-318) applied to q in channel c.
+ * Plain host arithmetic with one IEEE rounding per operation, bit-identical to the kernels. */
+void ff_bn_lut_build(const float* in_scale, const float* bn_scale, const float* bn_offset,
+                     const float* inv_out, int C, int8_t* lut);
 
 /* Devices visible to the process; <0 on a CUDA error. */
 int ffcu_device_count(void);
