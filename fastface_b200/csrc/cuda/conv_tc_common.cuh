@@ -244,7 +244,12 @@ enum { EPI_RUNTIME = 0, EPI_PLAIN = 1, EPI_SLOPE = 2, EPI_RES_BN = 3, EPI_RES = 
 
 #define TC_MAX_STAGES 8
 #define TC_NTAB 5          // w_scale, bias, slope, res_scale, inv_out (the fused BN is a byte table)
-#define TC_EPI_WARPS 8     // warps 2..9: two per TMEM lane quarter, each takes half the columns
+#ifndef TC_EPI_WARPS
+#define TC_EPI_WARPS 8     // warps 2..9: two per TMEM lane quarter, each takes half the columns (16 measured no faster)
+#endif
+#define TC_EPI_COLGROUPS (TC_EPI_WARPS / 4)
+// epilogue warps that actually have columns to process for a BN-wide tile (a chunk is 32 columns)
+#define TC_EPI_ACTIVE(BN) (4 * ((BN) / 32 < TC_EPI_COLGROUPS ? (BN) / 32 : TC_EPI_COLGROUPS))
 #define TC_THREADS (32 * (2 + TC_EPI_WARPS))
 
 struct TcShared {                 // lives after the stage ring and the tables
@@ -360,7 +365,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
 }
 
 // Epilogue role shared by both kernels.  Warps 2..9: warp w reads TMEM lanes
-// [32*(w%4), +32) (the hardware's per-warp lane window) and the column half (w-2)/4.
+// [32*(w%4), +32) (the hardware's per-warp lane window) and the column group (w-2)/4.
 template <int BN, bool CONTRACT, bool OUT_F32, int EPI>
 __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float* tab, const uint8_t* lut, TcShared* sh,
                                                  uint32_t tmem_base, volatile int* abort_flag, int warp, int lane,
@@ -368,9 +373,11 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
                                                  uint32_t remote_acc_empty /* 0: local barrier */)
 {
     const int q = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = (warp - 2) >> 2;                     // column group of this warp
     constexpr int CHUNKS = BN / 32;                       // 2, 4 or 8
-    constexpr int PER = CHUNKS / 2;
+    constexpr int GROUPS = CHUNKS < TC_EPI_COLGROUPS ? CHUNKS : TC_EPI_COLGROUPS;
+    constexpr int PER = CHUNKS / GROUPS;
+    if (half >= GROUPS) return;                           // narrow tiles: the extra warps have no columns
     const int row = q * 32 + lane;
     const int iw = row % p.TW;
     const int ih = (row / p.TW) % p.TH;
@@ -433,11 +440,11 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
     }
 }
 
-__device__ __forceinline__ void tc_setup(TcShared* sh, int stages, uint32_t tmem_cols, int warp)
+__device__ __forceinline__ void tc_setup(TcShared* sh, int stages, uint32_t tmem_cols, int warp, int epi_active)
 {
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; s++) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), 1); }
-        for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&sh->acc_full[a]), 1); mbar_init(smem_u32(&sh->acc_empty[a]), TC_EPI_WARPS); }
+        for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&sh->acc_full[a]), 1); mbar_init(smem_u32(&sh->acc_empty[a]), epi_active); }
         mbar_init(smem_u32(&sh->w_full), 1);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
