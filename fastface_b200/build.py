@@ -18,6 +18,7 @@ ROOT = os.path.dirname(PKG)
 INC = os.path.join(ROOT, "include")
 OBJ = os.path.join(PKG, "csrc", "_obj")
 LIB = os.path.join(PKG, "libfastface_b200.so")
+CLI = os.path.join(PKG, "fastface_int8_b200")     # reference-compatible command-line driver
 
 HOST_SRCS = ["csrc/host/ff_model.c", "csrc/host/ff_plan.c", "csrc/host/fastface_api.c"]
 CUDA_SRCS = ["csrc/cuda/ffcu_context.cu", "csrc/cuda/kernels_simt.cu", "csrc/cuda/conv_tc.cu",
@@ -81,6 +82,15 @@ def build(force: bool = False, verbose: bool = False) -> str:
         r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout.decode()}")
+    cli_src = os.path.join(PKG, "csrc", "host", "fastface_cli.c")
+    if force or _stale(CLI, [cli_src, LIB] + hdrs):
+        cmd = ["gcc", "-std=c11", "-O2", "-Wall", "-I" + INC, cli_src, "-o", CLI, "-L" + PKG, "-lfastface_b200",
+               "-Wl,-rpath,$ORIGIN", "-lm"]
+        if verbose:
+            print(" ".join(cmd))
+        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+        if r.returncode != 0:
+            raise RuntimeError(f"building the CLI failed:\n{r.stdout.decode()}")
     return LIB
 
 

@@ -345,3 +345,30 @@ def test_multi_device_context_shards_the_batch(built_lib, model_root, ffw4, orac
     with ff.FastFace(ffw4, cwd=model_root, devices=[0, 1], max_batch=4) as e:
         got = e.embed_batch(faces)          # 5 + 4 faces, in steps of at most 4 per device
     assert np.array_equal(got, want)
+
+
+def test_cli_file_and_server_modes(built_lib, model_root, ffw4, oracle):
+    """The reference-compatible CLI (arcface_forward_int8_batched.c:523-553): --in/--out dumps and
+    the --server stdin/stdout protocol its Python / Go wrappers speak."""
+    import subprocess
+    from fastface_b200 import build as _b
+    exe = _b.CLI
+    faces = synth.faces(4, seed=88)
+    want = oracle.forward(faces, ffo.CONTRACT)
+    inp, outp = os.path.join(model_root, "_cli_in.bin"), os.path.join(model_root, "_cli_out.bin")
+    faces.tofile(inp)
+    r = subprocess.run([exe, ffw4, "--batch", "4", "--in", inp, "--out", outp], cwd=model_root, capture_output=True, timeout=300)
+    assert r.returncode == 0, r.stderr.decode()[-500:]
+    assert np.array_equal(np.fromfile(outp, np.float32).reshape(4, 512), want)
+    p = subprocess.Popen([exe, ffw4, "--batch", "2", "--server"], cwd=model_root, stdin=subprocess.PIPE,
+                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL)
+    try:
+        for k in (0, 2):
+            p.stdin.write(faces[k:k + 2].tobytes()); p.stdin.flush()
+            raw = p.stdout.read(2 * 512 * 4)
+            assert np.array_equal(np.frombuffer(raw, np.float32).reshape(2, 512), want[k:k + 2])
+        p.stdin.write(b"\0" * 100); p.stdin.close()          # partial batch: abort with exit code 4
+        assert p.wait(timeout=60) == 4
+    finally:
+        if p.poll() is None:
+            p.kill()
