@@ -119,6 +119,7 @@ class FastFace:
             raise RuntimeError("fastface_create failed: " + self.lib.fastface_last_error().decode())
         self.max_batch = mb
         self.n_devices = len(devs)
+        self.device0 = devs[0]
 
     # -- reference wrapper surface -------------------------------------------------
     def embed(self, arr: np.ndarray) -> np.ndarray:

@@ -7,6 +7,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <map>
 #include <vector>
 
 static thread_local char g_cu_err[512];
@@ -57,6 +58,11 @@ struct ffcu_ctx {
     int no_fc_small = 0;         // FF_FC_SMALL=0: small batches take the large-batch FC path too
     int launches = 0;
     bool finalized = false;
+    // Small batches are launch-bound (55 short kernels): their forward is captured once per
+    // (batch, mode, input/output slot) into a CUDA graph and replayed.
+    int graph_max_batch = 64;    // FF_GRAPH=0 disables (0)
+    std::map<long long, cudaGraphExec_t> graphs;
+    std::map<long long, int> graph_launches;
 };
 
 extern "C" int ffcu_device_count(void)
@@ -111,6 +117,7 @@ extern "C" ffcu_ctx* ffcu_create(int device, int max_batch, int n_bufs, size_t b
     const char* impl = getenv("FF_CONV_IMPL");
     c->force_simt = (impl && strcmp(impl, "simt") == 0) ? 1 : 0;
     { const char* e = getenv("FF_FC_SMALL"); c->no_fc_small = (e && e[0] == '0') ? 1 : 0; }
+    { const char* e = getenv("FF_GRAPH"); if (e && e[0] == '0') c->graph_max_batch = 0; }
     if (!ok) {
         ffcu_set_error("device allocation failed on device %d: %s", device, cudaGetErrorString(cudaGetLastError()));
         ffcu_destroy(c);
@@ -126,6 +133,7 @@ extern "C" void ffcu_destroy(ffcu_ctx* c)
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->s_in) cudaStreamSynchronize(c->s_in);
     if (c->s_out) cudaStreamSynchronize(c->s_out);
+    for (auto& g : c->graphs) cudaGraphExecDestroy(g.second);
     for (auto& L : c->layers) {
         cudaFree(L.w); cudaFree(L.bn_lut);
         for (float* t : L.tab) cudaFree(t);
@@ -278,6 +286,43 @@ static int launch_forward(ffcu_ctx* c, int n)
     return 0;
 }
 
+// Forward for n faces on the compute stream: replay of a captured graph for small batches
+// (after one eager run of that shape, which also sets the kernels' one-time attributes).
+static int run_forward(ffcu_ctx* c, int n, int slot)
+{
+    if (n > c->graph_max_batch) return launch_forward(c, n);
+    const long long key = ((long long)n << 8) | ((long long)c->mode << 4) | slot;
+    auto it = c->graphs.find(key);
+    if (it != c->graphs.end()) {
+        FFCU_CHECK(cudaGraphLaunch(it->second, c->stream));
+        c->launches = c->graph_launches[key];
+        return 0;
+    }
+    auto seen = c->graph_launches.find(key);
+    if (seen == c->graph_launches.end()) {          // first time: eager
+        int rc = launch_forward(c, n);
+        if (rc == 0) c->graph_launches[key] = c->launches;
+        return rc;
+    }
+    cudaGraph_t graph = nullptr;
+    FFCU_CHECK(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    int rc = launch_forward(c, n);
+    cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+    if (rc != 0 || e != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        c->graph_max_batch = 0;                     // capture not possible here: stay eager
+        return rc != 0 ? rc : launch_forward(c, n);
+    }
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess || !exec) { cudaGetLastError(); c->graph_max_batch = 0; return launch_forward(c, n); }
+    c->graphs[key] = exec;
+    FFCU_CHECK(cudaGraphLaunch(exec, c->stream));
+    return 0;
+}
+
 extern "C" int ffcu_submit(ffcu_ctx* c, const float* host_in, int n, float* host_out)
 {
     if (!c || !c->finalized || !host_in || !host_out || n < 1 || n > c->max_batch) {
@@ -295,7 +340,7 @@ extern "C" int ffcu_submit(ffcu_ctx* c, const float* host_in, int n, float* host
     FFCU_CHECK(cudaStreamWaitEvent(c->stream, c->ev_in_ready[slot], 0));
     if (reused) FFCU_CHECK(cudaStreamWaitEvent(c->stream, c->ev_out_copied[slot], 0));
     c->d_in = c->in_slot[slot]; c->d_out = c->out_slot[slot];
-    int rc = launch_forward(c, n);
+    int rc = run_forward(c, n, slot);
     if (rc != 0) return rc;
     FFCU_CHECK(cudaEventRecord(c->ev_compute_done[slot], c->stream));
     // copy-out stream
@@ -378,6 +423,7 @@ extern "C" int ffcu_bench_resident(ffcu_ctx* c, const float* host_in, int n, int
 {
     if (!c || !c->finalized || !host_in || !ms || n < 1 || n > c->max_batch || iters < 1) return -1;
     FFCU_CHECK(cudaSetDevice(c->device));
+    c->d_in = c->in_slot[0]; c->d_out = c->out_slot[0];
     FFCU_CHECK(cudaMemcpyAsync(c->d_in, host_in, (size_t)n * 37632 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
     cudaEvent_t e0, e1;
     FFCU_CHECK(cudaEventCreate(&e0));
@@ -385,7 +431,7 @@ extern "C" int ffcu_bench_resident(ffcu_ctx* c, const float* host_in, int n, int
     FFCU_CHECK(cudaStreamSynchronize(c->stream));
     FFCU_CHECK(cudaEventRecord(e0, c->stream));
     int rc = 0;
-    for (int it = 0; it < iters && rc == 0; it++) rc = launch_forward(c, n);
+    for (int it = 0; it < iters && rc == 0; it++) rc = run_forward(c, n, 0);
     FFCU_CHECK(cudaEventRecord(e1, c->stream));
     int wrc = ffcu_wait(c);
     if (rc == 0) rc = wrc;
