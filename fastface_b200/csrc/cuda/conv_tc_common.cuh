@@ -196,6 +196,18 @@ __device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, int (&v)[32]) { tmem_ld32(taddr, v); }
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, int (&v)[16]) { tmem_ld16(taddr, v); }
+
 // K-major shared-memory matrix descriptor: rows of ROWB bytes (= swizzle span), 8-row groups
 // 8*ROWB bytes apart, descriptor version 1 (sm_100), layout 2 = 128B swizzle / 4 = 64B swizzle.
 template <int ROWB>
@@ -233,7 +245,7 @@ struct TcParams {
     int stages;
     int lut_bytes;           // shared-memory bytes of the fused BN's table (BN * 256, or 0)
     int group;               // K blocks per pipeline stage (one barrier hand-shake per `group` blocks)
-    int dbg;                 // timing experiments only: bit 0 = skip the TMA loads, bit 1 = skip the MMAs
+    int dbg;                 // timing experiments only ($FF_TC_DBG): bit 0 = skip the TMA loads, bit 1 = skip the MMAs
 };
 
 // Epilogue variants.  All but EPI_RUNTIME fix the presence of PReLU / residual / fused BN at
@@ -245,11 +257,11 @@ enum { EPI_RUNTIME = 0, EPI_PLAIN = 1, EPI_SLOPE = 2, EPI_RES_BN = 3, EPI_RES = 
 #define TC_MAX_STAGES 8
 #define TC_NTAB 5          // w_scale, bias, slope, res_scale, inv_out (the fused BN is a byte table)
 #ifndef TC_EPI_WARPS
-#define TC_EPI_WARPS 8     // warps 2..9: two per TMEM lane quarter, each takes half the columns (16 measured no faster)
+#define TC_EPI_WARPS 8     // warps 2..9: two per TMEM lane quarter, each takes half the columns (16 warps, with 16-column chunks for the narrow tiles, measured no faster: the epilogue is issue-bound, not latency-bound)
 #endif
 #define TC_EPI_COLGROUPS (TC_EPI_WARPS / 4)
 // epilogue warps that actually have columns to process for a BN-wide tile (a chunk is 32 columns)
-#define TC_EPI_ACTIVE(BN) (4 * ((BN) / 32 < TC_EPI_COLGROUPS ? (BN) / 32 : TC_EPI_COLGROUPS))
+#define TC_EPI_ACTIVE(BN) (4 * ((BN) / 16 < TC_EPI_COLGROUPS ? (BN) / 16 : TC_EPI_COLGROUPS))
 #define TC_THREADS (32 * (2 + TC_EPI_WARPS))
 
 struct TcShared {                 // lives after the stage ring and the tables
@@ -300,17 +312,18 @@ __device__ __forceinline__ void ld_global_32B(const void* ptr, int (&w)[8])
 // (= pixel * Cout + first channel cb).  Replaces fused_epilogue_int8 for those 32 values
 // (reference kernels/int8_epilogue.c:25-112), optionally followed by the next BN pass
 // (:253-318) as a second output.
-template <bool CONTRACT, bool OUT_F32, int EPI>
-__device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float* tab, const uint8_t* lut32,
-                                                  const int (&v)[32], const int (&rw)[8], int cb, size_t o,
+template <bool CONTRACT, bool OUT_F32, int EPI, int CW>
+__device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float* tab, const uint8_t* lutc,
+                                                  const int (&v)[CW], const int (&rw)[CW / 4], int cb, size_t o,
                                                   bool rt_res, bool rt_slope, bool rt_bn2)
 {
+    constexpr int NG = CW / 4;                            // groups of four channels
     const bool has_res = (EPI == EPI_RUNTIME) ? rt_res : (EPI == EPI_RES_BN || EPI == EPI_RES);
     const bool has_slope = (EPI == EPI_RUNTIME) ? rt_slope : (EPI == EPI_SLOPE);
     const bool has_bn2 = (EPI == EPI_RUNTIME) ? rt_bn2 : (EPI == EPI_RES_BN);
-    if (p.acc_out) {
+    if (p.acc_out) {                                      // dump-point mode: raw accumulators
 #pragma unroll
-        for (int g = 0; g < 4; g++) {
+        for (int g = 0; g < CW / 8; g++) {
             const int w8[8] = {v[8 * g], v[8 * g + 1], v[8 * g + 2], v[8 * g + 3], v[8 * g + 4], v[8 * g + 5], v[8 * g + 6], v[8 * g + 7]};
             st_global_32B(p.acc_out + o + 8 * g, w8);
         }
@@ -318,7 +331,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
     if (OUT_F32) {
         float4* dst = (float4*)((float*)p.out + o);
 #pragma unroll
-        for (int g = 0; g < 8; g++) {
+        for (int g = 0; g < NG; g++) {
             const float4 ws = *(const float4*)&tab[0 * TC_MAX_COUT + cb + 4 * g];
             const float4 bi = *(const float4*)&tab[1 * TC_MAX_COUT + cb + 4 * g];
             float4 r;
@@ -330,13 +343,9 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
         }
         return;
     }
-    int ow_[8], ow2_[8];
-    if (p.dbg & 8) {                                                                       // timing experiment: no math
+    int ow_[NG], ow2_[NG];
 #pragma unroll
-        for (int g = 0; g < 8; g++) { ow_[g] = v[4 * g] ^ v[4 * g + 1] ^ v[4 * g + 2] ^ v[4 * g + 3]; ow2_[g] = ow_[g] + 1; }
-    } else
-#pragma unroll
-    for (int g = 0; g < 8; g++) {
+    for (int g = 0; g < NG; g++) {
         const float4 ws = *(const float4*)&tab[0 * TC_MAX_COUT + cb + 4 * g];
         const float4 bi = *(const float4*)&tab[1 * TC_MAX_COUT + cb + 4 * g];
         const float4 sl = *(const float4*)&tab[2 * TC_MAX_COUT + cb + 4 * g];
@@ -352,16 +361,26 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
         ow_[g] = ffcu_pack4(q0, q1, q2, q3);
         if (has_bn2) {
             // BN of the four int8 results just packed: one table row per channel, indexed by the byte
-            const uint8_t* lc = lut32 + (4 * g) * 256;
+            const uint8_t* lc = lutc + (4 * g) * 256;
             const unsigned w = (unsigned)ow_[g];
             const unsigned b0 = lc[w & 0xffu], b1 = lc[256 + ((w >> 8) & 0xffu)];
             const unsigned b2 = lc[512 + ((w >> 16) & 0xffu)], b3 = lc[768 + (w >> 24)];
             ow2_[g] = (int)(b0 | (b1 << 8) | (b2 << 16) | (b3 << 24));
+        } else {
+            ow2_[g] = 0;
         }
     }
-    if ((p.dbg & 4) && (ow_[0] ^ ow_[3] ^ ow_[5] ^ ow2_[1]) != 0x12345679) return;   // timing experiment: no stores
-    st_global_32B((int8_t*)p.out + o, ow_);
-    if (has_bn2) st_global_32B(p.out2 + o, ow2_);
+    if (CW == 32) {
+        const int w0[8] = {ow_[0], ow_[1], ow_[2], ow_[3], ow_[NG - 4], ow_[NG - 3], ow_[NG - 2], ow_[NG - 1]};
+        st_global_32B((int8_t*)p.out + o, w0);
+        if (has_bn2) {
+            const int w1[8] = {ow2_[0], ow2_[1], ow2_[2], ow2_[3], ow2_[NG - 4], ow2_[NG - 3], ow2_[NG - 2], ow2_[NG - 1]};
+            st_global_32B(p.out2 + o, w1);
+        }
+    } else {
+        *(int4*)((int8_t*)p.out + o) = make_int4(ow_[0], ow_[1], ow_[2], ow_[3]);
+        if (has_bn2) *(int4*)(p.out2 + o) = make_int4(ow2_[0], ow2_[1], ow2_[2], ow2_[3]);
+    }
 }
 
 // Epilogue role shared by both kernels.  Warps 2..9: warp w reads TMEM lanes
@@ -373,11 +392,13 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
                                                  uint32_t remote_acc_empty /* 0: local barrier */)
 {
     const int q = warp & 3;
-    const int half = (warp - 2) >> 2;                     // column group of this warp
-    constexpr int CHUNKS = BN / 32;                       // 2, 4 or 8
+    const int cg = (warp - 2) >> 2;                       // column group of this warp
+    // chunk width: 32 columns, or 16 for the narrow (BN = 64) tiles so all column groups have work
+    constexpr int CW = (BN / 32 >= TC_EPI_COLGROUPS) ? 32 : 16;
+    constexpr int CHUNKS = BN / CW;
     constexpr int GROUPS = CHUNKS < TC_EPI_COLGROUPS ? CHUNKS : TC_EPI_COLGROUPS;
     constexpr int PER = CHUNKS / GROUPS;
-    if (half >= GROUPS) return;                           // narrow tiles: the extra warps have no columns
+    if (cg >= GROUPS) return;
     const int row = q * 32 + lane;
     const int iw = row % p.TW;
     const int ih = (row / p.TW) % p.TH;
@@ -401,11 +422,14 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
         const int a = local & 1;
         const uint32_t aphase = (uint32_t)(local >> 1) & 1;
         // the residual operand does not depend on the accumulator: fetch the first chunk's
-        // 32 bytes before waiting for the MMAs, the next chunk's while computing this one
-        int rw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        const size_t o0 = pix * p.Cout + n0 + half * PER * 32;
-        if (has_res && valid && !(p.dbg & 4)) {
-            ld_global_32B(p.res + o0, rw);
+        // bytes before waiting for the MMAs, the next chunk's while computing this one
+        int rw[CW / 4];
+#pragma unroll
+        for (int g = 0; g < CW / 4; g++) rw[g] = 0;
+        const size_t o0 = pix * p.Cout + n0 + cg * PER * CW;
+        if (has_res && valid) {
+            if (CW == 32) { int t8[8]; ld_global_32B(p.res + o0, t8); for (int g = 0; g < CW / 4; g++) rw[g] = t8[g]; }
+            else { const int4 t4 = *(const int4*)(p.res + o0); rw[0] = t4.x; rw[1] = t4.y; rw[2] = t4.z; rw[3] = t4.w; }
         }
         ok = mbar_wait(smem_u32(&sh->acc_full[a]), aphase, abort_flag, p.err, FFCU_ERR_EPI_TIMEOUT);
         if (!ok) break;
@@ -413,24 +437,24 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
         const uint32_t taddr = tmem_base + (uint32_t)(a * BN) + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
         for (int jj = 0; jj < PER; jj++) {
-            const int j = half * PER + jj;
-            int v[32];
-            if (p.dbg & 16) {                       // timing experiment: no TMEM reads
-#pragma unroll
-                for (int i = 0; i < 32; i++) v[i] = i + j;
-            } else
-            tmem_ld32(taddr + (uint32_t)(j * 32), v);
+            const int j = cg * PER + jj;
+            int v[CW];
+            tmem_ld(taddr + (uint32_t)(j * CW), v);
             if (!valid) continue;
-            int rn[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            if (has_res && jj + 1 < PER && !(p.dbg & 4)) {
-                ld_global_32B(p.res + o0 + (size_t)(jj + 1) * 32, rn);
-            }
-            const int cb = n0 + j * 32;
-            tc_epilogue_chunk<CONTRACT, OUT_F32, EPI>(p, tab, lut + (size_t)(j * 32) * 256, v, rw, cb, pix * p.Cout + cb, has_res, has_slope, has_bn2);
+            int rn[CW / 4];
 #pragma unroll
-            for (int g = 0; g < 8; g++) rw[g] = rn[g];
+            for (int g = 0; g < CW / 4; g++) rn[g] = 0;
+            if (has_res && jj + 1 < PER) {
+                if (CW == 32) { int t8[8]; ld_global_32B(p.res + o0 + (size_t)(jj + 1) * CW, t8); for (int g = 0; g < CW / 4; g++) rn[g] = t8[g]; }
+                else { const int4 t4 = *(const int4*)(p.res + o0 + (size_t)(jj + 1) * CW); rn[0] = t4.x; rn[1] = t4.y; rn[2] = t4.z; rn[3] = t4.w; }
+            }
+            const int cb = n0 + j * CW;
+            tc_epilogue_chunk<CONTRACT, OUT_F32, EPI, CW>(p, tab, lut + (size_t)(j * CW) * 256, v, rw, cb, pix * p.Cout + cb,
+                                                          has_res, has_slope, has_bn2);
+#pragma unroll
+            for (int g = 0; g < CW / 4; g++) rw[g] = rn[g];
         }
-        // this warp's TMEM reads are complete (tcgen05.wait::ld inside tmem_ld32)
+        // this warp's TMEM reads are complete (tcgen05.wait::ld inside tmem_ld)
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {

@@ -33,15 +33,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 
     if (warp == 0) {
         const int G = p.group;
-        if (lane < 2 * G) {
-            // TMA producer.  A pipeline stage holds G consecutive K blocks; lane 2g fetches the
+        {
+            // TMA producer.  The whole warp runs the loop (lanes stay converged; a lone lane
+            // looping while its 31 siblings sit at the final barrier was measured slower);
+            // lanes 0 .. 2G-1 issue.  A pipeline stage holds G consecutive K blocks; lane 2g fetches the
             // activation box of block g, lane 2g+1 its weight box, all in ONE instruction (both
             // tensor maps are 4-D).  One barrier hand-shake per stage: the hand-shake, not the copy,
             // is what a single-thread loop pays for, so it is amortised over G blocks.  Each lane
             // carries its own (kh, kw, c0) forward by G blocks per step: no divisions in the loop.
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            const int g = lane >> 1;
+            const bool issuer = lane < 2 * G;
+            const int g = issuer ? (lane >> 1) : 0;
             const bool is_a = (lane & 1) == 0;
             const CUtensorMap* map = is_a ? &mapA : &mapB;
             const uint32_t smem0 = smem_u32(smem) + (uint32_t)(g * SUB_BYTES) + (is_a ? 0u : (uint32_t)A_BYTES);
@@ -66,9 +69,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     if (p.dbg & 1) { if (lane == 0) mbar_arrive(full0 + stage * 8); }
                     else {
                         if (lane == 0) mbar_expect_tx(full0 + stage * 8, G * SUB_BYTES);
-                        __syncwarp((1u << (2 * G)) - 1u);       // the byte count is armed before any copy can land
+                        __syncwarp();                           // the byte count is armed before any copy can land
                         const int tapk = (kh * p.Kw + kw) * p.Cp + c0;
-                        tma_load_4d(smem0 + stage * stage_bytes, map, full0 + stage * 8,
+                        if (issuer) tma_load_4d(smem0 + stage * stage_bytes, map, full0 + stage * 8,
                                     is_a ? c0 : tapk, is_a ? x0 + kw : tn * BN, is_a ? y0 + kh : 0, c3);
                     }
                     c0 += G * KC;
@@ -78,8 +81,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            // MMA issuer
+        {
+            // MMA issuer: the warp loops and waits together, lane 0 issues
             int stage = 0; uint32_t phase = 0;
             int local = 0;
             bool ok = true;
@@ -100,17 +103,21 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     ok = mbar_wait(full0 + stage * 8, phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
                     if (!ok) break;
                     tc_fence_after();
-                    uint64_t soff = (uint64_t)((stage * stage_bytes) >> 4);
-                    if (!(p.dbg & 2))
-                    for (int g = 0; g < G; g++, soff += (uint64_t)(SUB_BYTES >> 4)) {
+                    if (lane == 0) {
+                        uint64_t soff = (uint64_t)((stage * stage_bytes) >> 4);
+                        if (!(p.dbg & 2))
+                        for (int g = 0; g < G; g++, soff += (uint64_t)(SUB_BYTES >> 4)) {
 #pragma unroll
-                        for (int k = 0; k < KC / 32; k++)
-                            umma_i8(d_tmem, da0 + soff + (uint64_t)(2 * k), db0 + soff + (uint64_t)(2 * k), IDESC, (it | g | k) ? 1u : 0u);
+                            for (int k = 0; k < KC / 32; k++)
+                                umma_i8(d_tmem, da0 + soff + (uint64_t)(2 * k), db0 + soff + (uint64_t)(2 * k), IDESC, (it | g | k) ? 1u : 0u);
+                        }
+                        umma_commit(empty0 + stage * 8);   // frees the stage once these MMAs have read it
                     }
-                    umma_commit(empty0 + stage * 8);   // frees the stage once these MMAs have read it
+                    __syncwarp();
                     if (++stage == p.stages) { stage = 0; phase ^= 1; }
                 }
-                if (ok) umma_commit(smem_u32(&sh->acc_full[a]));
+                if (ok && lane == 0) umma_commit(smem_u32(&sh->acc_full[a]));
+                __syncwarp();
             }
         }
     } else {

@@ -42,11 +42,12 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     volatile int* abort_flag = &sh->abort_flag;
 
     if (warp == 0) {
-        if (lane == 0) {
+        {
+            // the warp loops and waits together (lanes stay converged); lanes 0..2 issue one box each
             const uint32_t wbar = smem_u32(&sh->w_full);
-            mbar_expect_tx(wbar, W_BYTES);
-            for (int tap = 0; tap < 9; tap++)
-                tma_load_4d(smem_u32(s_w + tap * W_TAP_BYTES), &mapB, wbar, tap * p.Cp, 0, 0, 0);
+            if (lane == 0) mbar_expect_tx(wbar, W_BYTES);
+            __syncwarp();
+            if (lane < 9) tma_load_4d(smem_u32(s_w + lane * W_TAP_BYTES), &mapB, wbar, lane * p.Cp, 0, 0, 0);
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
@@ -58,14 +59,15 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 if (!ok) break;
                 const uint32_t bar = smem_u32(&sh->full[stage]);
                 const uint32_t sa = smem_u32(s_a + (size_t)stage * WS_A_BYTES);
-                mbar_expect_tx(bar, WS_A_BYTES);
-                for (int kw = 0; kw < 3; kw++)
-                    tma_load_4d(sa + kw * (WS_BOX_ROWS * 64), &mapA, bar, 0, tw * WS_TW + kw - 1, th * WS_TH - 1, b);
+                if (lane == 0) mbar_expect_tx(bar, WS_A_BYTES);
+                __syncwarp();
+                if (lane < 3) tma_load_4d(sa + lane * (WS_BOX_ROWS * 64), &mapA, bar, 0, tw * WS_TW + lane - 1, th * WS_TH - 1, b);
                 if (++stage == p.stages) { stage = 0; phase ^= 1; }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        {
+            // MMA issuer: the warp loops and waits together, lane 0 issues
             bool ok = mbar_wait(smem_u32(&sh->w_full), 0, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
             tc_fence_after();
             int stage = 0; uint32_t phase = 0;
@@ -81,6 +83,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
                 const uint64_t da0 = smem_desc<KC>(smem_u32(s_a + (size_t)stage * WS_A_BYTES));
+                if (lane == 0) {
 #pragma unroll
                 for (int kw = 0; kw < 3; kw++)
 #pragma unroll
@@ -94,6 +97,8 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     }
                 umma_commit(smem_u32(&sh->empty[stage]));
                 umma_commit(smem_u32(&sh->acc_full[a]));
+                }
+                __syncwarp();
                 if (++stage == p.stages) { stage = 0; phase ^= 1; }
             }
         }
