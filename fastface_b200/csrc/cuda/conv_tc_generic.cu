@@ -10,7 +10,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 {
     extern __shared__ uint8_t smem_raw[];
     // stage ring must start on a 1024-byte boundary (swizzle atoms)
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // round up to 1024 bytes by pointer arithmetic on the __shared__ array (an integer round-trip
+    // would hide the address space from the compiler and turn every table read into a generic load)
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     constexpr int A_BYTES = TC_TILE_M * KC;
     constexpr int B_BYTES = BN * KC;
     constexpr int SUB_BYTES = A_BYTES + B_BYTES;          // one K block: [A 128 x KC | B BN x KC]

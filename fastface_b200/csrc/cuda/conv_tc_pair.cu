@@ -20,7 +20,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
 {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // round up to 1024 bytes by pointer arithmetic on the __shared__ array (an integer round-trip
+    // would hide the address space from the compiler and turn every table read into a generic load)
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     constexpr int KC = 128;
     constexpr int A_BYTES = TC_TILE_M * KC;
     constexpr int B_BYTES = (BN / 2) * KC;

@@ -19,7 +19,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
 {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // round up to 1024 bytes by pointer arithmetic on the __shared__ array (an integer round-trip
+    // would hide the address space from the compiler and turn every table read into a generic load)
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     constexpr int KC = 64;
     constexpr int W_TAP_BYTES = BN * KC;
     constexpr int W_BYTES = 9 * W_TAP_BYTES;
@@ -59,6 +61,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 if (!ok) break;
                 const uint32_t bar = smem_u32(&sh->full[stage]);
                 const uint32_t sa = smem_u32(s_a + (size_t)stage * WS_A_BYTES);
+                if (p.dbg & 1) { if (lane == 0) mbar_arrive(bar); if (++stage == p.stages) { stage = 0; phase ^= 1; } continue; }
                 if (lane == 0) mbar_expect_tx(bar, WS_A_BYTES);
                 __syncwarp();
                 if (lane < 3) tma_load_4d(sa + lane * (WS_BOX_ROWS * 64), &mapA, bar, 0, tw * WS_TW + lane - 1, th * WS_TH - 1, b);
@@ -84,6 +87,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
                 const uint64_t da0 = smem_desc<KC>(smem_u32(s_a + (size_t)stage * WS_A_BYTES));
                 if (lane == 0) {
+                if (!(p.dbg & 2))
 #pragma unroll
                 for (int kw = 0; kw < 3; kw++)
 #pragma unroll

@@ -8,7 +8,9 @@ template <int BN>
 __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int* err)
 {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // round up to 1024 bytes by pointer arithmetic on the __shared__ array (an integer round-trip
+    // would hide the address space from the compiler and turn every table read into a generic load)
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     __shared__ uint64_t done_bar;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
