@@ -203,7 +203,7 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
         prm.TW = WS_TW; prm.TH = WS_TH; prm.TB = 1;
         prm.tiles_w = d.Wo / WS_TW; prm.tiles_h = (d.Ho + WS_TH - 1) / WS_TH; prm.tiles_b = batch; prm.tiles_n = 1;
         prm.total_tiles = prm.tiles_w * prm.tiles_h * batch;
-        prm.stages = p->ws_stages; prm.group = 1; prm.dbg = 0; prm.lut_bytes = p->lut_bytes;
+        prm.stages = p->ws_stages; prm.group = 1; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes;
         int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
         return tc_launch_ws(p->BN, mode, epi, grid, p->ws_smem_bytes, s, p->mapA_ws, p->mapB, prm);
     }

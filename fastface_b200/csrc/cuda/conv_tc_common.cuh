@@ -260,6 +260,11 @@ enum { EPI_RUNTIME = 0, EPI_PLAIN = 1, EPI_SLOPE = 2, EPI_RES_BN = 3, EPI_RES = 
 #define TC_EPI_WARPS 8     // warps 2..9: two per TMEM lane quarter, each takes half the columns (16 warps, with 16-column chunks for the narrow tiles, measured no faster: the epilogue is issue-bound, not latency-bound)
 #endif
 #define TC_EPI_COLGROUPS (TC_EPI_WARPS / 4)
+// Accumulator ring in TMEM: 512 columns hold 512 / BN tiles.  With short K loops (the
+// 64-channel layers) a tile's MMAs take less time than the hand-shake round trip to the
+// epilogue warps and back, so the issuer must be able to run several tiles ahead.
+#define TC_MAX_ACC 8
+#define TC_NACC(BN) (512 / (BN) > TC_MAX_ACC ? TC_MAX_ACC : 512 / (BN))
 // epilogue warps that actually have columns to process for a BN-wide tile (a chunk is 32 columns)
 #define TC_EPI_ACTIVE(BN) (4 * ((BN) / 16 < TC_EPI_COLGROUPS ? (BN) / 16 : TC_EPI_COLGROUPS))
 #define TC_THREADS (32 * (2 + TC_EPI_WARPS))
@@ -267,8 +272,8 @@ enum { EPI_RUNTIME = 0, EPI_PLAIN = 1, EPI_SLOPE = 2, EPI_RES_BN = 3, EPI_RES = 
 struct TcShared {                 // lives after the stage ring and the tables
     uint64_t full[TC_MAX_STAGES];
     uint64_t empty[TC_MAX_STAGES];
-    uint64_t acc_full[2];
-    uint64_t acc_empty[2];
+    uint64_t acc_full[TC_MAX_ACC];
+    uint64_t acc_empty[TC_MAX_ACC];
     uint64_t w_full;              // weight-stationary kernel: weights have landed
     uint32_t tmem_base;
     int abort_flag;
@@ -420,8 +425,8 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
         const bool valid = (ow < p.Wo) && (oh < p.Ho) && (b < p.batch);
         const size_t pix = ((size_t)b * p.Ho + oh) * p.Wo + ow;
         const int n0 = tn * BN;
-        const int a = local & 1;
-        const uint32_t aphase = (uint32_t)(local >> 1) & 1;
+        const int a = local % TC_NACC(BN);
+        const uint32_t aphase = (uint32_t)(local / TC_NACC(BN)) & 1;
         // the residual operand does not depend on the accumulator: fetch the first chunk's
         // bytes before waiting for the MMAs, the next chunk's while computing this one
         int rw[CW / 4];
@@ -476,7 +481,7 @@ __device__ __forceinline__ void tc_setup(TcShared* sh, int stages, uint32_t tmem
 {
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; s++) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), 1); }
-        for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&sh->acc_full[a]), 1); mbar_init(smem_u32(&sh->acc_empty[a]), epi_active); }
+        for (int a = 0; a < TC_MAX_ACC; a++) { mbar_init(smem_u32(&sh->acc_full[a]), 1); mbar_init(smem_u32(&sh->acc_empty[a]), epi_active); }
         mbar_init(smem_u32(&sh->w_full), 1);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

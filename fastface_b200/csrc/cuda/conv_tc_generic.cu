@@ -16,7 +16,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     constexpr int A_BYTES = TC_TILE_M * KC;
     constexpr int B_BYTES = BN * KC;
     constexpr int SUB_BYTES = A_BYTES + B_BYTES;          // one K block: [A 128 x KC | B BN x KC]
-    constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;    // 128 / 256 / 512: powers of two
+    constexpr uint32_t TMEM_COLS = TC_NACC(BN) * BN;        // the whole accumulator ring: 512 columns
     constexpr uint32_t IDESC = idesc_i8(BN);
 
     float* tab = (float*)(smem + (size_t)p.stages * p.group * SUB_BYTES);       // [TC_NTAB][TC_MAX_COUT]
@@ -95,8 +95,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             const uint64_t da0 = smem_desc<KC>(smem_u32(smem));
             const uint64_t db0 = smem_desc<KC>(smem_u32(smem) + A_BYTES);
             for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, local++) {
-                const int a = local & 1;
-                const uint32_t aphase = (uint32_t)(local >> 1) & 1;
+                const int a = local % TC_NACC(BN);
+                const uint32_t aphase = (uint32_t)(local / TC_NACC(BN)) & 1;
                 ok = mbar_wait(smem_u32(&sh->acc_empty[a]), aphase ^ 1, abort_flag, p.err, FFCU_ERR_TMEM_TIMEOUT);
                 if (!ok) break;
                 tc_fence_after();

@@ -27,7 +27,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     constexpr int A_BYTES = TC_TILE_M * KC;
     constexpr int B_BYTES = (BN / 2) * KC;
     constexpr int SUB_BYTES = A_BYTES + B_BYTES;          // one K block: [A 128 x 128 | B-half BN/2 x 128]
-    constexpr uint32_t TMEM_COLS = 2 * BN;
+    constexpr uint32_t TMEM_COLS = TC_NACC(BN) * BN;
     constexpr uint32_t IDESC = idesc_i8(BN, 256);
 
     float* tab = (float*)(smem + (size_t)p.stages * p.group * SUB_BYTES);
@@ -46,7 +46,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     tc_load_lut(lut, p, (int)(pair_id % p.tiles_n) * BN, BN);
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; s++) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), 1); }
-        for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&sh->acc_full[a]), 1); mbar_init(smem_u32(&sh->acc_empty[a]), 2 * TC_EPI_ACTIVE(BN)); }
+        for (int a = 0; a < TC_MAX_ACC; a++) { mbar_init(smem_u32(&sh->acc_full[a]), 1); mbar_init(smem_u32(&sh->acc_empty[a]), 2 * TC_EPI_ACTIVE(BN)); }
         mbar_init(smem_u32(&sh->w_full), 1);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -126,8 +126,8 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             const uint64_t da0 = smem_desc<KC>(smem_u32(smem));
             const uint64_t db0 = smem_desc<KC>(smem_u32(smem) + A_BYTES);
             for (int tile = pair_id; tile < total && ok; tile += n_pairs, local++) {
-                const int a = local & 1;
-                const uint32_t aphase = (uint32_t)(local >> 1) & 1;
+                const int a = local % TC_NACC(BN);
+                const uint32_t aphase = (uint32_t)(local / TC_NACC(BN)) & 1;
                 ok = mbar_wait_cluster(smem_u32(&sh->acc_empty[a]), aphase ^ 1, abort_flag, p.err, FFCU_ERR_TMEM_TIMEOUT);
                 if (!ok) break;
                 tc_fence_after();

@@ -25,7 +25,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     constexpr int KC = 64;
     constexpr int W_TAP_BYTES = BN * KC;
     constexpr int W_BYTES = 9 * W_TAP_BYTES;
-    constexpr uint32_t TMEM_COLS = 2 * BN;
+    constexpr uint32_t TMEM_COLS = TC_NACC(BN) * BN;
     constexpr uint32_t IDESC = idesc_i8(BN);
 
     uint8_t* s_w = smem;                                        // [9][BN][64]
@@ -77,8 +77,8 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             int local = 0;
             const uint64_t dw = smem_desc<KC>(smem_u32(s_w));
             for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, local++) {
-                const int a = local & 1;
-                const uint32_t aphase = (uint32_t)(local >> 1) & 1;
+                const int a = local % TC_NACC(BN);
+                const uint32_t aphase = (uint32_t)(local / TC_NACC(BN)) & 1;
                 ok = mbar_wait(smem_u32(&sh->acc_empty[a]), aphase ^ 1, abort_flag, p.err, FFCU_ERR_TMEM_TIMEOUT);
                 if (!ok) break;
                 ok = mbar_wait(smem_u32(&sh->full[stage]), phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
