@@ -317,7 +317,7 @@ __device__ __forceinline__ void ld_global_32B(const void* ptr, int (&w)[8])
 // (= pixel * Cout + first channel cb).  Replaces fused_epilogue_int8 for those 32 values
 // (reference kernels/int8_epilogue.c:25-112), optionally followed by the next BN pass
 // (:253-318) as a second output.
-template <bool CONTRACT, bool OUT_F32, int EPI, int CW>
+template <bool CONTRACT, bool OUT_F32, int EPI, int CW, bool CHECK>
 __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float* tab, const uint8_t* lutc,
                                                   const int (&v)[CW], const int (&rw)[CW / 4], int cb, size_t o,
                                                   bool rt_res, bool rt_slope, bool rt_bn2)
@@ -361,8 +361,8 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
         float f1 = ffcu_conv_fp<CONTRACT>(v[4 * g + 1], ws.y, bi.y, has_res, (int)(int8_t)((r >> 8) & 0xff), rs.y, has_slope, sl.y);
         float f2 = ffcu_conv_fp<CONTRACT>(v[4 * g + 2], ws.z, bi.z, has_res, (int)(int8_t)((r >> 16) & 0xff), rs.z, has_slope, sl.z);
         float f3 = ffcu_conv_fp<CONTRACT>(v[4 * g + 3], ws.w, bi.w, has_res, (int)(int8_t)((r >> 24) & 0xff), rs.w, has_slope, sl.w);
-        int q0 = ffcu_requant_nosat(f0, iv.x), q1 = ffcu_requant_nosat(f1, iv.y);
-        int q2 = ffcu_requant_nosat(f2, iv.z), q3 = ffcu_requant_nosat(f3, iv.w);
+        int q0 = ffcu_requant_nosat<CHECK>(f0, iv.x), q1 = ffcu_requant_nosat<CHECK>(f1, iv.y);
+        int q2 = ffcu_requant_nosat<CHECK>(f2, iv.z), q3 = ffcu_requant_nosat<CHECK>(f3, iv.w);
         ow_[g] = ffcu_pack4(q0, q1, q2, q3);
         if (has_bn2) {
             // BN of the four int8 results just packed: one table row per channel, indexed by the byte
@@ -387,6 +387,29 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
         *(int4*)((int8_t*)p.out + o) = make_int4(ow_[0], ow_[1], ow_[2], ow_[3]);
         if (has_bn2) *(int4*)(p.out2 + o) = make_int4(ow2_[0], ow2_[1], ow2_[2], ow2_[3]);
     }
+}
+
+// Tile walk.  A CTA visits tiles first, first + step, ...; the launchers keep step a multiple of
+// tiles_n, so the column tile never changes and the row-tile index m advances by a constant.
+// Its (w, h, batch) digits are carried forward with two compare-and-carry steps per tile: the
+// three divisions a fresh decomposition costs are a third of a small tile's epilogue.
+struct TileWalk { int tw, th, tb, dw, dh, db; };
+__device__ __forceinline__ void walk_init(TileWalk& w, const TcParams& p, int first_m, int step_m)
+{
+    int m = first_m;
+    w.tw = m % p.tiles_w; m /= p.tiles_w; w.th = m % p.tiles_h; w.tb = m / p.tiles_h;
+    m = step_m;
+    w.dw = m % p.tiles_w; m /= p.tiles_w; w.dh = m % p.tiles_h; w.db = m / p.tiles_h;
+}
+__device__ __forceinline__ void walk_next(TileWalk& w, const TcParams& p)
+{
+    w.tw += w.dw;
+    int c = (w.tw >= p.tiles_w) ? 1 : 0;
+    w.tw -= c ? p.tiles_w : 0;
+    w.th += w.dh + c;
+    c = (w.th >= p.tiles_h) ? 1 : 0;
+    w.th -= c ? p.tiles_h : 0;
+    w.tb += w.db + c;
 }
 
 // Epilogue role shared by both kernels.  Warps 2..9: warp w reads TMEM lanes
@@ -415,12 +438,11 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
     const bool has_bn2 = p.out2 != nullptr;
     int local = 0;
     bool ok = true;
-    for (int tile = first; tile < total && ok; tile += step, local++) {
-        const int tn = tile % p.tiles_n;
-        int m = (tile / p.tiles_n) * m_mul + m_off;
-        const int tw = m % p.tiles_w; m /= p.tiles_w;
-        const int th = m % p.tiles_h;
-        const int tb = m / p.tiles_h;
+    const int tn = first % p.tiles_n;
+    TileWalk wk;
+    walk_init(wk, p, (first / p.tiles_n) * m_mul + m_off, (step / p.tiles_n) * m_mul);
+    for (int tile = first; tile < total && ok; tile += step, local++, walk_next(wk, p)) {
+        const int tw = wk.tw, th = wk.th, tb = wk.tb;
         const int ow = tw * p.TW + iw, oh = th * p.TH + ih, b = tb * p.TB + ib;
         const bool valid = (ow < p.Wo) && (oh < p.Ho) && (b < p.batch);
         const size_t pix = ((size_t)b * p.Ho + oh) * p.Wo + ow;
@@ -462,8 +484,12 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
                 else { const int4 t4 = *(const int4*)(p.res + o0 + (size_t)(jj + 1) * CW); rn[0] = t4.x; rn[1] = t4.y; rn[2] = t4.z; rn[3] = t4.w; }
             }
             const int cb = n0 + j * CW;
-            tc_epilogue_chunk<CONTRACT, OUT_F32, EPI, CW>(p, tab, lut + (size_t)(j * CW) * 256, v, rw, cb, pix * p.Cout + cb,
-                                                          has_res, has_slope, has_bn2);
+            if (p.t.no_overflow)
+                tc_epilogue_chunk<CONTRACT, OUT_F32, EPI, CW, false>(p, tab, lut + (size_t)(j * CW) * 256, v, rw, cb, pix * p.Cout + cb,
+                                                                     has_res, has_slope, has_bn2);
+            else
+                tc_epilogue_chunk<CONTRACT, OUT_F32, EPI, CW, true>(p, tab, lut + (size_t)(j * CW) * 256, v, rw, cb, pix * p.Cout + cb,
+                                                                    has_res, has_slope, has_bn2);
 #pragma unroll
             for (int g = 0; g < CW / 4; g++) rw[g] = rn[g];
         }

@@ -53,12 +53,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
             const int stage_bytes = G * SUB_BYTES;
             const int n_steps = kblocks / G;
-            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-                const int tn = tile % p.tiles_n;
-                int m = tile / p.tiles_n;
-                const int tw = m % p.tiles_w; m /= p.tiles_w;
-                const int th = m % p.tiles_h;
-                const int tb = m / p.tiles_h;                   // may be past the batch: TMA zero-fills
+            const int tn = blockIdx.x % p.tiles_n;
+            TileWalk wk;
+            walk_init(wk, p, blockIdx.x / p.tiles_n, gridDim.x / p.tiles_n);
+            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, walk_next(wk, p)) {
+                const int tw = wk.tw, th = wk.th, tb = wk.tb;   // tb may be past the batch: TMA zero-fills
                 const int x0 = tw * p.TW * p.stride - p.pad;
                 const int y0 = th * p.TH * p.stride - p.pad;
                 const int c3 = is_a ? tb * p.TB : 0;

@@ -84,12 +84,11 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             const uint32_t full0_leader = map_to_cta(full0, 0);
             const int stage_bytes = G * SUB_BYTES;
             const int n_steps = kblocks / G;
-            for (int tile = pair_id; tile < total && ok; tile += n_pairs) {
-                const int tn = tile % p.tiles_n;
-                int m = (tile / p.tiles_n) * 2 + (int)rank;
-                const int tw = m % p.tiles_w; m /= p.tiles_w;
-                const int th = m % p.tiles_h;
-                const int tb = m / p.tiles_h;                   // may be past the batch: TMA zero-fills
+            const int tn = pair_id % p.tiles_n;
+            TileWalk wk;
+            walk_init(wk, p, (pair_id / p.tiles_n) * 2 + (int)rank, (n_pairs / p.tiles_n) * 2);
+            for (int tile = pair_id; tile < total && ok; tile += n_pairs, walk_next(wk, p)) {
+                const int tw = wk.tw, th = wk.th, tb = wk.tb;   // tb may be past the batch: TMA zero-fills
                 const int x0 = tw * p.TW * p.stride - p.pad;
                 const int y0 = th * p.TH * p.stride - p.pad;
                 const int c3 = is_a ? tb * p.TB : 0;

@@ -52,11 +52,10 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             if (lane < 9) tma_load_4d(smem_u32(s_w + lane * W_TAP_BYTES), &mapB, wbar, lane * p.Cp, 0, 0, 0);
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-                int m = tile;
-                const int tw = m % p.tiles_w; m /= p.tiles_w;
-                const int th = m % p.tiles_h;
-                const int b = m / p.tiles_h;
+            TileWalk wk;
+            walk_init(wk, p, blockIdx.x, gridDim.x);
+            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, walk_next(wk, p)) {
+                const int tw = wk.tw, th = wk.th, b = wk.tb;
                 ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, p.err, FFCU_ERR_EMPTY_TIMEOUT);
                 if (!ok) break;
                 const uint32_t bar = smem_u32(&sh->full[stage]);

@@ -2,6 +2,7 @@
 // launch list, submit / wait, dump points and the resident-input timing loop.
 
 #include "ffcu_internal.cuh"
+#include <math.h>
 
 #include <stdarg.h>
 #include <stdio.h>
@@ -154,6 +155,28 @@ extern "C" void ffcu_destroy(ffcu_ctx* c)
     delete c;
 }
 
+// True when no int8 input can drive the requantised value of this conv layer near the range
+// of a 32-bit integer: |acc| <= 128 * sum|w|, so per channel
+//   |t| <= (128 * sum|w| * |w_scale| + |bias| + 128 * |res_scale|) * max(1, |slope|)
+// and the converted value is at most |t| * |inv_out| + 0.5.  The bound is evaluated in double
+// and compared with 2^30, a factor two inside the limit to cover the fp32 roundings.
+static bool epilogue_cannot_overflow(const ffcu_layer* l)
+{
+    if (l->kind != FFCU_CONV || !l->w || !l->w_scale || !l->bias || !l->inv_out || l->Cout < 1) return false;
+    const size_t K = l->w_bytes / (size_t)l->Cout;
+    for (int c = 0; c < l->Cout; c++) {
+        double s = 0.0;
+        const int8_t* wr = l->w + (size_t)c * K;
+        for (size_t k = 0; k < K; k++) s += fabs((double)wr[k]);
+        double t = 128.0 * s * fabs((double)l->w_scale[c]) + fabs((double)l->bias[c]);
+        if (l->res_scale) t += 128.0 * fabs((double)l->res_scale[c]);
+        if (l->slope) { const double a = fabs((double)l->slope[c]); if (a > 1.0) t *= a; if (!(a == a)) return false; }
+        const double q = t * fabs((double)l->inv_out[c]) + 1.0;
+        if (!(q < 1073741824.0)) return false;            // also rejects NaN / inf
+    }
+    return true;
+}
+
 extern "C" int ffcu_add_layer(ffcu_ctx* c, const ffcu_layer* l)
 {
     if (!c || !l || c->finalized) { ffcu_set_error("ffcu_add_layer: bad state"); return -1; }
@@ -189,6 +212,7 @@ extern "C" int ffcu_add_layer(ffcu_ctx* c, const ffcu_layer* l)
         cudaMemcpy(L.bn_lut, lut.data(), lut.size(), cudaMemcpyHostToDevice);
     }
     L.epi.bn_lut = L.bn_lut;
+    L.epi.no_overflow = epilogue_cannot_overflow(l) ? 1 : 0;
     L.d.bn2_lut = nullptr;
     L.d.bn2_in_scale = L.d.bn2_scale = L.d.bn2_offset = L.d.bn2_inv_out = nullptr;
     L.d.w = nullptr;

@@ -44,6 +44,10 @@ struct EpiTables {
     const float* bn_offset;
     const float* bn_inv;
     const int8_t* bn_lut;    // [Cout][256]: BN of every int8 value (ff_bn_lut_build), or NULL
+    // 1 when the host has proved, from the weights and tables, that |t * inv + 0.5| stays far
+    // below 2^31 for every int8 input: the kernels then skip the per-element emulation of
+    // x86's out-of-range conversion result (it cannot trigger).
+    int no_overflow;
 };
 
 // ---------------------------------------------------------------------------
@@ -65,13 +69,15 @@ __device__ __forceinline__ int ffcu_requant(float t, float inv)
 }
 
 // Same rounding as ffcu_requant, but the clamp is left to the caller (ffcu_pack4 saturates).
+// CHECK = false is for layers whose EpiTables::no_overflow is set.
+template <bool CHECK = true>
 __device__ __forceinline__ int ffcu_requant_nosat(float t, float inv)
 {
     float q = __fmul_rn(t, inv);
     float half = __int_as_float(0x3f000000 | (__float_as_int(q) & 0x80000000));
     float r = __fadd_rn(q, half);
     int i = __float2int_rz(r);
-    if (!(fabsf(r) < 2147483648.0f)) i = INT_MIN;
+    if (CHECK) { if (!(fabsf(r) < 2147483648.0f)) i = INT_MIN; }
     return i;
 }
 

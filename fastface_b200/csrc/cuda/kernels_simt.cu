@@ -251,7 +251,7 @@ int ffcu_launch_fc_simt(const int8_t* act, const int8_t* w, const float* w_scale
 // shared memory, weights ([tap][co] words) and the per-channel tables sit there too.
 // ---------------------------------------------------------------------------
 #define STEM_T 16
-template <bool CONTRACT, bool HAS_SLOPE, bool HAS_BN2>
+template <bool CONTRACT, bool HAS_SLOPE, bool HAS_BN2, bool CHECK>
 __global__ void __launch_bounds__(256) stem_kernel(const float* __restrict__ in, const float* __restrict__ inv3,
                                                    const int8_t* __restrict__ w, EpiTables t,
                                                    int8_t* __restrict__ out, int8_t* __restrict__ out2,
@@ -317,11 +317,11 @@ __global__ void __launch_bounds__(256) stem_kernel(const float* __restrict__ in,
             const float4 bi = *(const float4*)&s_tab[1 * C + co];
             const float4 sl = *(const float4*)&s_tab[2 * C + co];
             const float4 iv = *(const float4*)&s_tab[3 * C + co];
-            int q0 = ffcu_requant(ffcu_conv_fp<CONTRACT>(acc0, ws.x, bi.x, false, 0, 0.0f, has_slope, sl.x), iv.x);
-            int q1 = ffcu_requant(ffcu_conv_fp<CONTRACT>(acc1, ws.y, bi.y, false, 0, 0.0f, has_slope, sl.y), iv.y);
-            int q2 = ffcu_requant(ffcu_conv_fp<CONTRACT>(acc2, ws.z, bi.z, false, 0, 0.0f, has_slope, sl.z), iv.z);
-            int q3 = ffcu_requant(ffcu_conv_fp<CONTRACT>(acc3, ws.w, bi.w, false, 0, 0.0f, has_slope, sl.w), iv.w);
-            wo[g] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
+            int q0 = ffcu_requant_nosat<CHECK>(ffcu_conv_fp<CONTRACT>(acc0, ws.x, bi.x, false, 0, 0.0f, has_slope, sl.x), iv.x);
+            int q1 = ffcu_requant_nosat<CHECK>(ffcu_conv_fp<CONTRACT>(acc1, ws.y, bi.y, false, 0, 0.0f, has_slope, sl.y), iv.y);
+            int q2 = ffcu_requant_nosat<CHECK>(ffcu_conv_fp<CONTRACT>(acc2, ws.z, bi.z, false, 0, 0.0f, has_slope, sl.z), iv.z);
+            int q3 = ffcu_requant_nosat<CHECK>(ffcu_conv_fp<CONTRACT>(acc3, ws.w, bi.w, false, 0, 0.0f, has_slope, sl.w), iv.w);
+            wo[g] = ffcu_pack4(q0, q1, q2, q3);              // saturates to [-128, 127]
             if (has_bn2) {
                 const uint8_t* lc = s_lut + co * 256;
                 const unsigned w4 = (unsigned)wo[g];
@@ -340,7 +340,9 @@ int ffcu_launch_stem(const float* in_f32, const float* inv3, const int8_t* w, co
 {
     dim3 grid(112 / STEM_T, 112 / STEM_T, batch);
     const bool sl = t.slope != nullptr, bn = (out_bn2 != nullptr) && (t.bn_lut != nullptr);
-#define STEM_GO(C_, S_, B_) stem_kernel<C_, S_, B_><<<grid, 256, 0, s>>>(in_f32, inv3, w, t, out, out_bn2, (int*)q_out)
+#define STEM_GO(C_, S_, B_) do { \
+        if (t.no_overflow) stem_kernel<C_, S_, B_, false><<<grid, 256, 0, s>>>(in_f32, inv3, w, t, out, out_bn2, (int*)q_out); \
+        else               stem_kernel<C_, S_, B_, true><<<grid, 256, 0, s>>>(in_f32, inv3, w, t, out, out_bn2, (int*)q_out); } while (0)
     if (mode) {
         if (sl && bn) STEM_GO(true, true, true); else if (sl) STEM_GO(true, true, false);
         else if (bn) STEM_GO(true, false, true); else STEM_GO(true, false, false);
