@@ -535,6 +535,7 @@ extern "C" int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mo
         FFCU_CHECK(cudaMemcpy(d_lut, lut.data(), lut.size(), cudaMemcpyHostToDevice));
     }
     EpiTables t{tab[0], tab[1], tab[2], tab[3], tab[4], tab[5], tab[6], tab[7], tab[8], d_lut};
+    t.no_overflow = epilogue_cannot_overflow(l) ? 1 : 0;
     cudaStream_t s; FFCU_CHECK(cudaStreamCreate(&s));
     int rc = 0;
     if (impl == 0) {

@@ -111,6 +111,25 @@ def test_single_layer_vs_oracle(built_lib, case, impl):
         assert not msg, msg
 
 
+@pytest.mark.parametrize("impl", ["tc", "simt"])
+def test_requant_out_of_range_matches_x86_conversion(built_lib, impl):
+    """With a requant scale so large that t * inv leaves the int32 range, the reference's
+    cvttps2dq yields INT_MIN (-> -128) for both signs (kernels/int8_epilogue.c:80-87).  The
+    library may only take its unchecked conversion path when the weights and tables prove
+    that cannot happen; here it can, so the checked path must reproduce the reference bytes."""
+    rng = np.random.default_rng(77)
+    L = random_layer(rng, 2, 56, 64, 64, 3, 1, True, False)
+    inv = L["inv"].copy()
+    inv[::2] = np.float32(3e10)                      # every other channel overflows for most pixels
+    for mode in (ff.EPILOGUE_CONTRACT, ff.EPILOGUE_STRICT):
+        acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], inv, stride=1, pad=L["pad"],
+                                slope=L["slope"], mode=mode, impl=impl)
+        acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], inv, 1, L["pad"], L["slope"], None, None, mode)
+        assert (out_o[..., ::2] == -128).mean() > 0.7        # the case does exercise the overflow
+        msg = describe_mismatch(f"int8 output (mode {mode})", out, out_o)
+        assert not msg, msg
+
+
 @pytest.mark.parametrize("case", [LAYER_CASES[0], LAYER_CASES[2], LAYER_CASES[4], LAYER_CASES[6], LAYER_CASES[8], LAYER_CASES[14]],
                          ids=lambda c: c[0])
 @pytest.mark.parametrize("impl", ["tc", "simt"])
