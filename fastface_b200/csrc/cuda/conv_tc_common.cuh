@@ -151,9 +151,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank)
 {
     uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank)); return r;
 }
+// Remote arrive on the leader CTA's barrier.  Relaxed: what the arrive publishes is "this
+// warp's tcgen05.ld reads have completed" (tcgen05.wait::ld has returned and
+// tcgen05.fence::before_thread_sync precedes the arrive); a release at cluster scope would also
+// wait for the warp's global stores to drain, which nobody on the other side reads.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
 {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void cluster_sync_all()
 {
