@@ -52,6 +52,11 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrive that publishes nothing but "my tcgen05.ld reads are done" (see mbar_arrive_cluster).
+__device__ __forceinline__ void mbar_arrive_relaxed(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
 {
     uint32_t ok;
@@ -502,7 +507,7 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
         __syncwarp();
         if (lane == 0) {
             if (remote_acc_empty) mbar_arrive_cluster(remote_acc_empty + (uint32_t)(a * 8));
-            else mbar_arrive(smem_u32(&sh->acc_empty[a]));
+            else mbar_arrive_relaxed(smem_u32(&sh->acc_empty[a]));
         }
     }
 }
