@@ -276,7 +276,13 @@ enum { EPI_RUNTIME = 0, EPI_PLAIN = 1, EPI_SLOPE = 2, EPI_RES_BN = 3, EPI_RES = 
 #define TC_NACC(BN) (512 / (BN) > TC_MAX_ACC ? TC_MAX_ACC : 512 / (BN))
 // epilogue warps that actually have columns to process for a BN-wide tile (a chunk is 32 columns)
 #define TC_EPI_ACTIVE(BN) (4 * ((BN) / 16 < TC_EPI_COLGROUPS ? (BN) / 16 : TC_EPI_COLGROUPS))
-#define TC_THREADS (32 * (2 + TC_EPI_WARPS))
+// Epilogue warp sets: set s takes the CTA's tiles s, s + SETS, ... (whole tiles, so a warp's work
+// per tile and the barrier counts stay as with one set, while twice the warps are in flight to
+// cover each other's fixed-latency and TMEM-load stalls).
+#ifndef TC_EPI_SETS
+#define TC_EPI_SETS 2
+#endif
+#define TC_THREADS (32 * (2 + TC_EPI_WARPS * TC_EPI_SETS))
 
 struct TcShared {                 // lives after the stage ring and the tables
     uint64_t full[TC_MAX_STAGES];
@@ -430,7 +436,8 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
                                                  uint32_t remote_acc_empty /* 0: local barrier */)
 {
     const int q = warp & 3;
-    const int cg = (warp - 2) >> 2;                       // column group of this warp
+    const int set = (warp - 2) / TC_EPI_WARPS;            // which of the CTA's tiles this warp takes
+    const int cg = ((warp - 2) % TC_EPI_WARPS) >> 2;      // column group of this warp
     // chunk width: 32 columns, or 16 for the narrow (BN = 64) tiles so all column groups have work
     constexpr int CW = (BN / 32 >= TC_EPI_COLGROUPS) ? 32 : 16;
     constexpr int CHUNKS = BN / CW;
@@ -445,12 +452,14 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
                                               : (EPI == EPI_RES_BN || EPI == EPI_RES);
     const bool has_slope = p.t.slope != nullptr;
     const bool has_bn2 = p.out2 != nullptr;
-    int local = 0;
+    int local = set;
     bool ok = true;
     const int tn = first % p.tiles_n;
+    first += set * step;
+    step *= TC_EPI_SETS;
     TileWalk wk;
     walk_init(wk, p, (first / p.tiles_n) * m_mul + m_off, (step / p.tiles_n) * m_mul);
-    for (int tile = first; tile < total && ok; tile += step, local++, walk_next(wk, p)) {
+    for (int tile = first; tile < total && ok; tile += step, local += TC_EPI_SETS, walk_next(wk, p)) {
         const int tw = wk.tw, th = wk.th, tb = wk.tb;
         const int ow = tw * p.TW + iw, oh = th * p.TH + ih, b = tb * p.TB + ib;
         const bool valid = (ow < p.Wo) && (oh < p.Ho) && (b < p.batch);
