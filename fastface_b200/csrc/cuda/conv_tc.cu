@@ -163,7 +163,7 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
         !(ws_env && ws_env[0] == '0')) {
         cuuint64_t adims[4] = {64, (cuuint64_t)L.W, (cuuint64_t)L.H, (cuuint64_t)max_batch};
         cuuint64_t astr[3] = {64, (cuuint64_t)64 * L.W, (cuuint64_t)64 * L.W * L.H};
-        cuuint32_t abox[4] = {64, WS_TW, WS_TH + 2, 1};
+        cuuint32_t abox[4] = {64, WS_PITCH, WS_TH + 2, 1};
         cuuint32_t aes[4] = {1, 1, 1, 1};
         r = enc(&p->mapA_ws, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d_in, adims, astr, abox, aes,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,

@@ -230,6 +230,18 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr)
     return d;
 }
 
+// Same with an explicit stride between 8-row groups.
+template <int ROWB>
+__device__ __forceinline__ uint64_t smem_desc_sbo(uint32_t saddr, uint32_t sbo_bytes)
+{
+    uint64_t d = (uint64_t)((saddr >> 4) & 0x3fff);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(sbo_bytes >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)(ROWB == 128 ? 2 : 4) << 61;
+    return d;
+}
+
 // kind::i8 instruction descriptor: D=s32, A=B=s8, both K-major, M=128, N=BN.
 __host__ __device__ constexpr uint32_t idesc_i8(int bn, int m = TC_TILE_M)
 {
@@ -569,5 +581,8 @@ int tc_launch_pair(int bn, int mode, int epi, bool f32, int grid, int smem, cuda
 
 #define WS_TW 8
 #define WS_TH 16
-#define WS_BOX_ROWS (WS_TW * (WS_TH + 2))          // 144 rows of 64 B per kw box
-#define WS_A_BYTES (3 * WS_BOX_ROWS * 64)          // 27 648 B per tile
+#ifndef WS_PITCH
+#define WS_PITCH 10                                // pixels per image row of the activation box (>= WS_TW + 2)
+#endif
+#define WS_BOX_ROWS (WS_PITCH * (WS_TH + 2))       // rows of 64 B in the box
+#define WS_A_BYTES ((WS_BOX_ROWS * 64 + 1023) / 1024 * 1024)

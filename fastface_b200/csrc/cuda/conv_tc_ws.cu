@@ -61,9 +61,11 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 const uint32_t bar = smem_u32(&sh->full[stage]);
                 const uint32_t sa = smem_u32(s_a + (size_t)stage * WS_A_BYTES);
                 if (p.dbg & 1) { if (lane == 0) mbar_arrive(bar); if (++stage == p.stages) { stage = 0; phase ^= 1; } continue; }
-                if (lane == 0) mbar_expect_tx(bar, WS_A_BYTES);
+                if (lane == 0) {
+                    mbar_expect_tx(bar, WS_BOX_ROWS * 64);
+                    tma_load_4d(sa, &mapA, bar, 0, tw * WS_TW - 1, th * WS_TH - 1, b);
+                }
                 __syncwarp();
-                if (lane < 3) tma_load_4d(sa + lane * (WS_BOX_ROWS * 64), &mapA, bar, 0, tw * WS_TW + lane - 1, th * WS_TH - 1, b);
                 if (++stage == p.stages) { stage = 0; phase ^= 1; }
             }
         }
@@ -84,7 +86,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
-                const uint64_t da0 = smem_desc<KC>(smem_u32(s_a + (size_t)stage * WS_A_BYTES));
+                const uint64_t da0 = smem_desc_sbo<KC>(smem_u32(s_a + (size_t)stage * WS_A_BYTES), WS_PITCH * 64);
                 if (lane == 0) {
                 if (!(p.dbg & 2))
 #pragma unroll
@@ -92,7 +94,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 #pragma unroll
                     for (int kh = 0; kh < 3; kh++) {
                         // box kw, image rows kh .. kh+15: start = kw * 9216 + kh * 512 bytes (>> 4)
-                        const uint64_t da = da0 + (uint64_t)((kw * WS_BOX_ROWS * 64 + kh * WS_TW * 64) >> 4);
+                        const uint64_t da = da0 + (uint64_t)(((kh * WS_PITCH + kw) * 64) >> 4);
                         const uint64_t db = dw + (uint64_t)(((kh * 3 + kw) * W_TAP_BYTES) >> 4);
 #pragma unroll
                         for (int k = 0; k < 2; k++)
