@@ -39,6 +39,9 @@ struct TcPlan {
     bool pair;               // CTA-pair kernel (cta_group::2) for >= 128 input channels
     CUtensorMap mapB_half;   // box {128, BN/2}
     int pair_stages, pair_smem_bytes;
+    bool shift;              // tap-shift pair kernel (3x3 stride-1, >= 128 input channels, 14x14 / 28x28 maps)
+    CUtensorMap mapA_shift;  // box {128, P, TR + 2, 1}
+    int shift_P, shift_TR, shift_na, shift_a_stride, shift_stages, shift_group, shift_smem_bytes;
     bool ws;                 // weight-stationary kernel (64-channel 3x3 stride-1 layers)
     CUtensorMap mapA_ws;     // box {64, 8, 18, 1}
     int ws_stages, ws_smem_bytes;
@@ -155,6 +158,36 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
             if (st >= 2) { p->pair = true; p->pair_stages = st; p->pair_smem_bytes = st * p->pair_group * sb + fixed; }
         }
     }
+    // tap-shift variant of the pair kernel: the tile's activation patch is fetched once for all nine taps
+    p->shift = false;
+    const char* sh_env = getenv("FF_TC_SHIFT");
+    if (p->pair && L.kind == FFCU_CONV && L.Kh == 3 && L.Kw == 3 && L.stride == 1 && L.pad == 1 && Cp % 128 == 0 &&
+        (L.W == 14 || L.W == 28) && L.H == L.W && !(sh_env && sh_env[0] == '0')) {
+        const int P = (L.W + 1 <= 16) ? 16 : 32, TR = 128 / P;
+        cuuint64_t adims[4] = {(cuuint64_t)Cp, (cuuint64_t)L.W, (cuuint64_t)L.H, (cuuint64_t)max_batch};
+        cuuint64_t astr[3] = {(cuuint64_t)Cp, (cuuint64_t)Cp * L.W, (cuuint64_t)Cp * L.W * L.H};
+        cuuint32_t abox[4] = {128, (cuuint32_t)P, (cuuint32_t)(TR + 2), 1};
+        cuuint32_t aes[4] = {1, 1, 1, 1};
+        r = enc(&p->mapA_shift, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d_in, adims, astr, abox, aes,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r == CUDA_SUCCESS) {
+            const int cb = Cp / 128;
+            // the last taps of the padding positions read up to 2 lines past the box: 8 spare lines
+            const int a_stride = ((P * (TR + 2) + 8) * 128 + 1023) / 1024 * 1024;
+            const int na = cb == 1 ? 2 : (cb + 1 > TC_MAX_ABUF ? TC_MAX_ABUF : cb + 1);
+            const int b_bytes = (p->BN / 2) * 128;
+            const char* ge = getenv("FF_TC_SHIFT_GROUP");
+            const int grp = (ge && atoi(ge) == 1) ? 1 : 3;       // taps per weight stage (a divisor of 9)
+            int st = (232448 - fixed - na * a_stride) / (grp * b_bytes);
+            if (st > TC_MAX_STAGES) st = TC_MAX_STAGES;
+            if (st >= 2) {
+                p->shift = true; p->shift_P = P; p->shift_TR = TR; p->shift_na = na; p->shift_a_stride = a_stride;
+                p->shift_stages = st; p->shift_group = grp;
+                p->shift_smem_bytes = na * a_stride + st * grp * b_bytes + fixed;
+            }
+        }
+    }
     // weight-stationary variant
     p->ws = false;
     const char* ws_env = getenv("FF_TC_WS");
@@ -195,7 +228,7 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
     else if (has_res && has_bn2 && !has_slope) epi = EPI_RES_BN;
     else if (has_res && !has_bn2 && !has_slope) epi = EPI_RES;
     if (p->ws) {
-        TcParams prm;
+        TcParams prm = {};
         prm.t = t; prm.res = res; prm.acc_out = acc_out; prm.out = out; prm.err = d_err;
         prm.out2 = (out_bn2 && t.bn_in) ? out_bn2 : nullptr;
         prm.batch = batch; prm.Ho = d.Ho; prm.Wo = d.Wo; prm.Cout = d.Cout;
@@ -206,6 +239,25 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
         prm.stages = p->ws_stages; prm.group = 1; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes;
         int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
         return tc_launch_ws(p->BN, mode, epi, grid, p->ws_smem_bytes, s, p->mapA_ws, p->mapB, prm);
+    }
+    if (p->shift) {
+        TcParams prm = {};
+        prm.t = t; prm.res = res; prm.acc_out = acc_out; prm.out = out; prm.err = d_err;
+        prm.out2 = (out_bn2 && t.bn_in) ? out_bn2 : nullptr;
+        prm.batch = batch; prm.Ho = d.Ho; prm.Wo = d.Wo; prm.Cout = d.Cout;
+        prm.taps = 9; prm.Kw = 3; prm.Cp = d.Cin_pad; prm.cin_blocks = d.Cin_pad / 128; prm.stride = 1; prm.pad = 1;
+        prm.TW = p->shift_P; prm.TH = p->shift_TR; prm.TB = 1;
+        prm.tiles_w = 1; prm.tiles_h = (d.Ho + p->shift_TR - 1) / p->shift_TR; prm.tiles_b = batch;
+        prm.tiles_n = d.Cout / p->BN;
+        prm.total_tiles = prm.tiles_h * batch * prm.tiles_n;
+        prm.stages = p->shift_stages; prm.group = p->shift_group; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes;
+        prm.na = p->shift_na; prm.a_stride = p->shift_a_stride;
+        const int m_tiles = prm.tiles_h * batch;
+        const int pairs = prm.tiles_n * ((m_tiles + 1) / 2);
+        const int max_pairs = p->n_sm / 2;
+        int npairs = pairs < max_pairs ? pairs : max_pairs;
+        if (npairs > prm.tiles_n) npairs -= npairs % prm.tiles_n;      // a pair keeps one column tile (its BN table)
+        return tc_launch_shift(p->BN, mode, epi, 2 * npairs, p->shift_smem_bytes, s, p->mapA_shift, p->mapB_half, prm);
     }
     int TW, TH, TB;
     pick_geometry(d.Wo, d.Ho, batch, &TW, &TH, &TB);
@@ -219,7 +271,7 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
         if (!encode_A(p, g)) return -1;
         p->n_geoms++;
     }
-    TcParams prm;
+    TcParams prm = {};
     prm.t = t; prm.res = res; prm.acc_out = acc_out; prm.out = out; prm.err = d_err;
     prm.out2 = (out_bn2 && t.bn_in) ? out_bn2 : nullptr;
     prm.batch = batch; prm.Ho = d.Ho; prm.Wo = d.Wo; prm.Cout = d.Cout;

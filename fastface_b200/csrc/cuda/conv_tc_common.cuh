@@ -127,6 +127,20 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64
                  "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// Warp-uniform issue: every lane executes the surrounding code (so the descriptor arithmetic is
+// uniform across the warp and needs no per-lane-to-uniform register moves), `leader` is
+// non-zero in the one lane whose instruction takes effect.
+__device__ __forceinline__ void umma_i8_w(uint32_t leader, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+                 "@q tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader) : "memory");
+}
+__device__ __forceinline__ void umma_commit_w(uint32_t leader, uint32_t bar)
+{
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+                 "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar), "r"(leader) : "memory");
+}
 // arrives on the mbarrier once every MMA issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
@@ -188,6 +202,18 @@ __device__ __forceinline__ void umma2_i8(uint32_t d_tmem, uint64_t a_desc, uint6
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma2_i8_w(uint32_t leader, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+                 "@q tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader) : "memory");
+}
+__device__ __forceinline__ void umma2_commit_both_w(uint32_t leader, uint32_t bar)
+{
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+                 "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}"
+                 ::"r"(bar), "h"((uint16_t)3), "r"(leader) : "memory");
 }
 // arrives, once the pair's MMAs issued so far are complete, on the mbarrier at this offset in BOTH CTAs
 __device__ __forceinline__ void umma2_commit_both(uint32_t bar)
@@ -266,6 +292,7 @@ struct TcParams {
     int stages;
     int lut_bytes;           // shared-memory bytes of the fused BN's table (BN * 256, or 0)
     int group;               // K blocks per pipeline stage (one barrier hand-shake per `group` blocks)
+    int na, a_stride;        // tap-shift kernel: activation-slice buffers in the ring, bytes per buffer
     int dbg;                 // timing experiments only ($FF_TC_DBG): bit 0 = skip the TMA loads, bit 1 = skip the MMAs, bit 2 = no global memory in the epilogue, bit 3 = no epilogue arithmetic
 };
 
@@ -276,6 +303,7 @@ struct TcParams {
 enum { EPI_RUNTIME = 0, EPI_PLAIN = 1, EPI_SLOPE = 2, EPI_RES_BN = 3, EPI_RES = 4 };
 
 #define TC_MAX_STAGES 8
+#define TC_MAX_ABUF 4
 #define TC_NTAB 5          // w_scale, bias, slope, res_scale, inv_out (the fused BN is a byte table)
 #ifndef TC_EPI_WARPS
 #define TC_EPI_WARPS 8     // warps 2..9: two per TMEM lane quarter, each takes half the columns (16 warps, with 16-column chunks for the narrow tiles, measured no faster: the epilogue is issue-bound, not latency-bound)
@@ -301,6 +329,8 @@ struct TcShared {                 // lives after the stage ring and the tables
     uint64_t empty[TC_MAX_STAGES];
     uint64_t acc_full[TC_MAX_ACC];
     uint64_t acc_empty[TC_MAX_ACC];
+    uint64_t a_full[TC_MAX_ABUF]; // tap-shift kernel: activation-slice ring
+    uint64_t a_empty[TC_MAX_ABUF];
     uint64_t w_full;              // weight-stationary kernel: weights have landed
     uint32_t tmem_base;
     int abort_flag;
@@ -574,6 +604,8 @@ __device__ __forceinline__ void tc_teardown(volatile int* abort_flag, uint32_t t
 // epi is an EPI_* value; f32 selects the FC epilogue (f32 output, no requantisation).
 int tc_launch_generic(int bn, int kc, int mode, int epi, bool f32, int grid, int smem, cudaStream_t s,
                       const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
+int tc_launch_shift(int bn, int mode, int epi, int grid, int smem, cudaStream_t s,
+                    const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
 int tc_launch_ws(int bn, int mode, int epi, int grid, int smem, cudaStream_t s,
                  const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
 int tc_launch_pair(int bn, int mode, int epi, bool f32, int grid, int smem, cudaStream_t s,

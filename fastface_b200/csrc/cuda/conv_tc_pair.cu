@@ -124,6 +124,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
             const uint64_t da0 = smem_desc<KC>(smem_u32(smem));
             const uint64_t db0 = smem_desc<KC>(smem_u32(smem) + A_BYTES);
+            const uint32_t leader = (lane == 0) ? 1u : 0u;
             for (int tile = pair_id; tile < total && ok; tile += n_pairs, local++) {
                 const int a = local % TC_NACC(BN);
                 const uint32_t aphase = (uint32_t)(local / TC_NACC(BN)) & 1;
@@ -135,21 +136,19 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                     ok = mbar_wait_cluster(full0 + stage * 8, phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
                     if (!ok) break;
                     tc_fence_after();
-                    if (lane == 0) {
-                        uint64_t soff = (uint64_t)((stage * stage_bytes) >> 4);
+                    {
+                        uint32_t soff = (uint32_t)((stage * stage_bytes) >> 4);
                         if (!(p.dbg & 2))
-                        for (int g = 0; g < G; g++, soff += (uint64_t)(SUB_BYTES >> 4)) {
+                        for (int g = 0; g < G; g++, soff += (uint32_t)(SUB_BYTES >> 4)) {
 #pragma unroll
                             for (int k = 0; k < KC / 32; k++)
-                                umma2_i8(d_tmem, da0 + soff + (uint64_t)(2 * k), db0 + soff + (uint64_t)(2 * k), IDESC, (it | g | k) ? 1u : 0u);
+                                umma2_i8_w(leader, d_tmem, da0 + (uint64_t)(soff + 2 * k), db0 + (uint64_t)(soff + 2 * k), IDESC, (it | g | k) ? 1u : 0u);
                         }
-                        umma2_commit_both(empty0 + stage * 8);   // frees the stage once these MMAs have read it
+                        umma2_commit_both_w(leader, empty0 + stage * 8);   // frees the stage once these MMAs have read it
                     }
-                    __syncwarp();
                     if (++stage == p.stages) { stage = 0; phase ^= 1; }
                 }
-                if (ok && lane == 0) umma2_commit_both(smem_u32(&sh->acc_full[a]));
-                __syncwarp();
+                if (ok) umma2_commit_both_w(leader, smem_u32(&sh->acc_full[a]));
             }
         }
     } else {

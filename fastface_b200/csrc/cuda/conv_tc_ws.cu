@@ -77,6 +77,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             int stage = 0; uint32_t phase = 0;
             int local = 0;
             const uint64_t dw = smem_desc<KC>(smem_u32(s_w));
+            const uint32_t leader = (lane == 0) ? 1u : 0u;
             for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, local++) {
                 const int a = local % TC_NACC(BN);
                 const uint32_t aphase = (uint32_t)(local / TC_NACC(BN)) & 1;
@@ -87,7 +88,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
                 const uint64_t da0 = smem_desc_sbo<KC>(smem_u32(s_a + (size_t)stage * WS_A_BYTES), WS_PITCH * 64);
-                if (lane == 0) {
+                {
                 if (!(p.dbg & 2))
 #pragma unroll
                 for (int kw = 0; kw < 3; kw++)
@@ -98,12 +99,11 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         const uint64_t db = dw + (uint64_t)(((kh * 3 + kw) * W_TAP_BYTES) >> 4);
 #pragma unroll
                         for (int k = 0; k < 2; k++)
-                            umma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, (kw | kh | k) ? 1u : 0u);
+                            umma_i8_w(leader, d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, (kw | kh | k) ? 1u : 0u);
                     }
-                umma_commit(smem_u32(&sh->empty[stage]));
-                umma_commit(smem_u32(&sh->acc_full[a]));
+                umma_commit_w(leader, smem_u32(&sh->empty[stage]));
+                umma_commit_w(leader, smem_u32(&sh->acc_full[a]));
                 }
-                __syncwarp();
                 if (++stage == p.stages) { stage = 0; phase ^= 1; }
             }
         }
