@@ -5,13 +5,14 @@
 #include "conv_tc_common.cuh"
 
 template <int BN>
-__global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int* err)
+__global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int* err, int mode)
 {
     extern __shared__ uint8_t smem_raw[];
     // round up to 1024 bytes by pointer arithmetic on the __shared__ array (an integer round-trip
     // would hide the address space from the compiler and turn every table read into a generic load)
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     __shared__ uint64_t done_bar;
+    __shared__ uint64_t scratch_bar;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     constexpr int KC = 128;
@@ -20,6 +21,7 @@ __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int* err)
     for (int i = threadIdx.x; i < (TC_TILE_M + BN) * KC / 4; i += blockDim.x) ((uint32_t*)smem)[i] = 0x01010101u * (i & 3);
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&done_bar), 1);
+        mbar_init(smem_u32(&scratch_bar), 1);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -35,9 +37,22 @@ __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int* err)
     if (threadIdx.x == 0) {
         const uint64_t da = smem_desc<KC>(smem_u32(smem));
         const uint64_t db = smem_desc<KC>(smem_u32(smem) + TC_TILE_M * KC);
-        for (int it = 0; it < iters; it++) {
+        if (mode == 0) {
+            for (int it = 0; it < iters; it++) {
 #pragma unroll
-            for (int k = 0; k < 4; k++) umma_i8(tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, (it | k) ? 1u : 0u);
+                for (int k = 0; k < 4; k++) umma_i8(tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, (it | k) ? 1u : 0u);
+            }
+        } else {
+            // issue-pattern experiments ($FF_PROBE_MODE): bit 0 = the descriptors move from round to
+            // round as a stage ring's would, bit 1 = one commit per round on a scratch barrier
+            int stage = 0;
+            for (int it = 0; it < iters; it++) {
+                const uint32_t off = (mode & 1) ? (uint32_t)(stage * 64) : 0u;
+#pragma unroll
+                for (int k = 0; k < 4; k++) umma_i8(tmem, da + (uint64_t)(off + 2 * k), db + (uint64_t)(off + 2 * k), IDESC, (it | k) ? 1u : 0u);
+                if (mode & 2) umma_commit(smem_u32(&scratch_bar));
+                if (++stage == 4) stage = 0;
+            }
         }
         umma_commit(smem_u32(&done_bar));
         mbar_wait(smem_u32(&done_bar), 0, &abort_flag, err, FFCU_ERR_MMA_TIMEOUT);
@@ -61,7 +76,9 @@ extern "C" int ffcu_i8_mma_peak(int device, int bn, int iters, float* tops, floa
     int* d_err = nullptr;
     FFCU_CHECK(cudaMalloc(&d_err, sizeof(int)));
     FFCU_CHECK(cudaMemset(d_err, 0, sizeof(int)));
-    const int smem = (TC_TILE_M + bn) * 128 + 1024;
+    const int smem = (TC_TILE_M + bn) * 128 + 1024 + 4096;
+    const char* me = getenv("FF_PROBE_MODE");
+    const int mode = me ? atoi(me) : 0;
     cudaEvent_t e0, e1;
     FFCU_CHECK(cudaEventCreate(&e0)); FFCU_CHECK(cudaEventCreate(&e1));
     float best = 1e30f;
@@ -69,13 +86,13 @@ extern "C" int ffcu_i8_mma_peak(int device, int bn, int iters, float* tops, floa
         FFCU_CHECK(cudaEventRecord(e0));
         if (bn == 64) {
             FFCU_CHECK(cudaFuncSetAttribute(mma_peak_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            mma_peak_kernel<64><<<n_sm, 128, smem>>>(iters, d_err);
+            mma_peak_kernel<64><<<n_sm, 128, smem>>>(iters, d_err, mode);
         } else if (bn == 128) {
             FFCU_CHECK(cudaFuncSetAttribute(mma_peak_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            mma_peak_kernel<128><<<n_sm, 128, smem>>>(iters, d_err);
+            mma_peak_kernel<128><<<n_sm, 128, smem>>>(iters, d_err, mode);
         } else {
             FFCU_CHECK(cudaFuncSetAttribute(mma_peak_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            mma_peak_kernel<256><<<n_sm, 128, smem>>>(iters, d_err);
+            mma_peak_kernel<256><<<n_sm, 128, smem>>>(iters, d_err, mode);
         }
         FFCU_CHECK(cudaEventRecord(e1));
         FFCU_CHECK(cudaEventSynchronize(e1));
