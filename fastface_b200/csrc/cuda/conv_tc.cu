@@ -162,7 +162,7 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
     p->shift = false;
     const char* sh_env = getenv("FF_TC_SHIFT");
     if (p->pair && L.kind == FFCU_CONV && L.Kh == 3 && L.Kw == 3 && L.stride == 1 && L.pad == 1 && Cp % 128 == 0 &&
-        (L.W == 14 || L.W == 28) && L.H == L.W && !(sh_env && sh_env[0] == '0')) {
+        (L.W == 14 || L.W == 28) && L.H == L.W && sh_env && sh_env[0] == '1') {     // opt-in: measured no faster than the per-tap pair kernel
         const int P = (L.W + 1 <= 16) ? 16 : 32, TR = 128 / P;
         cuuint64_t adims[4] = {(cuuint64_t)Cp, (cuuint64_t)L.W, (cuuint64_t)L.H, (cuuint64_t)max_batch};
         cuuint64_t astr[3] = {(cuuint64_t)Cp, (cuuint64_t)Cp * L.W, (cuuint64_t)Cp * L.W * L.H};

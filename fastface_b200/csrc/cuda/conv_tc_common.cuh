@@ -322,7 +322,10 @@ enum { EPI_RUNTIME = 0, EPI_PLAIN = 1, EPI_SLOPE = 2, EPI_RES_BN = 3, EPI_RES = 
 #ifndef TC_EPI_SETS
 #define TC_EPI_SETS 2
 #endif
-#define TC_THREADS (32 * (2 + TC_EPI_WARPS * TC_EPI_SETS))
+// Warp 0: TMA producer, warp 1: MMA issuer, warps 2 .. 2 + EPI_WARPS * SETS - 1: epilogue,
+// last warp: second MMA issuer (weight-stationary kernel only, idle elsewhere).
+#define TC_ISSUER2_WARP (2 + TC_EPI_WARPS * TC_EPI_SETS)
+#define TC_THREADS (32 * (3 + TC_EPI_WARPS * TC_EPI_SETS))
 
 struct TcShared {                 // lives after the stage ring and the tables
     uint64_t full[TC_MAX_STAGES];
@@ -477,6 +480,7 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
                                                  int first, int step, int total, int m_mul, int m_off,
                                                  uint32_t remote_acc_empty /* 0: local barrier */)
 {
+    if (warp >= TC_ISSUER2_WARP) return;                  // not an epilogue warp
     const int q = warp & 3;
     const int set = (warp - 2) / TC_EPI_WARPS;            // which of the CTA's tiles this warp takes
     const int cg = ((warp - 2) % TC_EPI_WARPS) >> 2;      // column group of this warp

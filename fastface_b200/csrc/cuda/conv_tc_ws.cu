@@ -69,16 +69,20 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 if (++stage == p.stages) { stage = 0; phase ^= 1; }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == TC_ISSUER2_WARP) {
         {
-            // MMA issuer: the warp loops and waits together, lane 0 issues
+            // Two MMA issuers take alternate tiles: a tile is 18 short MMAs (128 x BN x 32), and one
+            // thread cannot issue them as fast as the tensor pipe retires them.  Each issuer derives
+            // its ring positions from the tile's index, so the two never touch the same stage or
+            // accumulator.  The warp loops and waits together, lane 0 issues.
+            const int me = (warp == 1) ? 0 : 1;
             bool ok = mbar_wait(smem_u32(&sh->w_full), 0, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
             tc_fence_after();
-            int stage = 0; uint32_t phase = 0;
-            int local = 0;
             const uint64_t dw = smem_desc<KC>(smem_u32(s_w));
             const uint32_t leader = (lane == 0) ? 1u : 0u;
-            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, local++) {
+            for (int tile = blockIdx.x + me * gridDim.x, local = me; tile < p.total_tiles && ok; tile += 2 * gridDim.x, local += 2) {
+                const int stage = local % p.stages;
+                const uint32_t phase = (uint32_t)(local / p.stages) & 1;
                 const int a = local % TC_NACC(BN);
                 const uint32_t aphase = (uint32_t)(local / TC_NACC(BN)) & 1;
                 ok = mbar_wait(smem_u32(&sh->acc_empty[a]), aphase ^ 1, abort_flag, p.err, FFCU_ERR_TMEM_TIMEOUT);
@@ -104,7 +108,6 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 umma_commit_w(leader, smem_u32(&sh->empty[stage]));
                 umma_commit_w(leader, smem_u32(&sh->acc_full[a]));
                 }
-                if (++stage == p.stages) { stage = 0; phase ^= 1; }
             }
         }
     } else {

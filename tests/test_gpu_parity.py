@@ -189,6 +189,25 @@ def test_64ch_layers_on_the_per_tap_kernel(built_lib, case, monkeypatch):
     assert np.array_equal(acc, acc_o) and np.array_equal(out, out_o)
 
 
+@pytest.mark.parametrize("case", LAYER_CASES[4:8], ids=lambda c: c[0])
+def test_tap_shift_kernel(built_lib, case, monkeypatch):
+    """FF_TC_SHIFT=1 routes the 3x3 stride-1 layers on 14x14 / 28x28 maps through the CTA-pair
+    kernel that keeps the activation patch in shared memory for all nine taps (each tap is the
+    same buffer read from a shifted descriptor start address); same bytes as the oracle."""
+    monkeypatch.setenv("FF_TC_SHIFT", "1")
+    name, B, H, Cin, Cout, k, stride, sl, rs = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()) + 5)
+    L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
+    acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
+                            slope=L["slope"], res=L["res"], res_scale=L["rs"], impl="tc")
+    acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
+                               L["res"], L["rs"], ffo.CONTRACT)
+    msg = describe_mismatch("int32 accumulators", acc, acc_o)
+    assert not msg, msg
+    msg = describe_mismatch("int8 output", out, out_o)
+    assert not msg, msg
+
+
 @pytest.mark.parametrize("case", [c for c in LAYER_CASES if c[3] >= 128], ids=lambda c: c[0])
 def test_wide_layers_on_the_single_cta_kernel(built_lib, case, monkeypatch):
     """FF_TC_PAIR=0 routes the >=128-input-channel layers through the one-CTA kernel instead of
