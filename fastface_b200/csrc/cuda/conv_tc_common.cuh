@@ -449,6 +449,47 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
     }
 }
 
+// Programmatic dependent launch.  Each tensor-core kernel is launched with
+// cudaLaunchAttributeProgrammaticStreamSerialization: its CTAs may become resident while the
+// previous kernel of the stream is still finishing, run their set-up (barriers, TMEM, the
+// per-channel tables, which no kernel writes) and then block here until that kernel has
+// completed and its stores are visible.  Nothing a previous kernel produced, and nothing it may
+// still read, is touched before this point.
+__device__ __forceinline__ void tc_pdl_sync()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Launch with the programmatic-serialisation attribute (and the CTA-pair cluster shape when
+// pair is set).  $FF_PDL=0 launches the plain way.
+template <typename... KArgs, typename... Args>
+static int tc_launch_ex(void (*kern)(KArgs...), int grid, int smem, cudaStream_t s, bool pair, Args&&... args)
+{
+    static int pdl = -1;
+    if (pdl < 0) { const char* e = getenv("FF_PDL"); pdl = (e && e[0] == '0') ? 0 : 1; }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (pair) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 2; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1;
+        n++;
+    }
+    if (pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    cfg.attrs = attr; cfg.numAttrs = n;
+    FFCU_CHECK(cudaLaunchKernelEx(&cfg, kern, args...));
+    return 0;
+}
+
 // Tile walk.  A CTA visits tiles first, first + step, ...; the launchers keep step a multiple of
 // tiles_n, so the column tile never changes and the row-tile index m advances by a constant.
 // Its (w, h, batch) digits are carried forward with two compare-and-carry steps per tile: the

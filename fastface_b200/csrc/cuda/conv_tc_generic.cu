@@ -30,6 +30,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     tc_load_tables(tab, p);
     tc_load_lut(lut, p, (int)(blockIdx.x % p.tiles_n) * BN, BN);
     tc_setup(sh, p.stages, TMEM_COLS, warp, TC_EPI_ACTIVE(BN));
+    tc_pdl_sync();
     const uint32_t tmem_base = sh->tmem_base;
     volatile int* abort_flag = &sh->abort_flag;
 
@@ -139,9 +140,7 @@ static int launch_g(int grid, int smem, cudaStream_t s, const CUtensorMap& mapA,
         FFCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         smem_set[dev & 63] = smem;
     }
-    kern<<<grid, TC_THREADS, smem, s>>>(mapA, mapB, prm);
-    FFCU_CHECK(cudaGetLastError());
-    return 0;
+    return tc_launch_ex(kern, grid, smem, s, false, mapA, mapB, prm);
 }
 
 template <int BN, int KC>

@@ -68,6 +68,7 @@ conv_shift_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     __syncthreads();
     cluster_sync_all();                                  // peer's barriers are initialised
     tc_fence_after();
+    tc_pdl_sync();
     const uint32_t tmem_base = sh->tmem_base;
     volatile int* abort_flag = &sh->abort_flag;
 
@@ -193,17 +194,7 @@ static int launch_s(int grid, int smem, cudaStream_t s, const CUtensorMap& mapA,
         FFCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         smem_set[dev & 63] = smem;
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(TC_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr; cfg.numAttrs = 1;
-    FFCU_CHECK(cudaLaunchKernelEx(&cfg, kern, mapA, mapB, prm));
-    return 0;
+    return tc_launch_ex(kern, grid, smem, s, true, mapA, mapB, prm);
 }
 
 template <int BN>

@@ -40,6 +40,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     tc_load_tables(tab, p);
     tc_load_lut(lut, p, 0 * BN, BN);
     tc_setup(sh, p.stages, TMEM_COLS, warp, TC_EPI_ACTIVE(BN));
+    tc_pdl_sync();
     const uint32_t tmem_base = sh->tmem_base;
     volatile int* abort_flag = &sh->abort_flag;
 
@@ -130,9 +131,7 @@ static int launch_w(int grid, int smem, cudaStream_t s, const CUtensorMap& mapA,
         FFCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         smem_set[dev & 63] = smem;
     }
-    kern<<<grid, TC_THREADS, smem, s>>>(mapA, mapB, prm);
-    FFCU_CHECK(cudaGetLastError());
-    return 0;
+    return tc_launch_ex(kern, grid, smem, s, false, mapA, mapB, prm);
 }
 
 template <int BN>
