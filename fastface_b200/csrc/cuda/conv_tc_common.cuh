@@ -231,6 +231,29 @@ __device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
+// Non-blocking barrier tests.  A barrier test takes a few hundred cycles to answer; an issuer
+// loop that tests the barrier of the NEXT stage before issuing this stage's MMAs, and reads the
+// answer a round later, keeps that latency off its critical path (measured with the probe:
+// 163 -> 110 cycles per MMA at four MMAs per stage).
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ uint32_t mbar_test_cluster(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16])
 {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "

@@ -95,6 +95,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             const uint64_t da0 = smem_desc<KC>(smem_u32(smem));
             const uint64_t db0 = smem_desc<KC>(smem_u32(smem) + A_BYTES);
             const uint32_t leader = (lane == 0) ? 1u : 0u;
+            uint32_t ready = 0;                          // answer of the early test for the upcoming stage
             for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, local++) {
                 const int a = local % TC_NACC(BN);
                 const uint32_t aphase = (uint32_t)(local / TC_NACC(BN)) & 1;
@@ -103,8 +104,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
                 for (int it = 0; it < n_steps; it++) {
-                    ok = mbar_wait(full0 + stage * 8, phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
-                    if (!ok) break;
+                    if (!ready) {
+                        ok = mbar_wait(full0 + stage * 8, phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
+                        if (!ok) break;
+                    }
+                    // test the next stage's barrier now, use the answer next round
+                    int ns = stage + 1; uint32_t np = phase;
+                    if (ns == p.stages) { ns = 0; np ^= 1; }
+                    ready = mbar_test(full0 + ns * 8, np);
                     tc_fence_after();
                     {
                         uint32_t soff = (uint32_t)((stage * stage_bytes) >> 4);
@@ -116,7 +123,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         }
                         umma_commit_w(leader, empty0 + stage * 8);   // frees the stage once these MMAs have read it
                     }
-                    if (++stage == p.stages) { stage = 0; phase ^= 1; }
+                    stage = ns; phase = np;
                 }
                 if (ok) umma_commit_w(leader, smem_u32(&sh->acc_full[a]));
             }
