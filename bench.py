@@ -48,15 +48,40 @@ def rank_env():
 
 
 class Clocks:
-    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+    """Samples one GPU's SM clock and clock-event reasons while the timed region runs (read-only NVML
+    queries every 5 ms from a thread; falls back to an `nvidia-smi -lms` child if NVML cannot be loaded)."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    BITS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
     def __init__(self, gpu: int):
         self.gpu, self.rows, self.proc = gpu, [], None
+        self.sm, self.mx, self.mask, self.stop, self.t = [], None, 0, False, None
+
+    def _poll_nvml(self, nv, h):
+        while not self.stop:
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                try:
+                    self.mask |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
+                except AttributeError:
+                    self.mask |= int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+            except Exception:
+                pass
+            time.sleep(0.005)
 
     def __enter__(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.gpu)
+            self.mx = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            self.t = threading.Thread(target=self._poll_nvml, args=(nv, h), daemon=True)
+            self.t.start()
+            return self
+        except Exception:
+            self.t = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS,
                                           "--format=csv,noheader,nounits", "-lms", "100"],
@@ -72,14 +97,20 @@ class Clocks:
             self.rows.append([x.strip() for x in line.split(",")])
 
     def __exit__(self, *exc):
+        self.stop = True
         if self.proc:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+        elif self.t:
+            self.t.join(timeout=1)
 
     def summary(self):
+        if not self.proc and self.sm:
+            return {"sm_mhz": statistics.median(self.sm), "sm_max_mhz": self.mx,
+                    "reasons": [n for n, bit in self.BITS if self.mask & bit], "samples": len(self.sm)}
         sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
         mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
@@ -371,6 +402,34 @@ def run_own_arm(args, rank, local_rank, world):
     tmp.cleanup()
 
 
+def run_single_layer_cases():
+    """Three single-layer convolutions through the C-ABI entry ffcu_conv_once, sized for a profiler
+    capture (tensors larger than L2, a fraction of a GB on the device): one per tensor-core kernel."""
+    sys.path.insert(0, ROOT)
+    import fastface_b200 as ff
+    rng = np.random.default_rng(0)
+
+    def run(B, H, Cin, Cout, res):
+        x = rng.integers(-127, 128, size=(B, H, H, Cin), dtype=np.int8)
+        w = rng.integers(-127, 128, size=(Cout, Cin, 3, 3), dtype=np.int8)
+        ws = np.full(Cout, 1e-4, np.float32)
+        bias = np.zeros(Cout, np.float32)
+        inv = np.full(Cout, 10.0, np.float32)
+        slope = None if res else np.full(Cout, 0.1, np.float32)
+        r = rng.integers(-127, 128, size=(B, H, H, Cout), dtype=np.int8) if res else None
+        rs = np.full(Cout, 0.01, np.float32) if res else None
+        bn2 = (np.full(Cout, 0.1, np.float32), np.ones(Cout, np.float32), np.zeros(Cout, np.float32),
+               np.full(Cout, 10.0, np.float32)) if res else None
+        out = ff.conv_once(x, w, ws, bias, inv, slope=slope, res=r, res_scale=rs, bn2=bn2, impl="tc", want_acc=False)
+        print(json.dumps({"case": [B, H, Cin, Cout], "residual_bn": bool(res), "out_std": float(out[1].std())}), flush=True)
+
+    run(1024, 14, 256, 256, True)     # CTA-pair kernel, residual + fused BN (51 MB in, 51 MB residual, 2 x 51 MB out)
+    run(1024, 14, 256, 256, False)    # CTA-pair kernel, PReLU
+    run(256, 56, 64, 64, False)       # weight-stationary kernel, PReLU (51 MB in, 51 MB out)
+    run(256, 56, 64, 64, True)        # weight-stationary kernel, residual + fused BN
+    run(512, 28, 128, 128, True)      # CTA-pair kernel, BN = 128 (51 MB per tensor)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -382,7 +441,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", action="store_true", help="add per-layer milliseconds to the JSON line")
     ap.add_argument("--dry-run", action="store_true", help="rank protocol only, no GPU work (CPU tests)")
+    ap.add_argument("--single-layer-cases", action="store_true",
+                    help="run one small launch of each tensor-core kernel and exit (for profiler captures)")
     args = ap.parse_args()
+    if args.single_layer_cases:
+        run_single_layer_cases()
+        return
     rank, local_rank, world = rank_env()
     if args.impl == "reference":
         run_reference_arm(args, rank, world)

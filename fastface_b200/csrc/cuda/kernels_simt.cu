@@ -251,11 +251,12 @@ int ffcu_launch_fc_simt(const int8_t* act, const int8_t* w, const float* w_scale
 // shared memory, weights ([tap][co] words) and the per-channel tables sit there too.
 // ---------------------------------------------------------------------------
 #define STEM_T 16
+#define STEM_THREADS 128           // each thread computes two pixels (rows ty and ty + 8 of the tile)
 template <bool CONTRACT, bool HAS_SLOPE, bool HAS_BN2, bool CHECK>
-__global__ void __launch_bounds__(256) stem_kernel(const float* __restrict__ in, const float* __restrict__ inv3,
-                                                   const int8_t* __restrict__ w, EpiTables t,
-                                                   int8_t* __restrict__ out, int8_t* __restrict__ out2,
-                                                   int* __restrict__ q_out)
+__global__ void __launch_bounds__(STEM_THREADS) stem_kernel(const float* __restrict__ in, const float* __restrict__ inv3,
+                                                            const int8_t* __restrict__ w, EpiTables t,
+                                                            int8_t* __restrict__ out, int8_t* __restrict__ out2,
+                                                            int* __restrict__ q_out)
 {
     constexpr int H = 112, W = 112, C = 64, P = STEM_T + 2;
     __shared__ int s_in[P * P];
@@ -266,7 +267,7 @@ __global__ void __launch_bounds__(256) stem_kernel(const float* __restrict__ in,
     const int x0 = blockIdx.x * STEM_T, y0 = blockIdx.y * STEM_T;
     const float i0 = __ldg(inv3), i1 = __ldg(inv3 + 1), i2 = __ldg(inv3 + 2);
     constexpr bool has_bn2 = HAS_BN2;     // compile-time: keeps the per-element code branch-free
-    for (int i = threadIdx.x; i < P * P; i += 256) {
+    for (int i = threadIdx.x; i < P * P; i += STEM_THREADS) {
         int py = y0 - 1 + i / P, px = x0 - 1 + i % P;
         int v = 0;
         if (py >= 0 && py < H && px >= 0 && px < W) {
@@ -278,60 +279,75 @@ __global__ void __launch_bounds__(256) stem_kernel(const float* __restrict__ in,
         }
         s_in[i] = v;
     }
-    for (int i = threadIdx.x; i < 9 * C; i += 256) {
+    for (int i = threadIdx.x; i < 9 * C; i += STEM_THREADS) {
         int tap = i / C, co = i % C;
         s_w[i] = __ldg((const int*)w + co * 9 + tap);     // global layout [co][tap] words
     }
-    for (int i = threadIdx.x; i < C; i += 256) {
+    for (int i = threadIdx.x; i < C; i += STEM_THREADS) {
         s_tab[0 * C + i] = t.w_scale[i]; s_tab[1 * C + i] = t.bias[i];
         s_tab[2 * C + i] = t.slope ? t.slope[i] : 0.0f; s_tab[3 * C + i] = t.inv_out[i];
     }
     if (has_bn2)
-        for (int i = threadIdx.x; i < C * 16; i += 256) ((int4*)s_lut)[i] = __ldg((const int4*)t.bn_lut + i);
+        for (int i = threadIdx.x; i < C * 16; i += STEM_THREADS) ((int4*)s_lut)[i] = __ldg((const int4*)t.bn_lut + i);
     __syncthreads();
-    const int tx = threadIdx.x % STEM_T, ty = threadIdx.x / STEM_T;
-    int a[9];
+    // Two pixels per thread: every weight word and table entry fetched from shared memory serves
+    // both (the kernel is bound by shared-memory reads, two thirds of them weights and tables).
+    const int tx = threadIdx.x % STEM_T, ty = threadIdx.x / STEM_T;       // ty in 0..7; second pixel at ty + 8
+    int a[2][9];
 #pragma unroll
-    for (int kh = 0; kh < 3; kh++)
+    for (int pp = 0; pp < 2; pp++)
 #pragma unroll
-        for (int kw = 0; kw < 3; kw++) a[kh * 3 + kw] = s_in[(ty + kh) * P + tx + kw];
-    const size_t pix = ((size_t)b * H + (y0 + ty)) * W + (x0 + tx);
-    if (q_out) q_out[pix] = a[4];
+        for (int kh = 0; kh < 3; kh++)
+#pragma unroll
+            for (int kw = 0; kw < 3; kw++) a[pp][kh * 3 + kw] = s_in[(ty + 8 * pp + kh) * P + tx + kw];
+    size_t pix[2];
+#pragma unroll
+    for (int pp = 0; pp < 2; pp++) {
+        pix[pp] = ((size_t)b * H + (y0 + ty + 8 * pp)) * W + (x0 + tx);
+        if (q_out) q_out[pix[pp]] = a[pp][4];
+    }
     constexpr bool has_slope = HAS_SLOPE;
-    int4* dst = (int4*)(out + pix * C);
-    int4* dst2 = (int4*)(out2 + pix * C);
 #pragma unroll 1
-    for (int g16 = 0; g16 < C / 16; g16++) {          // 16 channels -> one 16-byte store
-        int wo[4], wo2[4];
+    for (int g16 = 0; g16 < C / 16; g16++) {          // 16 channels -> one 16-byte store per pixel
+        int wo[2][4], wo2[2][4];
 #pragma unroll
         for (int g = 0; g < 4; g++) {
             const int co = g16 * 16 + g * 4;
-            int acc0 = 0, acc1 = 0, acc2 = 0, acc3 = 0;
+            int acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
 #pragma unroll
             for (int tap = 0; tap < 9; tap++) {
                 const int4 ww = *(const int4*)&s_w[tap * C + co];
-                acc0 = __dp4a(a[tap], ww.x, acc0); acc1 = __dp4a(a[tap], ww.y, acc1);
-                acc2 = __dp4a(a[tap], ww.z, acc2); acc3 = __dp4a(a[tap], ww.w, acc3);
+#pragma unroll
+                for (int pp = 0; pp < 2; pp++) {
+                    acc[pp][0] = __dp4a(a[pp][tap], ww.x, acc[pp][0]); acc[pp][1] = __dp4a(a[pp][tap], ww.y, acc[pp][1]);
+                    acc[pp][2] = __dp4a(a[pp][tap], ww.z, acc[pp][2]); acc[pp][3] = __dp4a(a[pp][tap], ww.w, acc[pp][3]);
+                }
             }
             const float4 ws = *(const float4*)&s_tab[0 * C + co];
             const float4 bi = *(const float4*)&s_tab[1 * C + co];
             const float4 sl = *(const float4*)&s_tab[2 * C + co];
             const float4 iv = *(const float4*)&s_tab[3 * C + co];
-            int q0 = ffcu_requant_nosat<CHECK>(ffcu_conv_fp<CONTRACT>(acc0, ws.x, bi.x, false, 0, 0.0f, has_slope, sl.x), iv.x);
-            int q1 = ffcu_requant_nosat<CHECK>(ffcu_conv_fp<CONTRACT>(acc1, ws.y, bi.y, false, 0, 0.0f, has_slope, sl.y), iv.y);
-            int q2 = ffcu_requant_nosat<CHECK>(ffcu_conv_fp<CONTRACT>(acc2, ws.z, bi.z, false, 0, 0.0f, has_slope, sl.z), iv.z);
-            int q3 = ffcu_requant_nosat<CHECK>(ffcu_conv_fp<CONTRACT>(acc3, ws.w, bi.w, false, 0, 0.0f, has_slope, sl.w), iv.w);
-            wo[g] = ffcu_pack4(q0, q1, q2, q3);              // saturates to [-128, 127]
-            if (has_bn2) {
-                const uint8_t* lc = s_lut + co * 256;
-                const unsigned w4 = (unsigned)wo[g];
-                const unsigned r0 = lc[w4 & 0xffu], r1 = lc[256 + ((w4 >> 8) & 0xffu)];
-                const unsigned r2 = lc[512 + ((w4 >> 16) & 0xffu)], r3 = lc[768 + (w4 >> 24)];
-                wo2[g] = (int)(r0 | (r1 << 8) | (r2 << 16) | (r3 << 24));
+#pragma unroll
+            for (int pp = 0; pp < 2; pp++) {
+                int q0 = ffcu_requant_nosat<CHECK>(ffcu_conv_fp<CONTRACT>(acc[pp][0], ws.x, bi.x, false, 0, 0.0f, has_slope, sl.x), iv.x);
+                int q1 = ffcu_requant_nosat<CHECK>(ffcu_conv_fp<CONTRACT>(acc[pp][1], ws.y, bi.y, false, 0, 0.0f, has_slope, sl.y), iv.y);
+                int q2 = ffcu_requant_nosat<CHECK>(ffcu_conv_fp<CONTRACT>(acc[pp][2], ws.z, bi.z, false, 0, 0.0f, has_slope, sl.z), iv.z);
+                int q3 = ffcu_requant_nosat<CHECK>(ffcu_conv_fp<CONTRACT>(acc[pp][3], ws.w, bi.w, false, 0, 0.0f, has_slope, sl.w), iv.w);
+                wo[pp][g] = ffcu_pack4(q0, q1, q2, q3);              // saturates to [-128, 127]
+                if (has_bn2) {
+                    const uint8_t* lc = s_lut + co * 256;
+                    const unsigned w4 = (unsigned)wo[pp][g];
+                    const unsigned r0 = lc[w4 & 0xffu], r1 = lc[256 + ((w4 >> 8) & 0xffu)];
+                    const unsigned r2 = lc[512 + ((w4 >> 16) & 0xffu)], r3 = lc[768 + (w4 >> 24)];
+                    wo2[pp][g] = (int)(r0 | (r1 << 8) | (r2 << 16) | (r3 << 24));
+                }
             }
         }
-        dst[g16] = make_int4(wo[0], wo[1], wo[2], wo[3]);
-        if (has_bn2) dst2[g16] = make_int4(wo2[0], wo2[1], wo2[2], wo2[3]);
+#pragma unroll
+        for (int pp = 0; pp < 2; pp++) {
+            ((int4*)(out + pix[pp] * C))[g16] = make_int4(wo[pp][0], wo[pp][1], wo[pp][2], wo[pp][3]);
+            if (has_bn2) ((int4*)(out2 + pix[pp] * C))[g16] = make_int4(wo2[pp][0], wo2[pp][1], wo2[pp][2], wo2[pp][3]);
+        }
     }
 }
 
@@ -341,8 +357,8 @@ int ffcu_launch_stem(const float* in_f32, const float* inv3, const int8_t* w, co
     dim3 grid(112 / STEM_T, 112 / STEM_T, batch);
     const bool sl = t.slope != nullptr, bn = (out_bn2 != nullptr) && (t.bn_lut != nullptr);
 #define STEM_GO(C_, S_, B_) do { \
-        if (t.no_overflow) stem_kernel<C_, S_, B_, false><<<grid, 256, 0, s>>>(in_f32, inv3, w, t, out, out_bn2, (int*)q_out); \
-        else               stem_kernel<C_, S_, B_, true><<<grid, 256, 0, s>>>(in_f32, inv3, w, t, out, out_bn2, (int*)q_out); } while (0)
+        if (t.no_overflow) stem_kernel<C_, S_, B_, false><<<grid, STEM_THREADS, 0, s>>>(in_f32, inv3, w, t, out, out_bn2, (int*)q_out); \
+        else               stem_kernel<C_, S_, B_, true><<<grid, STEM_THREADS, 0, s>>>(in_f32, inv3, w, t, out, out_bn2, (int*)q_out); } while (0)
     if (mode) {
         if (sl && bn) STEM_GO(true, true, true); else if (sl) STEM_GO(true, true, false);
         else if (bn) STEM_GO(true, false, true); else STEM_GO(true, false, false);
