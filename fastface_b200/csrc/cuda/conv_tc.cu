@@ -34,6 +34,7 @@ struct TcPlan {
     int n_sm;
     int group, pair_group;   // K blocks per pipeline stage
     int lut_bytes;           // shared memory for the fused BN's byte table
+    int ntab;                // per-channel tables in shared memory (5, or 9 with an arithmetic fused BN)
     TcGeom geoms[8];
     int n_geoms;
     bool pair;               // CTA-pair kernel (cta_group::2) for >= 128 input channels
@@ -99,8 +100,15 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
     p->BN = L.Cout >= 256 ? 256 : L.Cout;
     const char* bn_env = getenv("FF_TC_BN");
     if (bn_env) { int v = atoi(bn_env); if ((v == 64 || v == 128 || v == 256) && L.Cout % v == 0) p->BN = v; }
-    const int lut_bytes = (L.kind == FFCU_CONV && L.bn2_dst_buf >= 0) ? p->BN * 256 : 0;
-    const int fixed = TC_NTAB * TC_MAX_COUT * 4 + (int)sizeof(TcShared) + 1024 + lut_bytes;
+    // fused BN: a byte table in shared memory for tiles up to $FF_TC_BNLUT_MAX channels wide, arithmetic beyond
+    // (default: the table everywhere; measured 2 - 3 % faster per step than arithmetic for the wide tiles although
+    // it costs those a pipeline stage)
+    const char* lm = getenv("FF_TC_BNLUT_MAX");
+    const int lut_max = lm ? atoi(lm) : 256;
+    const int lut_bytes = (L.kind == FFCU_CONV && L.bn2_dst_buf >= 0 && p->BN <= lut_max) ? p->BN * 256 : 0;
+    const int ntab = (L.kind == FFCU_CONV && L.bn2_dst_buf >= 0 && !lut_bytes) ? 9 : 5;
+    p->ntab = ntab;
+    const int fixed = ntab * TC_MAX_COUT * 4 + (int)sizeof(TcShared) + 1024 + lut_bytes;
     p->lut_bytes = lut_bytes;
     const int kblocks = L.Kh * L.Kw * (Cp / p->KC);
     const char* genv = getenv("FF_TC_GROUP");
@@ -236,7 +244,7 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
         prm.TW = WS_TW; prm.TH = WS_TH; prm.TB = 1;
         prm.tiles_w = d.Wo / WS_TW; prm.tiles_h = (d.Ho + WS_TH - 1) / WS_TH; prm.tiles_b = batch; prm.tiles_n = 1;
         prm.total_tiles = prm.tiles_w * prm.tiles_h * batch;
-        prm.stages = p->ws_stages; prm.group = 1; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes;
+        prm.stages = p->ws_stages; prm.group = 1; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab;
         int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
         return tc_launch_ws(p->BN, mode, epi, grid, p->ws_smem_bytes, s, p->mapA_ws, p->mapB, prm);
     }
@@ -250,7 +258,7 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
         prm.tiles_w = 1; prm.tiles_h = (d.Ho + p->shift_TR - 1) / p->shift_TR; prm.tiles_b = batch;
         prm.tiles_n = d.Cout / p->BN;
         prm.total_tiles = prm.tiles_h * batch * prm.tiles_n;
-        prm.stages = p->shift_stages; prm.group = p->shift_group; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes;
+        prm.stages = p->shift_stages; prm.group = p->shift_group; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab;
         prm.na = p->shift_na; prm.a_stride = p->shift_a_stride;
         const int m_tiles = prm.tiles_h * batch;
         const int pairs = prm.tiles_n * ((m_tiles + 1) / 2);
@@ -281,7 +289,7 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
     prm.tiles_w = (d.Wo + TW - 1) / TW; prm.tiles_h = (d.Ho + TH - 1) / TH; prm.tiles_b = (batch + TB - 1) / TB;
     prm.tiles_n = d.Cout / p->BN;
     prm.total_tiles = prm.tiles_w * prm.tiles_h * prm.tiles_b * prm.tiles_n;
-    prm.stages = p->stages; prm.group = p->group; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes;
+    prm.stages = p->stages; prm.group = p->group; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab;
     { const char* e = getenv("FF_TC_STAGES"); if (e && atoi(e) >= 2 && atoi(e) < prm.stages) prm.stages = atoi(e); }
     if (p->pair) {
         const int m_tiles = prm.tiles_w * prm.tiles_h * prm.tiles_b;

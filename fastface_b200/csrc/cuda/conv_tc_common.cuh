@@ -315,6 +315,7 @@ struct TcParams {
     int stages;
     int lut_bytes;           // shared-memory bytes of the fused BN's table (BN * 256, or 0)
     int group;               // K blocks per pipeline stage (one barrier hand-shake per `group` blocks)
+    int ntab;                // per-channel tables held in shared memory: 5, or 9 when the fused BN is computed arithmetically
     int na, a_stride;        // tap-shift kernel: activation-slice buffers in the ring, bytes per buffer
     int dbg;                 // timing experiments only ($FF_TC_DBG): bit 0 = skip the TMA loads, bit 1 = skip the MMAs, bit 2 = no global memory in the epilogue, bit 3 = no epilogue arithmetic
 };
@@ -327,7 +328,7 @@ enum { EPI_RUNTIME = 0, EPI_PLAIN = 1, EPI_SLOPE = 2, EPI_RES_BN = 3, EPI_RES = 
 
 #define TC_MAX_STAGES 8
 #define TC_MAX_ABUF 4
-#define TC_NTAB 5          // w_scale, bias, slope, res_scale, inv_out (the fused BN is a byte table)
+#define TC_NTAB 9          // w_scale, bias, slope, res_scale, inv_out | fused BN without a byte table: in_scale, scale, offset, inv_out
 #ifndef TC_EPI_WARPS
 #define TC_EPI_WARPS 8     // warps 2..9: two per TMEM lane quarter, each takes half the columns (16 warps, with 16-column chunks for the narrow tiles, measured no faster: the epilogue is issue-bound, not latency-bound)
 #endif
@@ -370,6 +371,12 @@ __device__ __forceinline__ void tc_load_tables(float* tab, const TcParams& p)
         tab[2 * TC_MAX_COUT + i] = p.t.slope ? p.t.slope[i] : 0.0f;
         tab[3 * TC_MAX_COUT + i] = p.t.res_scale ? p.t.res_scale[i] : 0.0f;
         tab[4 * TC_MAX_COUT + i] = p.t.inv_out ? p.t.inv_out[i] : 0.0f;
+        if (p.out2 && !p.lut_bytes) {
+            tab[5 * TC_MAX_COUT + i] = p.t.bn_in[i];
+            tab[6 * TC_MAX_COUT + i] = p.t.bn_scale[i];
+            tab[7 * TC_MAX_COUT + i] = p.t.bn_offset[i];
+            tab[8 * TC_MAX_COUT + i] = p.t.bn_inv[i];
+        }
     }
 }
 
@@ -447,7 +454,21 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
         int q0 = ffcu_requant_nosat<CHECK>(f0, iv.x), q1 = ffcu_requant_nosat<CHECK>(f1, iv.y);
         int q2 = ffcu_requant_nosat<CHECK>(f2, iv.z), q3 = ffcu_requant_nosat<CHECK>(f3, iv.w);
         ow_[g] = ffcu_pack4(q0, q1, q2, q3);
-        if (has_bn2) {
+        if (has_bn2 && !p.lut_bytes) {
+            // BN of the four int8 results by arithmetic (the wide tiles: their byte tables would take 32 - 64 KB
+            // from the stage ring and their lookups compete with the tensor core for shared-memory bandwidth)
+            const float4 b_in = *(const float4*)&tab[5 * TC_MAX_COUT + cb + 4 * g];
+            const float4 b_sc = *(const float4*)&tab[6 * TC_MAX_COUT + cb + 4 * g];
+            const float4 b_of = *(const float4*)&tab[7 * TC_MAX_COUT + cb + 4 * g];
+            const float4 b_iv = *(const float4*)&tab[8 * TC_MAX_COUT + cb + 4 * g];
+            const int w = ow_[g];
+            const int a0 = (int)(int8_t)(w & 0xff), a1 = (int)(int8_t)((w >> 8) & 0xff);
+            const int a2 = (int)(int8_t)((w >> 16) & 0xff), a3 = w >> 24;
+            ow2_[g] = ffcu_pack4(ffcu_bn_q_nosat<CHECK>(a0, b_in.x, b_sc.x, b_of.x, b_iv.x),
+                                 ffcu_bn_q_nosat<CHECK>(a1, b_in.y, b_sc.y, b_of.y, b_iv.y),
+                                 ffcu_bn_q_nosat<CHECK>(a2, b_in.z, b_sc.z, b_of.z, b_iv.z),
+                                 ffcu_bn_q_nosat<CHECK>(a3, b_in.w, b_sc.w, b_of.w, b_iv.w));
+        } else if (has_bn2) {
             // BN of the four int8 results just packed: one table row per channel, indexed by the byte
             const uint8_t* lc = lutc + (4 * g) * 256;
             const unsigned w = (unsigned)ow_[g];

@@ -35,7 +35,7 @@ conv_shift_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     uint8_t* s_a = smem;                                                    // [na][a_stride]
     uint8_t* s_b = smem + (size_t)p.na * p.a_stride;                        // [stages][group][B_BYTES]
     float* tab = (float*)(s_b + (size_t)p.stages * p.group * B_BYTES);
-    uint8_t* lut = (uint8_t*)(tab + TC_NTAB * TC_MAX_COUT);
+    uint8_t* lut = (uint8_t*)(tab + p.ntab * TC_MAX_COUT);
     TcShared* sh = (TcShared*)(lut + p.lut_bytes);
 
     const int warp = threadIdx.x >> 5;

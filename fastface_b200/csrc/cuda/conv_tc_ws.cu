@@ -31,7 +31,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     uint8_t* s_w = smem;                                        // [9][BN][64]
     uint8_t* s_a = smem + W_BYTES;                              // [stages][3][144][64]
     float* tab = (float*)(s_a + (size_t)p.stages * WS_A_BYTES);
-    uint8_t* lut = (uint8_t*)(tab + TC_NTAB * TC_MAX_COUT);                  // [BN][256] fused-BN table (lut_bytes may be 0)
+    uint8_t* lut = (uint8_t*)(tab + p.ntab * TC_MAX_COUT);                  // [BN][256] fused-BN table (lut_bytes may be 0)
     TcShared* sh = (TcShared*)(lut + p.lut_bytes);
 
     const int warp = threadIdx.x >> 5;

@@ -173,6 +173,12 @@ static bool epilogue_cannot_overflow(const ffcu_layer* l)
         if (l->slope) { const double a = fabs((double)l->slope[c]); if (a > 1.0) t *= a; if (!(a == a)) return false; }
         const double q = t * fabs((double)l->inv_out[c]) + 1.0;
         if (!(q < 1073741824.0)) return false;            // also rejects NaN / inf
+        if (l->bn2_in_scale && l->bn2_scale && l->bn2_offset && l->bn2_inv_out) {
+            // the fused BN of the int8 result: |128 * in_scale * scale + offset| * inv_out
+            const double b = (128.0 * fabs((double)l->bn2_in_scale[c]) * fabs((double)l->bn2_scale[c]) +
+                              fabs((double)l->bn2_offset[c])) * fabs((double)l->bn2_inv_out[c]) + 1.0;
+            if (!(b < 1073741824.0)) return false;
+        }
     }
     return true;
 }

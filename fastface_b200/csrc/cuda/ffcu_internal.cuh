@@ -91,11 +91,12 @@ __device__ __forceinline__ int ffcu_pack4(int a, int b, int c, int d)
 }
 
 // BN of an already-clamped int8 value, unclamped result (see ffcu_bn_q).
+template <bool CHECK = true>
 __device__ __forceinline__ int ffcu_bn_q_nosat(int a, float in_scale, float bn_scale, float bn_offset, float inv)
 {
     float t = __fmul_rn(__int2float_rn(a), in_scale);
     t = __fmaf_rn(t, bn_scale, bn_offset);
-    return ffcu_requant_nosat(t, inv);
+    return ffcu_requant_nosat<CHECK>(t, inv);
 }
 
 // Conv epilogue value before requantisation (reference kernels/int8_epilogue.c:53-76).

@@ -189,6 +189,34 @@ def test_64ch_layers_on_the_per_tap_kernel(built_lib, case, monkeypatch):
     assert np.array_equal(acc, acc_o) and np.array_equal(out, out_o)
 
 
+@pytest.mark.parametrize("case", [LAYER_CASES[2], LAYER_CASES[4], LAYER_CASES[6]], ids=lambda c: c[0])
+def test_fused_bn_by_arithmetic(built_lib, case, monkeypatch):
+    """FF_TC_BNLUT_MAX=0 computes the fused BN output arithmetically in the epilogue instead of through
+    the per-channel byte table; both must equal bn_prelu_requant_int8 (kernels/int8_epilogue.c:253-318)."""
+    monkeypatch.setenv("FF_TC_BNLUT_MAX", "0")
+    name, B, H, Cin, Cout, k, stride, sl, rs = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()) + 9)
+    L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
+    in_scale = (np.float32(1) / L["inv"]).astype(np.float32)
+    bn_s = rng.uniform(0.5, 1.5, Cout).astype(np.float32)
+    bn_o = (rng.standard_normal(Cout) * 0.1).astype(np.float32)
+    bn_inv = (np.float32(1) / (rng.uniform(0.005, 0.05, Cout).astype(np.float32) + np.float32(1e-9))).astype(np.float32)
+    acc, out, out2 = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
+                                  slope=L["slope"], res=L["res"], res_scale=L["rs"], impl="tc",
+                                  bn2=(in_scale, bn_s, bn_o, bn_inv))
+    acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
+                               L["res"], L["rs"], ffo.CONTRACT)
+    lib = _libffo()
+    want2 = np.zeros_like(out_o)
+    lib.ffo_bn_requant.argtypes = [C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                   C.c_float, C.c_void_p, C.c_int, C.c_int]
+    lib.ffo_bn_requant(out_o.ctypes.data, 1.0, in_scale.ctypes.data, bn_s.ctypes.data, bn_o.ctypes.data, None,
+                       bn_inv.ctypes.data, 1.0, want2.ctypes.data, out_o.size // Cout, Cout)
+    assert np.array_equal(out, out_o)
+    msg = describe_mismatch("fused BN output (arithmetic)", out2, want2)
+    assert not msg, msg
+
+
 @pytest.mark.parametrize("case", LAYER_CASES[4:8], ids=lambda c: c[0])
 def test_tap_shift_kernel(built_lib, case, monkeypatch):
     """FF_TC_SHIFT=1 routes the 3x3 stride-1 layers on 14x14 / 28x28 maps through the CTA-pair
