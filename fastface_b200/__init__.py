@@ -60,6 +60,8 @@ def load_library() -> C.CDLL:
     L.fastface_embed.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
     L.fastface_embed_batch.restype = C.c_int
     L.fastface_embed_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+    L.fastface_embed_batch_u8.restype = C.c_int
+    L.fastface_embed_batch_u8.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
     L.fastface_destroy.restype = None
     L.fastface_destroy.argtypes = [C.c_void_p]
     L.fastface_cos_sim.restype = C.c_float
@@ -145,6 +147,19 @@ class FastFace:
         rc = self.lib.fastface_embed_batch(self.h, _ptr(faces), n, _ptr(out))
         if rc != 0:
             raise RuntimeError(f"fastface_embed_batch rc={rc}: " + self.lib.fastface_last_error().decode())
+
+    def embed_batch_u8(self, pixels) -> np.ndarray:
+        """8-bit pixels [n,112,112,3] -> [n,512]; same embeddings as embed_batch((p - 127.5) / 127.5)."""
+        a = np.ascontiguousarray(np.asarray(pixels, dtype=np.uint8)).reshape(-1, *FACE_SHAPE)
+        out = np.empty((a.shape[0], EMB_DIM), np.float32)
+        self.embed_into_u8(a, out)
+        return out
+
+    def embed_into_u8(self, pixels: np.ndarray, out: np.ndarray) -> None:
+        n = pixels.shape[0]
+        rc = self.lib.fastface_embed_batch_u8(self.h, _ptr(pixels), n, _ptr(out))
+        if rc != 0:
+            raise RuntimeError(f"fastface_embed_batch_u8 rc={rc}: " + self.lib.fastface_last_error().decode())
 
     @staticmethod
     def cos_sim(a: np.ndarray, b: np.ndarray) -> float:

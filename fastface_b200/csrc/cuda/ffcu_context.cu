@@ -45,6 +45,7 @@ struct ffcu_ctx {
     float* in_slot[2] = {};      // [max_batch][112][112][3] f32
     float* out_slot[2] = {};     // [max_batch][512] f32
     float* d_in = nullptr;       // slot the next launch_forward reads
+    bool in_u8 = false;          // that slot holds 8-bit pixels [n][112][112][3] instead of fp32
     float* d_out = nullptr;      // slot the next launch_forward writes
     cudaEvent_t ev_in_ready[2] = {}, ev_compute_done[2] = {}, ev_out_copied[2] = {};
     unsigned long long seq = 0;
@@ -279,11 +280,12 @@ static int launch_layer(ffcu_ctx* c, size_t k, int n, int32_t* acc_dbg, bool unf
     switch (d.kind) {
     case FFCU_QUANT:
         if (L.skip && !unfused) return 0;
+        if (c->in_u8) { ffcu_set_error("8-bit pixel input needs the fused stem (FF_FUSE_STEM=0 or a dump-point run is in effect)"); return -1; }
         return ffcu_launch_quant(c->d_in, n * d.H * d.W, L.tab[4], c->bufs[d.dst_buf], s);
     case FFCU_CONV: {
         const int8_t* res = d.res_buf >= 0 ? c->bufs[d.res_buf] : nullptr;
         if (L.fused_stem && !unfused)
-            return ffcu_launch_stem(c->d_in, c->layers[0].tab[4], L.w, L.epi, n, c->mode, c->bufs[d.dst_buf], out2, nullptr, s);
+            return ffcu_launch_stem(c->d_in, c->in_u8 ? 1 : 0, c->layers[0].tab[4], L.w, L.epi, n, c->mode, c->bufs[d.dst_buf], out2, nullptr, s);
         if (L.tc) return ffcu_tc_launch(L.tc, n, c->mode, L.epi, res, acc_dbg, c->bufs[d.dst_buf], out2, c->d_err, s);
         return ffcu_launch_conv_simt(d, n, c->mode, c->bufs[d.src_buf], L.w, L.epi, res, acc_dbg, c->bufs[d.dst_buf], out2, s);
     }
@@ -321,7 +323,7 @@ static int launch_forward(ffcu_ctx* c, int n)
 static int run_forward(ffcu_ctx* c, int n, int slot)
 {
     if (n > c->graph_max_batch) return launch_forward(c, n);
-    const long long key = ((long long)n << 8) | ((long long)c->mode << 4) | slot;
+    const long long key = ((long long)n << 8) | ((long long)c->mode << 4) | (c->in_u8 ? 2 : 0) | slot;
     auto it = c->graphs.find(key);
     if (it != c->graphs.end()) {
         FFCU_CHECK(cudaGraphLaunch(it->second, c->stream));
@@ -353,7 +355,7 @@ static int run_forward(ffcu_ctx* c, int n, int slot)
     return 0;
 }
 
-extern "C" int ffcu_submit(ffcu_ctx* c, const float* host_in, int n, float* host_out)
+static int submit_impl(ffcu_ctx* c, const void* host_in, size_t bytes_per_face, bool u8, int n, float* host_out)
 {
     if (!c || !c->finalized || !host_in || !host_out || n < 1 || n > c->max_batch) {
         ffcu_set_error("ffcu_submit: bad arguments");
@@ -364,13 +366,15 @@ extern "C" int ffcu_submit(ffcu_ctx* c, const float* host_in, int n, float* host
     const bool reused = c->seq >= 2;
     // copy-in stream: the slot is free once the forward that last read it has finished
     if (reused) FFCU_CHECK(cudaStreamWaitEvent(c->s_in, c->ev_compute_done[slot], 0));
-    FFCU_CHECK(cudaMemcpyAsync(c->in_slot[slot], host_in, (size_t)n * 37632 * sizeof(float), cudaMemcpyHostToDevice, c->s_in));
+    FFCU_CHECK(cudaMemcpyAsync(c->in_slot[slot], host_in, (size_t)n * bytes_per_face, cudaMemcpyHostToDevice, c->s_in));
     FFCU_CHECK(cudaEventRecord(c->ev_in_ready[slot], c->s_in));
     // compute stream: needs the input, and the output slot drained by the copy-out of two steps ago
     FFCU_CHECK(cudaStreamWaitEvent(c->stream, c->ev_in_ready[slot], 0));
     if (reused) FFCU_CHECK(cudaStreamWaitEvent(c->stream, c->ev_out_copied[slot], 0));
     c->d_in = c->in_slot[slot]; c->d_out = c->out_slot[slot];
+    c->in_u8 = u8;
     int rc = run_forward(c, n, slot);
+    c->in_u8 = false;
     if (rc != 0) return rc;
     FFCU_CHECK(cudaEventRecord(c->ev_compute_done[slot], c->stream));
     // copy-out stream
@@ -379,6 +383,16 @@ extern "C" int ffcu_submit(ffcu_ctx* c, const float* host_in, int n, float* host
     FFCU_CHECK(cudaEventRecord(c->ev_out_copied[slot], c->s_out));
     c->seq++;
     return 0;
+}
+
+extern "C" int ffcu_submit(ffcu_ctx* c, const float* host_in, int n, float* host_out)
+{
+    return submit_impl(c, host_in, 37632 * sizeof(float), false, n, host_out);
+}
+
+extern "C" int ffcu_submit_u8(ffcu_ctx* c, const uint8_t* host_pixels, int n, float* host_out)
+{
+    return submit_impl(c, host_pixels, 37632, true, n, host_out);
 }
 
 extern "C" int ffcu_wait(ffcu_ctx* c)

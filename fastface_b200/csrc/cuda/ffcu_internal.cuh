@@ -143,7 +143,7 @@ int ffcu_launch_conv_simt(const ffcu_layer& L, int batch, int mode, const int8_t
                           int8_t* out_bn2, cudaStream_t s);
 // Fused stem: fp32 input -> per-channel int8 quantise -> conv3x3 3->64 -> epilogue (+BN second output).
 // q_out (optional) receives the quantised input as 4-byte pixels.
-int ffcu_launch_stem(const float* in_f32, const float* inv3, const int8_t* w, const EpiTables& t, int batch,
+int ffcu_launch_stem(const void* in_any, int in_u8, const float* inv3, const int8_t* w, const EpiTables& t, int batch,
                      int mode, int8_t* out, int8_t* out_bn2, int8_t* q_out, cudaStream_t s);
 int ffcu_launch_bn(const int8_t* in, int8_t* out, size_t n_pos, int C, const float* in_scale,
                    const float* bn_scale, const float* bn_offset, const float* inv_out, cudaStream_t s);

@@ -252,8 +252,8 @@ int ffcu_launch_fc_simt(const int8_t* act, const int8_t* w, const float* w_scale
 // ---------------------------------------------------------------------------
 #define STEM_T 16
 #define STEM_THREADS 128           // each thread computes two pixels (rows ty and ty + 8 of the tile)
-template <bool CONTRACT, bool HAS_SLOPE, bool HAS_BN2, bool CHECK>
-__global__ void __launch_bounds__(STEM_THREADS) stem_kernel(const float* __restrict__ in, const float* __restrict__ inv3,
+template <bool CONTRACT, bool HAS_SLOPE, bool HAS_BN2, bool CHECK, bool IN_U8>
+__global__ void __launch_bounds__(STEM_THREADS) stem_kernel(const void* __restrict__ in_any, const float* __restrict__ inv3,
                                                             const int8_t* __restrict__ w, EpiTables t,
                                                             int8_t* __restrict__ out, int8_t* __restrict__ out2,
                                                             int* __restrict__ q_out)
@@ -271,10 +271,22 @@ __global__ void __launch_bounds__(STEM_THREADS) stem_kernel(const float* __restr
         int py = y0 - 1 + i / P, px = x0 - 1 + i % P;
         int v = 0;
         if (py >= 0 && py < H && px >= 0 && px < W) {
-            const float* x = in + (((size_t)b * H + py) * W + px) * 3;
-            int q0 = max(-128, min(127, __float2int_rn(__fmul_rn(__ldg(x), i0))));
-            int q1 = max(-128, min(127, __float2int_rn(__fmul_rn(__ldg(x + 1), i1))));
-            int q2 = max(-128, min(127, __float2int_rn(__fmul_rn(__ldg(x + 2), i2))));
+            const size_t e = (((size_t)b * H + py) * W + px) * 3;
+            float f0, f1, f2;
+            if (IN_U8) {
+                // 8-bit pixels: the value the reference's wrapper feeds, (p - 127.5) / 127.5 in fp32
+                // (fastface.py:11), formed here with the same two roundings
+                const uint8_t* x = (const uint8_t*)in_any + e;
+                f0 = __fdiv_rn(__fsub_rn((float)__ldg(x), 127.5f), 127.5f);
+                f1 = __fdiv_rn(__fsub_rn((float)__ldg(x + 1), 127.5f), 127.5f);
+                f2 = __fdiv_rn(__fsub_rn((float)__ldg(x + 2), 127.5f), 127.5f);
+            } else {
+                const float* x = (const float*)in_any + e;
+                f0 = __ldg(x); f1 = __ldg(x + 1); f2 = __ldg(x + 2);
+            }
+            int q0 = max(-128, min(127, __float2int_rn(__fmul_rn(f0, i0))));
+            int q1 = max(-128, min(127, __float2int_rn(__fmul_rn(f1, i1))));
+            int q2 = max(-128, min(127, __float2int_rn(__fmul_rn(f2, i2))));
             v = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16);
         }
         s_in[i] = v;
@@ -351,14 +363,19 @@ __global__ void __launch_bounds__(STEM_THREADS) stem_kernel(const float* __restr
     }
 }
 
-int ffcu_launch_stem(const float* in_f32, const float* inv3, const int8_t* w, const EpiTables& t, int batch,
+int ffcu_launch_stem(const void* in_any, int in_u8, const float* inv3, const int8_t* w, const EpiTables& t, int batch,
                      int mode, int8_t* out, int8_t* out_bn2, int8_t* q_out, cudaStream_t s)
 {
     dim3 grid(112 / STEM_T, 112 / STEM_T, batch);
     const bool sl = t.slope != nullptr, bn = (out_bn2 != nullptr) && (t.bn_lut != nullptr);
 #define STEM_GO(C_, S_, B_) do { \
-        if (t.no_overflow) stem_kernel<C_, S_, B_, false><<<grid, STEM_THREADS, 0, s>>>(in_f32, inv3, w, t, out, out_bn2, (int*)q_out); \
-        else               stem_kernel<C_, S_, B_, true><<<grid, STEM_THREADS, 0, s>>>(in_f32, inv3, w, t, out, out_bn2, (int*)q_out); } while (0)
+        if (in_u8) { \
+            if (t.no_overflow) stem_kernel<C_, S_, B_, false, true><<<grid, STEM_THREADS, 0, s>>>(in_any, inv3, w, t, out, out_bn2, (int*)q_out); \
+            else               stem_kernel<C_, S_, B_, true, true><<<grid, STEM_THREADS, 0, s>>>(in_any, inv3, w, t, out, out_bn2, (int*)q_out); \
+        } else { \
+            if (t.no_overflow) stem_kernel<C_, S_, B_, false, false><<<grid, STEM_THREADS, 0, s>>>(in_any, inv3, w, t, out, out_bn2, (int*)q_out); \
+            else               stem_kernel<C_, S_, B_, true, false><<<grid, STEM_THREADS, 0, s>>>(in_any, inv3, w, t, out, out_bn2, (int*)q_out); \
+        } } while (0)
     if (mode) {
         if (sl && bn) STEM_GO(true, true, true); else if (sl) STEM_GO(true, true, false);
         else if (bn) STEM_GO(true, false, true); else STEM_GO(true, false, false);

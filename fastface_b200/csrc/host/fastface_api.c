@@ -144,6 +144,7 @@ void fastface_destroy(FastFace* ff)
 /* one device's share of a batch, in steps of max_batch */
 typedef struct {
     ffcu_ctx* ctx; const float* in; float* out; int n; int max_batch; int rc;
+    const uint8_t* in_u8;      /* non-NULL: 8-bit pixel input instead of `in` */
 } dev_job;
 
 static void* dev_job_run(void* arg)
@@ -152,8 +153,9 @@ static void* dev_job_run(void* arg)
     j->rc = 0;
     for (int done = 0; done < j->n; ) {
         int step = j->n - done < j->max_batch ? j->n - done : j->max_batch;
-        int rc = ffcu_submit(j->ctx, j->in + (size_t)done * FASTFACE_INPUT_N, step,
-                             j->out + (size_t)done * FASTFACE_OUTPUT_N);
+        int rc = j->in_u8
+            ? ffcu_submit_u8(j->ctx, j->in_u8 + (size_t)done * FASTFACE_INPUT_N, step, j->out + (size_t)done * FASTFACE_OUTPUT_N)
+            : ffcu_submit(j->ctx, j->in + (size_t)done * FASTFACE_INPUT_N, step, j->out + (size_t)done * FASTFACE_OUTPUT_N);
         if (rc != 0) { j->rc = rc; break; }
         done += step;
     }
@@ -174,17 +176,31 @@ int fastface_shard_plan(int n, int n_devices, int* starts, int* counts)
     return used;
 }
 
+static int embed_batch_any(FastFace* ff, const float* input_hwc, const uint8_t* pixels_hwc, int n, float* out_emb);
+
 int fastface_embed_batch(FastFace* ff, const float* input_hwc, int n, float* out_emb)
 {
     if (!ff || !input_hwc || !out_emb || n < 1) return -1;
+    return embed_batch_any(ff, input_hwc, NULL, n, out_emb);
+}
+
+int fastface_embed_batch_u8(FastFace* ff, const uint8_t* pixels_hwc, int n, float* out_emb)
+{
+    if (!ff || !pixels_hwc || !out_emb || n < 1) return -1;
+    return embed_batch_any(ff, NULL, pixels_hwc, n, out_emb);
+}
+
+static int embed_batch_any(FastFace* ff, const float* input_hwc, const uint8_t* pixels_hwc, int n, float* out_emb)
+{
     g_api_err[0] = 0;
     dev_job jobs[FF_MAX_DEVICES];
     pthread_t th[FF_MAX_DEVICES];
     int starts[FF_MAX_DEVICES], counts[FF_MAX_DEVICES];
     int used = fastface_shard_plan(n, ff->n_dev, starts, counts);
     for (int d = 0; d < used; d++)
-        jobs[d] = (dev_job){ ff->dev[d], input_hwc + (size_t)starts[d] * FASTFACE_INPUT_N,
-                             out_emb + (size_t)starts[d] * FASTFACE_OUTPUT_N, counts[d], ff->max_batch, 0 };
+        jobs[d] = (dev_job){ ff->dev[d], input_hwc ? input_hwc + (size_t)starts[d] * FASTFACE_INPUT_N : NULL,
+                             out_emb + (size_t)starts[d] * FASTFACE_OUTPUT_N, counts[d], ff->max_batch, 0,
+                             pixels_hwc ? pixels_hwc + (size_t)starts[d] * FASTFACE_INPUT_N : NULL };
     if (used == 1) {
         dev_job_run(&jobs[0]);
     } else {

@@ -22,6 +22,8 @@
 #ifndef FASTFACE_H
 #define FASTFACE_H
 
+#include <stdint.h>
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -61,6 +63,14 @@ FastFace* fastface_create_ex(const char* ffw4_path, const int* device_ids, int n
  * n >= 1: faces are split into contiguous chunks across the context's devices
  * and into steps of at most max_batch per device. */
 int fastface_embed_batch(FastFace* ff, const float* input_hwc, int n, float* out_emb);
+
+/* The same from 8-bit pixels, contiguous [n][112][112][3] uint8 (channel order as the fp32 entry).
+ * No counterpart in the reference's C API: its callers normalise on the host,
+ * x = (p - 127.5) / 127.5 in fp32 (fastface.py:11), and pass fp32.  This entry does that
+ * normalisation on the device with the same two fp32 roundings, so the embeddings are bit for
+ * bit those of fastface_embed_batch on the normalised floats, while a quarter of the input bytes
+ * cross PCIe. */
+int fastface_embed_batch_u8(FastFace* ff, const uint8_t* pixels_hwc, int n, float* out_emb);
 
 /* How fastface_embed_batch splits n faces over n_devices: contiguous chunks of
  * ceil(n / n_devices) faces (the last may be shorter; devices beyond the data get none).

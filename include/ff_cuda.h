@@ -88,6 +88,11 @@ int ffcu_set_mode(ffcu_ctx* c, int mode);
  * returns 0 or the device error word.  Takes over the op loop of
  * arcface_forward_int8_batched.c:339-516. */
 int ffcu_submit(ffcu_ctx* c, const float* host_in, int n, float* host_out);
+/* Same forward from 8-bit pixels [n][112][112][3]: the fused stem forms (p - 127.5f) / 127.5f in
+ * fp32 (the value the reference's wrapper computes on the host, fastface.py:11) and quantises it as
+ * quantize_fp32_nhwc_to_int8 does (kernels/int8_epilogue.c:231-247).  A quarter of the bytes
+ * cross PCIe.  Needs the fused stem (the default). */
+int ffcu_submit_u8(ffcu_ctx* c, const uint8_t* host_pixels, int n, float* host_out);
 int ffcu_wait(ffcu_ctx* c);
 
 /* Same forward with dump points; fn is called on the host after each layer. */

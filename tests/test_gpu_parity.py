@@ -347,6 +347,26 @@ def test_embed_and_embed_batch_agree_with_oracle(engine, oracle):
     assert ff.FastFace.cos_sim(got[0], want[0]) >= 0.99999
 
 
+def test_uint8_pixel_entry_point(engine, oracle):
+    """fastface_embed_batch_u8 normalises 8-bit pixels on the device exactly as the reference's wrapper
+    does on the host ((p - 127.5) / 127.5 in fp32, fastface.py:11): the embeddings must be bit for bit
+    those of the fp32 entry on the normalised floats, and of the oracle."""
+    rng = np.random.default_rng(11)
+    pix = rng.integers(0, 256, size=(5, 112, 112, 3), dtype=np.uint8)
+    pix[0, :2] = 0
+    pix[0, 2:4] = 255                                   # the range ends
+    x = ((pix.astype(np.float32) - np.float32(127.5)) / np.float32(127.5)).astype(np.float32)
+    e_u8 = engine.embed_batch_u8(pix)
+    e_f32 = engine.embed_batch(x)
+    assert np.array_equal(e_u8.view(np.uint32), e_f32.view(np.uint32))
+    want = oracle.forward(x, ffo.CONTRACT)
+    assert np.array_equal(e_u8.view(np.uint32), want.view(np.uint32))
+    one = engine.embed_batch_u8(pix[3:4])               # batch 1 goes through the CUDA-graph path on its third call
+    for _ in range(3):
+        one = engine.embed_batch_u8(pix[3:4])
+    assert np.array_equal(one[0].view(np.uint32), e_u8[3].view(np.uint32))
+
+
 def test_fc_paths(built_lib, model_root, ffw4, oracle, monkeypatch):
     """The FC runs as a split-K CUDA-core kernel for batch <= 16 and on the tensor cores above;
     both match the reference's matvec, and FF_FC_SMALL=0 sends a small batch down the large path."""

@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol(built_lib):
     lib = C.CDLL(built_lib)
     declared = _declared_symbols()
     assert {"fastface_create", "fastface_embed", "fastface_destroy", "fastface_embed_batch",
-            "fastface_cos_sim", "ffcu_submit", "ffcu_conv_once"} <= declared
+            "fastface_embed_batch_u8", "fastface_cos_sim", "ffcu_submit", "ffcu_submit_u8", "ffcu_conv_once"} <= declared
     for name in sorted(declared):
         assert hasattr(lib, name), f"{name} is declared in include/ but not exported"
 
@@ -37,6 +37,7 @@ def test_null_arguments(built_lib):
     # reference: embed returns -1 on NULL arguments (libfastface.c:313), destroy(NULL) is a no-op (:473)
     assert lib.fastface_embed(None, buf.ctypes.data, out.ctypes.data) == -1
     assert lib.fastface_embed_batch(None, buf.ctypes.data, 1, out.ctypes.data) == -1
+    assert lib.fastface_embed_batch_u8(None, buf.ctypes.data, 1, out.ctypes.data) == -1
     lib.fastface_destroy(None)
     assert lib.fastface_create(None) is None
 
