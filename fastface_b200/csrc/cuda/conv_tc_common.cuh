@@ -279,6 +279,17 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr)
     return d;
 }
 
+// 32-byte rows with 32-byte swizzle (K = 32 operands: the stem's im2col rows), 8-row groups 256 B apart.
+__device__ __forceinline__ uint64_t smem_desc_sw32(uint32_t saddr)
+{
+    uint64_t d = (uint64_t)((saddr >> 4) & 0x3fff);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(256 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)6 << 61;                              // swizzle mode: 32 B
+    return d;
+}
+
 // Same with an explicit stride between 8-row groups.
 template <int ROWB>
 __device__ __forceinline__ uint64_t smem_desc_sbo(uint32_t saddr, uint32_t sbo_bytes)
@@ -324,7 +335,7 @@ struct TcParams {
 // compile time, which turns the per-element code into one straight-line block the scheduler
 // can interleave across elements (the run-time form branches per element and runs several
 // times slower).
-enum { EPI_RUNTIME = 0, EPI_PLAIN = 1, EPI_SLOPE = 2, EPI_RES_BN = 3, EPI_RES = 4 };
+enum { EPI_RUNTIME = 0, EPI_PLAIN = 1, EPI_SLOPE = 2, EPI_RES_BN = 3, EPI_RES = 4, EPI_SLOPE_BN = 5 };
 
 #define TC_MAX_STAGES 8
 #define TC_MAX_ABUF 4
@@ -414,8 +425,8 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
 {
     constexpr int NG = CW / 4;                            // groups of four channels
     const bool has_res = (EPI == EPI_RUNTIME) ? rt_res : (EPI == EPI_RES_BN || EPI == EPI_RES);
-    const bool has_slope = (EPI == EPI_RUNTIME) ? rt_slope : (EPI == EPI_SLOPE);
-    const bool has_bn2 = (EPI == EPI_RUNTIME) ? rt_bn2 : (EPI == EPI_RES_BN);
+    const bool has_slope = (EPI == EPI_RUNTIME) ? rt_slope : (EPI == EPI_SLOPE || EPI == EPI_SLOPE_BN);
+    const bool has_bn2 = (EPI == EPI_RUNTIME) ? rt_bn2 : (EPI == EPI_RES_BN || EPI == EPI_SLOPE_BN);
     if (p.acc_out) {                                      // dump-point mode: raw accumulators
 #pragma unroll
         for (int g = 0; g < CW / 8; g++) {
@@ -695,6 +706,8 @@ int tc_launch_generic(int bn, int kc, int mode, int epi, bool f32, int grid, int
                       const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
 int tc_launch_shift(int bn, int mode, int epi, int grid, int smem, cudaStream_t s,
                     const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
+int tc_launch_k32(int mode, int epi, int grid, int smem, cudaStream_t s,
+                  const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
 int tc_launch_ws(int bn, int mode, int epi, int grid, int smem, cudaStream_t s,
                  const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
 int tc_launch_pair(int bn, int mode, int epi, bool f32, int grid, int smem, cudaStream_t s,

@@ -160,6 +160,14 @@ int ffcu_launch_fc_small(const int8_t* act, const int8_t* w, const float* w_scal
 // ---------------------------------------------------------------------------
 struct TcPlan;   // opaque: tile shape, TMA descriptors, launch geometry for one layer
 // NULL when the layer shape is not covered by the tensor-core kernel.
+int ffcu_launch_stem_pack(const void* in_any, int in_u8, const float* inv3, int batch, int8_t* col, cudaStream_t s);
+int ffcu_stem_weight_k32(const int8_t* d_w, int8_t* d_wk, int Cout, cudaStream_t s);
+// Tensor-core stem: plan over the im2col buffer d_col [max_batch * 12544][32] and the repacked weights d_wk [64][32]
+struct StemTcPlan;
+StemTcPlan* ffcu_stem_tc_plan(int max_batch, const int8_t* d_col, const int8_t* d_wk, bool has_bn2, int device);
+void ffcu_stem_tc_free(StemTcPlan* p);
+int ffcu_stem_tc_launch(const StemTcPlan* p, int batch, int mode, const EpiTables& t, int8_t* out, int8_t* out_bn2,
+                        int* d_err, cudaStream_t s);
 TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, const int8_t* d_w, int device);
 void    ffcu_tc_free(TcPlan* p);
 int     ffcu_tc_launch(const TcPlan* p, int batch, int mode, const EpiTables& t, const int8_t* res,

@@ -171,7 +171,8 @@ def test_unfused_plan_agrees(built_lib, model_root, ffw4, oracle, monkeypatch):
     monkeypatch.setenv("FF_FUSE_STEM", "0")
     with ff.FastFace(ffw4, cwd=model_root, max_batch=3) as e:
         assert np.array_equal(e.embed_batch(faces), want)
-        assert e.launches_per_forward == 81 and n_fused == 55   # + the FC finish kernel at batch <= 16
+        # fused: 1 + 1 stem (pack pass + K = 32 GEMM), 52 convs, FC + its finish kernel at batch <= 16
+        assert e.launches_per_forward == 81 and n_fused == 56
 
 
 @pytest.mark.parametrize("case", LAYER_CASES[:4], ids=lambda c: c[0])
@@ -365,6 +366,22 @@ def test_uint8_pixel_entry_point(engine, oracle):
     for _ in range(3):
         one = engine.embed_batch_u8(pix[3:4])
     assert np.array_equal(one[0].view(np.uint32), e_u8[3].view(np.uint32))
+
+
+def test_stem_on_cuda_cores_agrees(built_lib, model_root, ffw4, oracle, monkeypatch):
+    """FF_STEM_TC=0 runs the stem as the fused dp4a kernel instead of the pack pass + K = 32 tensor-core
+    GEMM; both give the oracle's bytes, from fp32 and from 8-bit pixel input."""
+    faces = synth.faces(3, seed=21)
+    want = oracle.forward(faces, ffo.CONTRACT)
+    pix = np.random.default_rng(3).integers(0, 256, size=(3, 112, 112, 3), dtype=np.uint8)
+    x = ((pix.astype(np.float32) - np.float32(127.5)) / np.float32(127.5)).astype(np.float32)
+    want_u8 = oracle.forward(x, ffo.CONTRACT)
+    for flag in ("1", "0"):
+        monkeypatch.setenv("FF_STEM_TC", flag)
+        with ff.FastFace(ffw4, cwd=model_root, max_batch=3) as e:
+            assert np.array_equal(e.embed_batch(faces), want), f"FF_STEM_TC={flag}"
+            assert np.array_equal(e.embed_batch_u8(pix), want_u8), f"FF_STEM_TC={flag}, uint8 input"
+            assert e.launches_per_forward == (56 if flag == "1" else 55)
 
 
 def test_fc_paths(built_lib, model_root, ffw4, oracle, monkeypatch):
