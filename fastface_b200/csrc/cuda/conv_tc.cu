@@ -221,6 +221,13 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
 
 void ffcu_tc_free(TcPlan* p) { delete p; }
 
+static int tc_issuers()
+{
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("FF_TC_ISSUERS"); v = (e && atoi(e) == 2) ? 2 : 1; }
+    return v;
+}
+
 int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, const int8_t* res,
                    int32_t* acc_out, void* out, int8_t* out_bn2, int* d_err, cudaStream_t s)
 {
@@ -244,7 +251,7 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
         prm.TW = WS_TW; prm.TH = WS_TH; prm.TB = 1;
         prm.tiles_w = d.Wo / WS_TW; prm.tiles_h = (d.Ho + WS_TH - 1) / WS_TH; prm.tiles_b = batch; prm.tiles_n = 1;
         prm.total_tiles = prm.tiles_w * prm.tiles_h * batch;
-        prm.stages = p->ws_stages; prm.group = 1; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab;
+        prm.stages = p->ws_stages; prm.group = 1; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab; prm.issuers = tc_issuers();
         int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
         return tc_launch_ws(p->BN, mode, epi, grid, p->ws_smem_bytes, s, p->mapA_ws, p->mapB, prm);
     }
@@ -258,7 +265,7 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
         prm.tiles_w = 1; prm.tiles_h = (d.Ho + p->shift_TR - 1) / p->shift_TR; prm.tiles_b = batch;
         prm.tiles_n = d.Cout / p->BN;
         prm.total_tiles = prm.tiles_h * batch * prm.tiles_n;
-        prm.stages = p->shift_stages; prm.group = p->shift_group; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab;
+        prm.stages = p->shift_stages; prm.group = p->shift_group; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab; prm.issuers = tc_issuers();
         prm.na = p->shift_na; prm.a_stride = p->shift_a_stride;
         const int m_tiles = prm.tiles_h * batch;
         const int pairs = prm.tiles_n * ((m_tiles + 1) / 2);
@@ -289,7 +296,7 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
     prm.tiles_w = (d.Wo + TW - 1) / TW; prm.tiles_h = (d.Ho + TH - 1) / TH; prm.tiles_b = (batch + TB - 1) / TB;
     prm.tiles_n = d.Cout / p->BN;
     prm.total_tiles = prm.tiles_w * prm.tiles_h * prm.tiles_b * prm.tiles_n;
-    prm.stages = p->stages; prm.group = p->group; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab;
+    prm.stages = p->stages; prm.group = p->group; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab; prm.issuers = tc_issuers();
     { const char* e = getenv("FF_TC_STAGES"); if (e && atoi(e) >= 2 && atoi(e) < prm.stages) prm.stages = atoi(e); }
     if (p->pair) {
         const int m_tiles = prm.tiles_w * prm.tiles_h * prm.tiles_b;

@@ -326,6 +326,7 @@ struct TcParams {
     int stages;
     int lut_bytes;           // shared-memory bytes of the fused BN's table (BN * 256, or 0)
     int group;               // K blocks per pipeline stage (one barrier hand-shake per `group` blocks)
+    int issuers;             // MMA issuer warps that take alternate tiles (1 or 2; 2 needs a ring of >= two tiles' stages)
     int ntab;                // per-channel tables held in shared memory: 5, or 9 when the fused BN is computed arithmetically
     int na, a_stride;        // tap-shift kernel: activation-slice buffers in the ring, bytes per buffer
     int dbg;                 // timing experiments only ($FF_TC_DBG): bit 0 = skip the TMA loads, bit 1 = skip the MMAs, bit 2 = no global memory in the epilogue, bit 3 = no epilogue arithmetic

@@ -82,21 +82,27 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 }
             }
         }
-    } else if (warp == 1) {
-        {
+    } else if (warp == 1 || warp == TC_ISSUER2_WARP) {
+        const int G = p.group;
+        const int n_steps = kblocks / G;
+        // With p.issuers == 2 and a ring that holds two tiles' stages, two issuer warps take alternate tiles.
+        const bool two = p.issuers == 2 && p.stages >= 2 * n_steps;
+        const int me = (warp == 1) ? 0 : 1;
+        if (me == 0 || two) {
             // MMA issuer: the warp loops and waits together, lane 0 issues
+            const int lstep = two ? 2 : 1;
+            const int skip = two ? n_steps : 0;          // stages of the other issuer's tile between two of mine
             int stage = 0; uint32_t phase = 0;
-            int local = 0;
+            { int adv = me * n_steps; while (adv >= p.stages) { adv -= p.stages; phase ^= 1; } stage = adv; }
+            int local = me;
             bool ok = true;
-            const int G = p.group;
-            const int n_steps = kblocks / G;
             const int stage_bytes = G * SUB_BYTES;
             const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
             const uint64_t da0 = smem_desc<KC>(smem_u32(smem));
             const uint64_t db0 = smem_desc<KC>(smem_u32(smem) + A_BYTES);
             const uint32_t leader = (lane == 0) ? 1u : 0u;
             uint32_t ready = 0;                          // answer of the early test for the upcoming stage
-            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, local++) {
+            for (int tile = blockIdx.x + me * gridDim.x; tile < p.total_tiles && ok; tile += lstep * gridDim.x, local += lstep) {
                 const int a = local % TC_NACC(BN);
                 const uint32_t aphase = (uint32_t)(local / TC_NACC(BN)) & 1;
                 ok = mbar_wait(smem_u32(&sh->acc_empty[a]), aphase ^ 1, abort_flag, p.err, FFCU_ERR_TMEM_TIMEOUT);
@@ -108,9 +114,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         ok = mbar_wait(full0 + stage * 8, phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
                         if (!ok) break;
                     }
-                    // test the next stage's barrier now, use the answer next round
-                    int ns = stage + 1; uint32_t np = phase;
-                    if (ns == p.stages) { ns = 0; np ^= 1; }
+                    // test this issuer's next stage now, use the answer next round (after a tile's last step
+                    // it lies beyond the other issuer's tile)
+                    int ns = stage + ((it + 1 < n_steps) ? 1 : 1 + skip); uint32_t np = phase;
+                    while (ns >= p.stages) { ns -= p.stages; np ^= 1; }
                     ready = mbar_test(full0 + ns * 8, np);
                     tc_fence_after();
                     {

@@ -218,6 +218,24 @@ def test_fused_bn_by_arithmetic(built_lib, case, monkeypatch):
     assert not msg, msg
 
 
+@pytest.mark.parametrize("case", [LAYER_CASES[4], LAYER_CASES[9], LAYER_CASES[13]], ids=lambda c: c[0])
+def test_two_issuer_warps_option(built_lib, case, monkeypatch):
+    """FF_TC_ISSUERS=2 lets two warps issue the MMAs of alternate tiles in the per-tap kernels (an option that
+    measured no faster there; the weight-stationary and stem kernels always use two).  Same bytes."""
+    monkeypatch.setenv("FF_TC_ISSUERS", "2")
+    name, B, H, Cin, Cout, k, stride, sl, rs = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()) + 13)
+    L = random_layer(rng, B * 3, H, Cin, Cout, k, stride, sl, rs)
+    acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
+                            slope=L["slope"], res=L["res"], res_scale=L["rs"], impl="tc")
+    acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
+                               L["res"], L["rs"], ffo.CONTRACT)
+    msg = describe_mismatch("int32 accumulators", acc, acc_o)
+    assert not msg, msg
+    msg = describe_mismatch("int8 output", out, out_o)
+    assert not msg, msg
+
+
 @pytest.mark.parametrize("case", LAYER_CASES[4:8], ids=lambda c: c[0])
 def test_tap_shift_kernel(built_lib, case, monkeypatch):
     """FF_TC_SHIFT=1 routes the 3x3 stride-1 layers on 14x14 / 28x28 maps through the CTA-pair
