@@ -46,6 +46,9 @@ struct TcPlan {
     bool ws;                 // weight-stationary kernel (64-channel 3x3 stride-1 layers)
     CUtensorMap mapA_ws;     // box {64, 8, 18, 1}
     int ws_stages, ws_smem_bytes;
+    bool ws2;                // its CTA-pair form (cta_group::2): half the weights per CTA, one MMA per two tiles
+    CUtensorMap mapB_ws_half; // box {64, BN/2, 1, 1}
+    int ws2_stages, ws2_smem_bytes;
 };
 
 // Output-tile shape {TW, TH, TB} with TW*TH*TB = 128 that wastes the fewest rows for this
@@ -214,6 +217,20 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
             int st = (232448 - wbytes - fixed) / WS_A_BYTES;
             if (st > TC_MAX_STAGES) st = TC_MAX_STAGES;
             if (st >= 2) { p->ws = true; p->ws_stages = st; p->ws_smem_bytes = wbytes + st * WS_A_BYTES + fixed; }
+            // CTA-pair form
+            const char* w2 = getenv("FF_TC_WS2");
+            p->ws2 = false;
+            if (p->ws && w2 && w2[0] == '1') {          // opt-in: measured no faster than the one-CTA form
+                cuuint32_t hbox[4] = {64, (cuuint32_t)(p->BN / 2), 1, 1};
+                CUresult r2 = enc(&p->mapB_ws_half, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d_w, dims, strides, hbox, estr,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                int st2 = (232448 - wbytes / 2 - fixed) / WS_A_BYTES;
+                if (st2 > TC_MAX_STAGES) st2 = TC_MAX_STAGES;
+                if (r2 == CUDA_SUCCESS && st2 >= 2) {
+                    p->ws2 = true; p->ws2_stages = st2; p->ws2_smem_bytes = wbytes / 2 + st2 * WS_A_BYTES + fixed;
+                }
+            }
         }
     }
     return p;
@@ -252,6 +269,12 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
         prm.tiles_w = d.Wo / WS_TW; prm.tiles_h = (d.Ho + WS_TH - 1) / WS_TH; prm.tiles_b = batch; prm.tiles_n = 1;
         prm.total_tiles = prm.tiles_w * prm.tiles_h * batch;
         prm.stages = p->ws_stages; prm.group = 1; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab; prm.issuers = tc_issuers();
+        if (p->ws2) {
+            const int pairs = (prm.total_tiles + 1) / 2, max_pairs = p->n_sm / 2;
+            const int npairs = pairs < max_pairs ? pairs : max_pairs;
+            prm.stages = p->ws2_stages;
+            return tc_launch_ws2(p->BN, mode, epi, 2 * npairs, p->ws2_smem_bytes, s, p->mapA_ws, p->mapB_ws_half, prm);
+        }
         int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
         return tc_launch_ws(p->BN, mode, epi, grid, p->ws_smem_bytes, s, p->mapA_ws, p->mapB, prm);
     }

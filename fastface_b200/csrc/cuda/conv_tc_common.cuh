@@ -707,6 +707,8 @@ int tc_launch_generic(int bn, int kc, int mode, int epi, bool f32, int grid, int
                       const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
 int tc_launch_shift(int bn, int mode, int epi, int grid, int smem, cudaStream_t s,
                     const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
+int tc_launch_ws2(int bn, int mode, int epi, int grid, int smem, cudaStream_t s,
+                  const CUtensorMap& mapA, const CUtensorMap& mapB_half, const TcParams& prm);
 int tc_launch_k32(int mode, int epi, int grid, int smem, cudaStream_t s,
                   const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
 int tc_launch_ws(int bn, int mode, int epi, int grid, int smem, cudaStream_t s,

@@ -236,6 +236,25 @@ def test_two_issuer_warps_option(built_lib, case, monkeypatch):
     assert not msg, msg
 
 
+@pytest.mark.parametrize("case", LAYER_CASES[:4], ids=lambda c: c[0])
+def test_weight_stationary_pair_kernel(built_lib, case, monkeypatch):
+    """FF_TC_WS2=1 runs the 64-input-channel 3x3 stride-1 layers on the CTA-pair form of the
+    weight-stationary kernel (cta_group::2, half the weights per CTA); same bytes as the oracle,
+    including an odd number of tiles (the pair's second CTA then works on a tile past the batch)."""
+    monkeypatch.setenv("FF_TC_WS2", "1")
+    name, B, H, Cin, Cout, k, stride, sl, rs = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()) + 17)
+    L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
+    acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
+                            slope=L["slope"], res=L["res"], res_scale=L["rs"], impl="tc")
+    acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
+                               L["res"], L["rs"], ffo.CONTRACT)
+    msg = describe_mismatch("int32 accumulators", acc, acc_o)
+    assert not msg, msg
+    msg = describe_mismatch("int8 output", out, out_o)
+    assert not msg, msg
+
+
 @pytest.mark.parametrize("case", LAYER_CASES[4:8], ids=lambda c: c[0])
 def test_tap_shift_kernel(built_lib, case, monkeypatch):
     """FF_TC_SHIFT=1 routes the 3x3 stride-1 layers on 14x14 / 28x28 maps through the CTA-pair
