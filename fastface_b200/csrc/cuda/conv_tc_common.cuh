@@ -326,6 +326,7 @@ struct TcParams {
     int stages;
     int lut_bytes;           // shared-memory bytes of the fused BN's table (BN * 256, or 0)
     int group;               // K blocks per pipeline stage (one barrier hand-shake per `group` blocks)
+    int x2;                  // contract-mode epilogue with two-lane fp32 instructions (fma / mul / add .f32x2)
     int issuers;             // MMA issuer warps that take alternate tiles (1 or 2; 2 needs a ring of >= two tiles' stages)
     int ntab;                // per-channel tables held in shared memory: 5, or 9 when the fused BN is computed arithmetically
     int na, a_stride;        // tap-shift kernel: activation-slice buffers in the ring, bytes per buffer
@@ -459,12 +460,20 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
         const float4 rs = *(const float4*)&tab[3 * TC_MAX_COUT + cb + 4 * g];
         const float4 iv = *(const float4*)&tab[4 * TC_MAX_COUT + cb + 4 * g];
         const int r = rw[g];
+        int q0, q1, q2, q3;
+        if (CONTRACT && !CHECK && p.x2) {
+            ffcu_conv_q2(v[4 * g + 0], v[4 * g + 1], ws.x, ws.y, bi.x, bi.y, has_res, (int)(int8_t)(r & 0xff), (int)(int8_t)((r >> 8) & 0xff),
+                         rs.x, rs.y, has_slope, sl.x, sl.y, iv.x, iv.y, q0, q1);
+            ffcu_conv_q2(v[4 * g + 2], v[4 * g + 3], ws.z, ws.w, bi.z, bi.w, has_res, (int)(int8_t)((r >> 16) & 0xff), (int)(int8_t)((r >> 24) & 0xff),
+                         rs.z, rs.w, has_slope, sl.z, sl.w, iv.z, iv.w, q2, q3);
+        } else {
         float f0 = ffcu_conv_fp<CONTRACT>(v[4 * g + 0], ws.x, bi.x, has_res, (int)(int8_t)(r & 0xff), rs.x, has_slope, sl.x);
         float f1 = ffcu_conv_fp<CONTRACT>(v[4 * g + 1], ws.y, bi.y, has_res, (int)(int8_t)((r >> 8) & 0xff), rs.y, has_slope, sl.y);
         float f2 = ffcu_conv_fp<CONTRACT>(v[4 * g + 2], ws.z, bi.z, has_res, (int)(int8_t)((r >> 16) & 0xff), rs.z, has_slope, sl.z);
         float f3 = ffcu_conv_fp<CONTRACT>(v[4 * g + 3], ws.w, bi.w, has_res, (int)(int8_t)((r >> 24) & 0xff), rs.w, has_slope, sl.w);
-        int q0 = ffcu_requant_nosat<CHECK>(f0, iv.x), q1 = ffcu_requant_nosat<CHECK>(f1, iv.y);
-        int q2 = ffcu_requant_nosat<CHECK>(f2, iv.z), q3 = ffcu_requant_nosat<CHECK>(f3, iv.w);
+        q0 = ffcu_requant_nosat<CHECK>(f0, iv.x); q1 = ffcu_requant_nosat<CHECK>(f1, iv.y);
+        q2 = ffcu_requant_nosat<CHECK>(f2, iv.z); q3 = ffcu_requant_nosat<CHECK>(f3, iv.w);
+        }
         ow_[g] = ffcu_pack4(q0, q1, q2, q3);
         if (has_bn2 && !p.lut_bytes) {
             // BN of the four int8 results by arithmetic (the wide tiles: their byte tables would take 32 - 64 KB

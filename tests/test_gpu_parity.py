@@ -236,6 +236,22 @@ def test_two_issuer_warps_option(built_lib, case, monkeypatch):
     assert not msg, msg
 
 
+@pytest.mark.parametrize("case", [LAYER_CASES[0], LAYER_CASES[2], LAYER_CASES[6], LAYER_CASES[13]], ids=lambda c: c[0])
+def test_two_lane_fp32_epilogue_option(built_lib, case, monkeypatch):
+    """FF_TC_X2=1 evaluates the contract-mode epilogue with fma / mul / add .f32x2 (two channels per
+    instruction, each lane the same IEEE operation); same bytes as the oracle."""
+    monkeypatch.setenv("FF_TC_X2", "1")
+    name, B, H, Cin, Cout, k, stride, sl, rs = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()) + 19)
+    L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
+    acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
+                            slope=L["slope"], res=L["res"], res_scale=L["rs"], impl="tc")
+    acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
+                               L["res"], L["rs"], ffo.CONTRACT)
+    msg = describe_mismatch("int8 output", out, out_o)
+    assert not msg, msg
+
+
 @pytest.mark.parametrize("case", LAYER_CASES[:4], ids=lambda c: c[0])
 def test_weight_stationary_pair_kernel(built_lib, case, monkeypatch):
     """FF_TC_WS2=1 runs the 64-input-channel 3x3 stride-1 layers on the CTA-pair form of the
