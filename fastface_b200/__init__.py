@@ -60,6 +60,8 @@ def load_library() -> C.CDLL:
     L.fastface_embed.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
     L.fastface_embed_batch.restype = C.c_int
     L.fastface_embed_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+    L.fastface_cos_sim_matrix.restype = C.c_int
+    L.fastface_cos_sim_matrix.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
     L.fastface_embed_batch_u8.restype = C.c_int
     L.fastface_embed_batch_u8.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
     L.fastface_destroy.restype = None
@@ -160,6 +162,16 @@ class FastFace:
         rc = self.lib.fastface_embed_batch_u8(self.h, _ptr(pixels), n, _ptr(out))
         if rc != 0:
             raise RuntimeError(f"fastface_embed_batch_u8 rc={rc}: " + self.lib.fastface_last_error().decode())
+
+    def cos_sim_matrix(self, a: np.ndarray, b: np.ndarray) -> np.ndarray:
+        """[n,512] x [m,512] -> [n,m] cosine similarities, the values cos_sim gives pair by pair."""
+        a = np.ascontiguousarray(a, dtype=np.float32).reshape(-1, EMB_DIM)
+        b = np.ascontiguousarray(b, dtype=np.float32).reshape(-1, EMB_DIM)
+        out = np.empty((a.shape[0], b.shape[0]), np.float32)
+        rc = self.lib.fastface_cos_sim_matrix(self.h, _ptr(a), a.shape[0], _ptr(b), b.shape[0], _ptr(out))
+        if rc != 0:
+            raise RuntimeError(f"fastface_cos_sim_matrix rc={rc}: " + self.lib.fastface_last_error().decode())
+        return out
 
     @staticmethod
     def cos_sim(a: np.ndarray, b: np.ndarray) -> float:

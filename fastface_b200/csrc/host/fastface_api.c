@@ -230,6 +230,12 @@ float fastface_cos_sim(const float* a, const float* b)
     return (float)(dot / (sqrt(na) * sqrt(nb)));
 }
 
+int fastface_cos_sim_matrix(const FastFace* ff, const float* a, int n, const float* b, int m, float* out)
+{
+    if (!ff || !a || !b || !out || n < 1 || m < 1) return -1;
+    return ffcu_cos_sim_matrix(ff->dev_id[0], a, n, b, m, out);
+}
+
 int fastface_set_epilogue_mode(FastFace* ff, int mode)
 {
     if (!ff || (mode != FF_EPILOGUE_STRICT && mode != FF_EPILOGUE_CONTRACT)) return -1;

@@ -81,6 +81,11 @@ int fastface_shard_plan(int n, int n_devices, int* starts, int* counts);
  * norm is 0 (reference go/fastface/fastface.go:157-168). */
 float fastface_cos_sim(const float* a, const float* b);
 
+/* All pairs at once: out[i * m + j] = fastface_cos_sim(a + 512 * i, b + 512 * j), computed on the
+ * context's first device with the same float64 arithmetic (bit-identical values).  The reference's
+ * consumers loop over pairs on the host (go/examples/findface/main.go, face_match.py). */
+int fastface_cos_sim_matrix(const FastFace* ff, const float* a, int n, const float* b, int m, float* out);
+
 /* fp32 evaluation order of the conv epilogue (see FF_EPILOGUE_* below);
  * default FF_EPILOGUE_CONTRACT, or $FF_EPILOGUE=strict|contract at create. */
 #define FF_EPILOGUE_STRICT   0  /* reference built with -ffp-contract=off            */

@@ -140,6 +140,10 @@ int ffcu_fc_small_noalloc(const int8_t* act, const int8_t* w, const float* w_sca
 /* Dense INT8 tensor-core throughput (TOP/s, 2 ops per MAC) measured with operands already in
  * shared memory: M=128, N=bn (64/128/256), all SMs busy, `iters` rounds of four K=32 MMAs.
  * The practical ceiling the convolution kernels are compared against. */
+/* Cosine-similarity matrix out[n][m] of host embeddings a[n][512], b[m][512] with the float64
+ * accumulation of the reference's Go wrapper (go/fastface/fastface.go:157-168), bit for bit. */
+int ffcu_cos_sim_matrix(int device, const float* a, int n, const float* b, int m, float* out);
+
 int ffcu_i8_mma_peak(int device, int bn, int iters, float* tops, float* ms);
 
 const char* ffcu_last_error(void);

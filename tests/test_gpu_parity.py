@@ -401,6 +401,20 @@ def test_embed_and_embed_batch_agree_with_oracle(engine, oracle):
     assert ff.FastFace.cos_sim(got[0], want[0]) >= 0.99999
 
 
+def test_cos_sim_matrix_matches_pairwise(engine):
+    """fastface_cos_sim_matrix gives, for every pair, the bits of fastface_cos_sim (float64 accumulation in
+    index order, go/fastface/fastface.go:157-168), including a zero vector (-> 0) and odd sizes."""
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((19, 512)).astype(np.float32)
+    b = rng.standard_normal((37, 512)).astype(np.float32) * np.float32(3.0)
+    b[5] = 0
+    b[6] = a[3]
+    got = engine.cos_sim_matrix(a, b)
+    want = np.array([[ff.FastFace.cos_sim(x, y) for y in b] for x in a], np.float32)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert got[3, 6] == np.float32(1.0) and np.all(got[:, 5] == 0)
+
+
 def test_uint8_pixel_entry_point(engine, oracle):
     """fastface_embed_batch_u8 normalises 8-bit pixels on the device exactly as the reference's wrapper
     does on the host ((p - 127.5) / 127.5 in fp32, fastface.py:11): the embeddings must be bit for bit

@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol(built_lib):
     lib = C.CDLL(built_lib)
     declared = _declared_symbols()
     assert {"fastface_create", "fastface_embed", "fastface_destroy", "fastface_embed_batch",
-            "fastface_embed_batch_u8", "fastface_cos_sim", "ffcu_submit", "ffcu_submit_u8", "ffcu_conv_once"} <= declared
+            "fastface_embed_batch_u8", "fastface_cos_sim", "fastface_cos_sim_matrix", "ffcu_cos_sim_matrix", "ffcu_submit", "ffcu_submit_u8", "ffcu_conv_once"} <= declared
     for name in sorted(declared):
         assert hasattr(lib, name), f"{name} is declared in include/ but not exported"
 
