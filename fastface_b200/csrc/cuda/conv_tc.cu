@@ -102,7 +102,18 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
     p->KC = (Cp % 128 == 0) ? 128 : 64;
     p->BN = L.Cout >= 256 ? 256 : L.Cout;
     const char* bn_env = getenv("FF_TC_BN");
+    // $FF_TC_BN: 64 / 128 / 256 pins the column tile where it divides Cout; "wide" keeps the widest tile at any batch
     if (bn_env) { int v = atoi(bn_env); if ((v == 64 || v == 128 || v == 256) && L.Cout % v == 0) p->BN = v; }
+    else {
+        // Small batches: a context whose largest batch yields fewer tiles than SMs (latency use: one face
+        // is 2 row tiles on the 14x14 maps) takes narrower column tiles, so that Cout / BN times as many SMs
+        // share the layer's weight stream instead of one SM reading all of it.
+        int n_sm = 148;
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device);
+        const long long rows = (L.kind == FFCU_FC) ? (long long)max_batch : (long long)max_batch * L.Ho * L.Wo;
+        const long long m_tiles = (rows + TC_TILE_M - 1) / TC_TILE_M;
+        while (p->BN > 64 && L.Cout % (p->BN / 2) == 0 && m_tiles * (L.Cout / p->BN) < n_sm) p->BN /= 2;
+    }
     // fused BN: a byte table in shared memory for tiles up to $FF_TC_BNLUT_MAX channels wide, arithmetic beyond
     // (default: the table everywhere; measured 2 - 3 % faster per step than arithmetic for the wide tiles although
     // it costs those a pipeline stage)

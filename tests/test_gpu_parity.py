@@ -72,6 +72,12 @@ def random_layer(rng, B, H, Cin, Cout, k, stride, with_slope, with_res):
     return dict(x=x, w=w, ws=ws, bias=bias, inv=inv, stride=stride, pad=pad, slope=slope, res=res, rs=rs)
 
 
+def force_wide_tiles(monkeypatch, Cout):
+    """Small test batches would get the narrow column tiles of the latency configuration; the kernel
+    variants under test here are the ones large batches run, so pin the widest tile."""
+    monkeypatch.setenv("FF_TC_BN", "wide")
+
+
 LAYER_CASES = [
     # name, B, H, Cin, Cout, k, stride, slope, res
     ("s1_64_64_56_prelu", 2, 56, 64, 64, 3, 1, True, False),
@@ -95,9 +101,14 @@ LAYER_CASES = [
 
 
 @pytest.mark.parametrize("case", LAYER_CASES, ids=[c[0] for c in LAYER_CASES])
-@pytest.mark.parametrize("impl", ["tc", "simt"])
-def test_single_layer_vs_oracle(built_lib, case, impl):
+@pytest.mark.parametrize("impl", ["tc", "tc_wide", "simt"])
+def test_single_layer_vs_oracle(built_lib, case, impl, monkeypatch):
+    """impl "tc": the tile width the library picks for this (small) batch, i.e. the narrow column tiles of
+    the latency configuration; "tc_wide": the widest tile (FF_TC_BN), which is what large batches run."""
     name, B, H, Cin, Cout, k, stride, sl, rs = case
+    if impl == "tc_wide":
+        monkeypatch.setenv("FF_TC_BN", "wide")
+        impl = "tc"
     rng = np.random.default_rng(zlib.crc32(name.encode()))
     L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
     for mode in (ff.EPILOGUE_CONTRACT, ff.EPILOGUE_STRICT):
@@ -133,10 +144,11 @@ def test_requant_out_of_range_matches_x86_conversion(built_lib, impl):
 @pytest.mark.parametrize("case", [LAYER_CASES[0], LAYER_CASES[2], LAYER_CASES[4], LAYER_CASES[6], LAYER_CASES[8], LAYER_CASES[14]],
                          ids=lambda c: c[0])
 @pytest.mark.parametrize("impl", ["tc", "simt"])
-def test_fused_bn_second_output(built_lib, case, impl):
+def test_fused_bn_second_output(built_lib, case, impl, monkeypatch):
     """The BN pass that follows a conv rides along as a second epilogue output; it must equal
     bn_prelu_requant_int8 (kernels/int8_epilogue.c:253-318) applied to the conv's int8 output."""
     name, B, H, Cin, Cout, k, stride, sl, rs = case
+    force_wide_tiles(monkeypatch, Cout)
     rng = np.random.default_rng(zlib.crc32(name.encode()) + 1)
     L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
     in_scale = (np.float32(1) / L["inv"]).astype(np.float32)
@@ -181,6 +193,7 @@ def test_64ch_layers_on_the_per_tap_kernel(built_lib, case, monkeypatch):
     instead of the weight-stationary one; both must give the same bytes."""
     monkeypatch.setenv("FF_TC_WS", "0")
     name, B, H, Cin, Cout, k, stride, sl, rs = case
+    force_wide_tiles(monkeypatch, Cout)
     rng = np.random.default_rng(zlib.crc32(name.encode()))
     L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
     acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
@@ -196,6 +209,7 @@ def test_fused_bn_by_arithmetic(built_lib, case, monkeypatch):
     the per-channel byte table; both must equal bn_prelu_requant_int8 (kernels/int8_epilogue.c:253-318)."""
     monkeypatch.setenv("FF_TC_BNLUT_MAX", "0")
     name, B, H, Cin, Cout, k, stride, sl, rs = case
+    force_wide_tiles(monkeypatch, Cout)
     rng = np.random.default_rng(zlib.crc32(name.encode()) + 9)
     L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
     in_scale = (np.float32(1) / L["inv"]).astype(np.float32)
@@ -224,6 +238,7 @@ def test_two_issuer_warps_option(built_lib, case, monkeypatch):
     measured no faster there; the weight-stationary and stem kernels always use two).  Same bytes."""
     monkeypatch.setenv("FF_TC_ISSUERS", "2")
     name, B, H, Cin, Cout, k, stride, sl, rs = case
+    force_wide_tiles(monkeypatch, Cout)
     rng = np.random.default_rng(zlib.crc32(name.encode()) + 13)
     L = random_layer(rng, B * 3, H, Cin, Cout, k, stride, sl, rs)
     acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
@@ -242,6 +257,7 @@ def test_two_lane_fp32_epilogue_option(built_lib, case, monkeypatch):
     instruction, each lane the same IEEE operation); same bytes as the oracle."""
     monkeypatch.setenv("FF_TC_X2", "1")
     name, B, H, Cin, Cout, k, stride, sl, rs = case
+    force_wide_tiles(monkeypatch, Cout)
     rng = np.random.default_rng(zlib.crc32(name.encode()) + 19)
     L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
     acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
@@ -259,6 +275,7 @@ def test_weight_stationary_pair_kernel(built_lib, case, monkeypatch):
     including an odd number of tiles (the pair's second CTA then works on a tile past the batch)."""
     monkeypatch.setenv("FF_TC_WS2", "1")
     name, B, H, Cin, Cout, k, stride, sl, rs = case
+    force_wide_tiles(monkeypatch, Cout)
     rng = np.random.default_rng(zlib.crc32(name.encode()) + 17)
     L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
     acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
@@ -278,6 +295,7 @@ def test_tap_shift_kernel(built_lib, case, monkeypatch):
     same buffer read from a shifted descriptor start address); same bytes as the oracle."""
     monkeypatch.setenv("FF_TC_SHIFT", "1")
     name, B, H, Cin, Cout, k, stride, sl, rs = case
+    force_wide_tiles(monkeypatch, Cout)
     rng = np.random.default_rng(zlib.crc32(name.encode()) + 5)
     L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
     acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
@@ -296,6 +314,7 @@ def test_wide_layers_on_the_single_cta_kernel(built_lib, case, monkeypatch):
     the CTA-pair (cta_group::2) one; both must give the same bytes."""
     monkeypatch.setenv("FF_TC_PAIR", "0")
     name, B, H, Cin, Cout, k, stride, sl, rs = case
+    force_wide_tiles(monkeypatch, Cout)
     rng = np.random.default_rng(zlib.crc32(name.encode()))
     L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
     acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
@@ -449,6 +468,16 @@ def test_stem_on_cuda_cores_agrees(built_lib, model_root, ffw4, oracle, monkeypa
             assert np.array_equal(e.embed_batch(faces), want), f"FF_STEM_TC={flag}"
             assert np.array_equal(e.embed_batch_u8(pix), want_u8), f"FF_STEM_TC={flag}, uint8 input"
             assert e.launches_per_forward == (56 if flag == "1" else 55)
+
+
+def test_network_with_the_large_batch_tiling(built_lib, model_root, ffw4, oracle, monkeypatch):
+    """A context for a small batch picks narrow column tiles; FF_TC_BN=wide pins the tiling large batches get
+    (CTA-pair kernels at BN = 256 / 128, weight-stationary kernel at 64 -> 128), here checked end to end."""
+    monkeypatch.setenv("FF_TC_BN", "wide")
+    faces = synth.faces(5, seed=31)
+    want = oracle.forward(faces, ffo.CONTRACT)
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=5) as e:
+        assert np.array_equal(e.embed_batch(faces), want)
 
 
 def test_fc_paths(built_lib, model_root, ffw4, oracle, monkeypatch):
