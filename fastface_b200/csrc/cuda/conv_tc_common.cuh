@@ -341,9 +341,9 @@ enum { EPI_RUNTIME = 0, EPI_PLAIN = 1, EPI_SLOPE = 2, EPI_RES_BN = 3, EPI_RES = 
 
 #define TC_MAX_STAGES 8
 #define TC_MAX_ABUF 4
-#define TC_NTAB 9          // w_scale, bias, slope, res_scale, inv_out | fused BN without a byte table: in_scale, scale, offset, inv_out
+#define TC_NTAB 9          // most tables a kernel holds: w_scale, bias, slope, res_scale, inv_out | fused BN without a byte table: in_scale, scale, offset, inv_out (TcParams::ntab is the count in use)
 #ifndef TC_EPI_WARPS
-#define TC_EPI_WARPS 8     // warps 2..9: two per TMEM lane quarter, each takes half the columns (16 warps, with 16-column chunks for the narrow tiles, measured no faster: the epilogue is issue-bound, not latency-bound)
+#define TC_EPI_WARPS 8     // epilogue warps per set: two per TMEM lane quarter, each takes half of the tile's columns
 #endif
 #define TC_EPI_COLGROUPS (TC_EPI_WARPS / 4)
 // Accumulator ring in TMEM: 512 columns hold 512 / BN tiles.  With short K loops (the

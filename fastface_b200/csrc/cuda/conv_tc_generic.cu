@@ -19,7 +19,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     constexpr uint32_t TMEM_COLS = TC_NACC(BN) * BN;        // the whole accumulator ring: 512 columns
     constexpr uint32_t IDESC = idesc_i8(BN);
 
-    float* tab = (float*)(smem + (size_t)p.stages * p.group * SUB_BYTES);       // [TC_NTAB][TC_MAX_COUT]
+    float* tab = (float*)(smem + (size_t)p.stages * p.group * SUB_BYTES);       // [p.ntab][TC_MAX_COUT]
     uint8_t* lut = (uint8_t*)(tab + p.ntab * TC_MAX_COUT);                  // [BN][256] fused-BN table (lut_bytes may be 0)
     TcShared* sh = (TcShared*)(lut + p.lut_bytes);
 
