@@ -87,6 +87,12 @@ def load_library() -> C.CDLL:
     L.ffcu_conv_once.restype = C.c_int
     L.ffcu_conv_once.argtypes = [C.c_int, C.POINTER(FfcuLayer), C.c_int, C.c_int, C.c_int,
                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    L.ffcu_conv_bench.restype = C.c_int
+    L.ffcu_conv_bench.argtypes = [C.c_int, C.POINTER(FfcuLayer), C.c_int, C.c_int, C.c_int,
+                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_float)]
+    L.ffcu_winograd_f23_once.restype = C.c_int
+    L.ffcu_winograd_f23_once.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                         C.c_int, C.c_void_p, C.POINTER(C.c_float)]
     L.ffcu_last_error.restype = C.c_char_p
     _lib = L
     return L
@@ -260,9 +266,10 @@ def conv_once(x: np.ndarray, w_oihw: np.ndarray, w_scale: np.ndarray, bias: np.n
               res: Optional[np.ndarray] = None, res_scale: Optional[np.ndarray] = None,
               mode: int = EPILOGUE_CONTRACT, impl: str = "tc", device: int = 0,
               bn2: Optional[Tuple[np.ndarray, np.ndarray, np.ndarray, np.ndarray]] = None,
-              want_acc: bool = True):
+              want_acc: bool = True, bench_iters: int = 0):
     """One conv layer through the C-ABI (ffcu_conv_once): x int8 [B,H,W,Cin],
-    w int8 [Cout,Cin,Kh,Kw] -> (int32 accumulators, int8 output), both [B,Ho,Wo,Cout]."""
+    w int8 [Cout,Cin,Kh,Kw] -> (int32 accumulators, int8 output), both [B,Ho,Wo,Cout].
+    bench_iters > 0 goes through ffcu_conv_bench instead and returns (ms per launch, int8 output[, BN output])."""
     lib = load_library()
     B, H, W, Cin = x.shape
     Cout, _, Kh, Kw = w_oihw.shape
@@ -289,9 +296,32 @@ def conv_once(x: np.ndarray, w_oihw: np.ndarray, w_scale: np.ndarray, bias: np.n
     acc = np.empty((B, Ho, Wo, Cout), np.int32) if want_acc else None
     out = np.empty((B, Ho, Wo, Cout), np.int8)
     r = None if res is None else np.ascontiguousarray(res, dtype=np.int8)
+    if bench_iters > 0:
+        ms = C.c_float(0)
+        rc = lib.ffcu_conv_bench(device, C.byref(L), B, mode, 0 if impl == "tc" else 1, _ptr(xp), _ptr(r), _ptr(out), _ptr(out2),
+                                 bench_iters, C.byref(ms))
+        if rc != 0:
+            raise RuntimeError(f"ffcu_conv_bench rc={rc}: " + lib.ffcu_last_error().decode())
+        return (float(ms.value), out, out2) if bn2 is not None else (float(ms.value), out)
     rc = lib.ffcu_conv_once(device, C.byref(L), B, mode, 0 if impl == "tc" else 1, _ptr(xp), _ptr(r), _ptr(acc), _ptr(out), _ptr(out2))
     if rc != 0:
         raise RuntimeError(f"ffcu_conv_once rc={rc}: " + lib.ffcu_last_error().decode())
     if bn2 is not None:
         return acc, out, out2
     return acc, out
+
+
+def winograd_f23(x: np.ndarray, w_oihw: np.ndarray, iters: int = 1, device: int = 0):
+    """3x3 stride-1 pad-1 conv by exact-integer Winograd F(2,3) on the CUDA cores (ffcu_winograd_f23_once):
+    x int8 [B,H,W,Cin], w int8 [Cout,Cin,3,3] -> (int32 [B,H,W,Cout] = 4 x the direct accumulators, ms per run)."""
+    lib = load_library()
+    B, H, W, Cin = x.shape
+    Cout = w_oihw.shape[0]
+    xc = np.ascontiguousarray(x, dtype=np.int8)
+    wc = np.ascontiguousarray(w_oihw, dtype=np.int8)
+    out = np.empty((B, H, W, Cout), np.int32)
+    ms = C.c_float(0)
+    rc = lib.ffcu_winograd_f23_once(device, _ptr(xc), _ptr(wc), B, H, W, Cin, Cout, iters, _ptr(out), C.byref(ms))
+    if rc != 0:
+        raise RuntimeError(f"ffcu_winograd_f23_once rc={rc}: " + lib.ffcu_last_error().decode())
+    return out, float(ms.value)

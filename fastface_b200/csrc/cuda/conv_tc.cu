@@ -1,5 +1,5 @@
 // conv_tc.cu -- host side of the tensor-core convolution: per-layer kernel choice, tile
-// geometry, TMA descriptors, launch.  The kernels live in conv_tc_{generic,ws,pair}.cu.
+// geometry, TMA descriptors, launch.  The kernels live in conv_tc_{generic,ws,pair,k32}.cu.
 #include "conv_tc_common.cuh"
 
 // ---------------------------------------------------------------------------
@@ -40,15 +40,9 @@ struct TcPlan {
     bool pair;               // CTA-pair kernel (cta_group::2) for >= 128 input channels
     CUtensorMap mapB_half;   // box {128, BN/2}
     int pair_stages, pair_smem_bytes;
-    bool shift;              // tap-shift pair kernel (3x3 stride-1, >= 128 input channels, 14x14 / 28x28 maps)
-    CUtensorMap mapA_shift;  // box {128, P, TR + 2, 1}
-    int shift_P, shift_TR, shift_na, shift_a_stride, shift_stages, shift_group, shift_smem_bytes;
     bool ws;                 // weight-stationary kernel (64-channel 3x3 stride-1 layers)
     CUtensorMap mapA_ws;     // box {64, 8, 18, 1}
     int ws_stages, ws_smem_bytes;
-    bool ws2;                // its CTA-pair form (cta_group::2): half the weights per CTA, one MMA per two tiles
-    CUtensorMap mapB_ws_half; // box {64, BN/2, 1, 1}
-    int ws2_stages, ws2_smem_bytes;
 };
 
 // Output-tile shape {TW, TH, TB} with TW*TH*TB = 128 that wastes the fewest rows for this
@@ -87,33 +81,55 @@ static bool encode_A(const TcPlan* p, TcGeom* g)
     return true;
 }
 
-TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, const int8_t* d_w, int device)
+// Column-tile width for a call of `batch` faces.  BN = min(256, Cout) when the batch fills the
+// machine.  A batch that yields fewer tiles than SMs (latency use: one face is 2 row tiles on the
+// 14x14 maps) takes narrower column tiles, so that Cout / BN times as many SMs share the layer's
+// weight stream instead of one SM reading all of it.  $FF_TC_BN: 64 / 128 / 256 pins the tile
+// where it divides Cout; "wide" keeps the widest tile at any batch.
+int ffcu_tc_pick_bn(const ffcu_layer& L, int batch, int device)
+{
+    int bn = L.Cout >= 256 ? 256 : L.Cout;
+    const char* bn_env = getenv("FF_TC_BN");
+    if (bn_env) {
+        int v = atoi(bn_env);
+        if ((v == 64 || v == 128 || v == 256) && L.Cout % v == 0) bn = v;
+        return bn;
+    }
+    static int n_sm_dev[64] = {};
+    int& n_sm = n_sm_dev[device & 63];
+    if (!n_sm && cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) n_sm = 148;
+    const long long rows = (L.kind == FFCU_FC) ? (long long)batch : (long long)batch * L.Ho * L.Wo;
+    const long long m_tiles = (rows + TC_TILE_M - 1) / TC_TILE_M;
+    while (bn > 64 && L.Cout % (bn / 2) == 0 && m_tiles * (L.Cout / bn) < n_sm) bn /= 2;
+    return bn;
+}
+
+// One-shot fault injection for the timeout-path test (ffcu_test_arm_timeout): consumed by the
+// next launch of the one-CTA per-tap kernel.
+static int g_test_drop_stage = -1;
+static long long g_test_full_wait = 0;
+
+extern "C" void ffcu_test_arm_timeout(int drop_stage, long long full_wait_cycles)
+{
+    g_test_drop_stage = drop_stage;
+    g_test_full_wait = full_wait_cycles;
+}
+
+TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, const int8_t* d_w, int device, int bn)
 {
     if (L.kind != FFCU_CONV && L.kind != FFCU_FC) return nullptr;
     const int Cp = L.Cin_pad;
     if (Cp % 64 != 0 || L.Cout % 64 != 0 || L.Cout > TC_MAX_COUT) return nullptr;
     if (L.stride < 1 || L.stride > 2 || L.Kh * L.Kw > 9) return nullptr;
     if (L.stride == 2 && getenv("FF_TC_STRIDE2") && atoi(getenv("FF_TC_STRIDE2")) == 0) return nullptr;
+    if ((bn != 64 && bn != 128 && bn != 256) || L.Cout % bn != 0) return nullptr;
     encode_tiled_fn enc = get_encode();
     if (!enc) return nullptr;
     TcPlan* p = new TcPlan();
     p->d = L; p->max_batch = max_batch; p->d_in = d_in; p->n_geoms = 0;
     p->out_f32 = (L.kind == FFCU_FC);
     p->KC = (Cp % 128 == 0) ? 128 : 64;
-    p->BN = L.Cout >= 256 ? 256 : L.Cout;
-    const char* bn_env = getenv("FF_TC_BN");
-    // $FF_TC_BN: 64 / 128 / 256 pins the column tile where it divides Cout; "wide" keeps the widest tile at any batch
-    if (bn_env) { int v = atoi(bn_env); if ((v == 64 || v == 128 || v == 256) && L.Cout % v == 0) p->BN = v; }
-    else {
-        // Small batches: a context whose largest batch yields fewer tiles than SMs (latency use: one face
-        // is 2 row tiles on the 14x14 maps) takes narrower column tiles, so that Cout / BN times as many SMs
-        // share the layer's weight stream instead of one SM reading all of it.
-        int n_sm = 148;
-        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device);
-        const long long rows = (L.kind == FFCU_FC) ? (long long)max_batch : (long long)max_batch * L.Ho * L.Wo;
-        const long long m_tiles = (rows + TC_TILE_M - 1) / TC_TILE_M;
-        while (p->BN > 64 && L.Cout % (p->BN / 2) == 0 && m_tiles * (L.Cout / p->BN) < n_sm) p->BN /= 2;
-    }
+    p->BN = bn;
     // fused BN: a byte table in shared memory for tiles up to $FF_TC_BNLUT_MAX channels wide, arithmetic beyond
     // (default: the table everywhere; measured 2 - 3 % faster per step than arithmetic for the wide tiles although
     // it costs those a pipeline stage)
@@ -180,36 +196,6 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
             if (st >= 2) { p->pair = true; p->pair_stages = st; p->pair_smem_bytes = st * p->pair_group * sb + fixed; }
         }
     }
-    // tap-shift variant of the pair kernel: the tile's activation patch is fetched once for all nine taps
-    p->shift = false;
-    const char* sh_env = getenv("FF_TC_SHIFT");
-    if (p->pair && L.kind == FFCU_CONV && L.Kh == 3 && L.Kw == 3 && L.stride == 1 && L.pad == 1 && Cp % 128 == 0 &&
-        (L.W == 14 || L.W == 28) && L.H == L.W && sh_env && sh_env[0] == '1') {     // opt-in: measured no faster than the per-tap pair kernel
-        const int P = (L.W + 1 <= 16) ? 16 : 32, TR = 128 / P;
-        cuuint64_t adims[4] = {(cuuint64_t)Cp, (cuuint64_t)L.W, (cuuint64_t)L.H, (cuuint64_t)max_batch};
-        cuuint64_t astr[3] = {(cuuint64_t)Cp, (cuuint64_t)Cp * L.W, (cuuint64_t)Cp * L.W * L.H};
-        cuuint32_t abox[4] = {128, (cuuint32_t)P, (cuuint32_t)(TR + 2), 1};
-        cuuint32_t aes[4] = {1, 1, 1, 1};
-        r = enc(&p->mapA_shift, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d_in, adims, astr, abox, aes,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r == CUDA_SUCCESS) {
-            const int cb = Cp / 128;
-            // the last taps of the padding positions read up to 2 lines past the box: 8 spare lines
-            const int a_stride = ((P * (TR + 2) + 8) * 128 + 1023) / 1024 * 1024;
-            const int na = cb == 1 ? 2 : (cb + 1 > TC_MAX_ABUF ? TC_MAX_ABUF : cb + 1);
-            const int b_bytes = (p->BN / 2) * 128;
-            const char* ge = getenv("FF_TC_SHIFT_GROUP");
-            const int grp = (ge && atoi(ge) == 1) ? 1 : 3;       // taps per weight stage (a divisor of 9)
-            int st = (232448 - fixed - na * a_stride) / (grp * b_bytes);
-            if (st > TC_MAX_STAGES) st = TC_MAX_STAGES;
-            if (st >= 2) {
-                p->shift = true; p->shift_P = P; p->shift_TR = TR; p->shift_na = na; p->shift_a_stride = a_stride;
-                p->shift_stages = st; p->shift_group = grp;
-                p->shift_smem_bytes = na * a_stride + st * grp * b_bytes + fixed;
-            }
-        }
-    }
     // weight-stationary variant
     p->ws = false;
     const char* ws_env = getenv("FF_TC_WS");
@@ -228,20 +214,6 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
             int st = (232448 - wbytes - fixed) / WS_A_BYTES;
             if (st > TC_MAX_STAGES) st = TC_MAX_STAGES;
             if (st >= 2) { p->ws = true; p->ws_stages = st; p->ws_smem_bytes = wbytes + st * WS_A_BYTES + fixed; }
-            // CTA-pair form
-            const char* w2 = getenv("FF_TC_WS2");
-            p->ws2 = false;
-            if (p->ws && w2 && w2[0] == '1') {          // opt-in: measured no faster than the one-CTA form
-                cuuint32_t hbox[4] = {64, (cuuint32_t)(p->BN / 2), 1, 1};
-                CUresult r2 = enc(&p->mapB_ws_half, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d_w, dims, strides, hbox, estr,
-                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-                int st2 = (232448 - wbytes / 2 - fixed) / WS_A_BYTES;
-                if (st2 > TC_MAX_STAGES) st2 = TC_MAX_STAGES;
-                if (r2 == CUDA_SUCCESS && st2 >= 2) {
-                    p->ws2 = true; p->ws2_stages = st2; p->ws2_smem_bytes = wbytes / 2 + st2 * WS_A_BYTES + fixed;
-                }
-            }
         }
     }
     return p;
@@ -249,29 +221,16 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
 
 void ffcu_tc_free(TcPlan* p) { delete p; }
 
-static int tc_x2()
-{
-    static int v = -1;
-    // opt-in: fewer issued instructions, but under the board's power cap the step measured 0.6 % slower
-    if (v < 0) { const char* e = getenv("FF_TC_X2"); v = (e && e[0] == '1') ? 1 : 0; }
-    return v;
-}
-
-static int tc_issuers()
-{
-    static int v = -1;
-    if (v < 0) { const char* e = getenv("FF_TC_ISSUERS"); v = (e && atoi(e) == 2) ? 2 : 1; }
-    return v;
-}
-
 int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, const int8_t* res,
                    int32_t* acc_out, void* out, int8_t* out_bn2, int* d_err, cudaStream_t s)
 {
     TcPlan* p = const_cast<TcPlan*>(cp);
     if (batch < 1 || batch > p->max_batch) { ffcu_set_error("tc launch: batch out of range"); return -1; }
     const ffcu_layer& d = p->d;
+#ifdef FF_TC_TIMING
     static int dbg = -1;
     if (dbg < 0) { const char* e = getenv("FF_TC_DBG"); dbg = e ? atoi(e) : 0; }
+#endif
     const bool has_res = res && t.res_scale, has_slope = t.slope != nullptr, has_bn2 = out_bn2 && t.bn_in;
     int epi = EPI_RUNTIME;
     if (p->out_f32 || (!has_res && !has_slope && !has_bn2)) epi = EPI_PLAIN;
@@ -287,34 +246,13 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
         prm.TW = WS_TW; prm.TH = WS_TH; prm.TB = 1;
         prm.tiles_w = d.Wo / WS_TW; prm.tiles_h = (d.Ho + WS_TH - 1) / WS_TH; prm.tiles_b = batch; prm.tiles_n = 1;
         prm.total_tiles = prm.tiles_w * prm.tiles_h * batch;
-        prm.stages = p->ws_stages; prm.group = 1; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab; prm.issuers = tc_issuers(); prm.x2 = tc_x2();
-        if (p->ws2) {
-            const int pairs = (prm.total_tiles + 1) / 2, max_pairs = p->n_sm / 2;
-            const int npairs = pairs < max_pairs ? pairs : max_pairs;
-            prm.stages = p->ws2_stages;
-            return tc_launch_ws2(p->BN, mode, epi, 2 * npairs, p->ws2_smem_bytes, s, p->mapA_ws, p->mapB_ws_half, prm);
-        }
+        prm.stages = p->ws_stages; prm.group = 1; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab;
+        prm.full_wait = TC_WAIT_CYCLES; prm.drop_stage = -1;
+#ifdef FF_TC_TIMING
+        prm.dbg = dbg;
+#endif
         int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
         return tc_launch_ws(p->BN, mode, epi, grid, p->ws_smem_bytes, s, p->mapA_ws, p->mapB, prm);
-    }
-    if (p->shift) {
-        TcParams prm = {};
-        prm.t = t; prm.res = res; prm.acc_out = acc_out; prm.out = out; prm.err = d_err;
-        prm.out2 = (out_bn2 && t.bn_in) ? out_bn2 : nullptr;
-        prm.batch = batch; prm.Ho = d.Ho; prm.Wo = d.Wo; prm.Cout = d.Cout;
-        prm.taps = 9; prm.Kw = 3; prm.Cp = d.Cin_pad; prm.cin_blocks = d.Cin_pad / 128; prm.stride = 1; prm.pad = 1;
-        prm.TW = p->shift_P; prm.TH = p->shift_TR; prm.TB = 1;
-        prm.tiles_w = 1; prm.tiles_h = (d.Ho + p->shift_TR - 1) / p->shift_TR; prm.tiles_b = batch;
-        prm.tiles_n = d.Cout / p->BN;
-        prm.total_tiles = prm.tiles_h * batch * prm.tiles_n;
-        prm.stages = p->shift_stages; prm.group = p->shift_group; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab; prm.issuers = tc_issuers(); prm.x2 = tc_x2();
-        prm.na = p->shift_na; prm.a_stride = p->shift_a_stride;
-        const int m_tiles = prm.tiles_h * batch;
-        const int pairs = prm.tiles_n * ((m_tiles + 1) / 2);
-        const int max_pairs = p->n_sm / 2;
-        int npairs = pairs < max_pairs ? pairs : max_pairs;
-        if (npairs > prm.tiles_n) npairs -= npairs % prm.tiles_n;      // a pair keeps one column tile (its BN table)
-        return tc_launch_shift(p->BN, mode, epi, 2 * npairs, p->shift_smem_bytes, s, p->mapA_shift, p->mapB_half, prm);
     }
     int TW, TH, TB;
     pick_geometry(d.Wo, d.Ho, batch, &TW, &TH, &TB);
@@ -338,7 +276,11 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
     prm.tiles_w = (d.Wo + TW - 1) / TW; prm.tiles_h = (d.Ho + TH - 1) / TH; prm.tiles_b = (batch + TB - 1) / TB;
     prm.tiles_n = d.Cout / p->BN;
     prm.total_tiles = prm.tiles_w * prm.tiles_h * prm.tiles_b * prm.tiles_n;
-    prm.stages = p->stages; prm.group = p->group; prm.dbg = dbg; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab; prm.issuers = tc_issuers(); prm.x2 = tc_x2();
+    prm.stages = p->stages; prm.group = p->group; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab;
+    prm.full_wait = TC_WAIT_CYCLES; prm.drop_stage = -1;
+#ifdef FF_TC_TIMING
+    prm.dbg = dbg;
+#endif
     { const char* e = getenv("FF_TC_STAGES"); if (e && atoi(e) >= 2 && atoi(e) < prm.stages) prm.stages = atoi(e); }
     if (p->pair) {
         const int m_tiles = prm.tiles_w * prm.tiles_h * prm.tiles_b;
@@ -352,6 +294,11 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
     }
     int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
     if (grid > prm.tiles_n) grid -= grid % prm.tiles_n;                // a CTA keeps one column tile (its BN table)
+    if (g_test_drop_stage >= 0) {                                      // armed for this one launch by the timeout test
+        prm.drop_stage = g_test_drop_stage;
+        if (g_test_full_wait > 0) prm.full_wait = g_test_full_wait;
+        g_test_drop_stage = -1; g_test_full_wait = 0;
+    }
     return tc_launch_generic(p->BN, p->KC, mode, epi, p->out_f32, grid, p->smem_bytes, s, g->mapA, p->mapB, prm);
 }
 
@@ -412,8 +359,11 @@ int ffcu_stem_tc_launch(const StemTcPlan* p, int batch, int mode, const EpiTable
     prm.TW = TC_TILE_M; prm.TH = 1; prm.TB = 1;
     prm.tiles_w = n_pix / TC_TILE_M; prm.tiles_h = 1; prm.tiles_b = 1; prm.tiles_n = 1;
     prm.total_tiles = prm.tiles_w;
-    prm.stages = p->stages; prm.group = 1; prm.lut_bytes = has_bn2 ? p->lut_bytes : 0; prm.ntab = 5; prm.x2 = tc_x2();
+    prm.stages = p->stages; prm.group = 1; prm.lut_bytes = has_bn2 ? p->lut_bytes : 0; prm.ntab = 5;
+    prm.full_wait = TC_WAIT_CYCLES; prm.drop_stage = -1;
+#ifdef FF_TC_TIMING
     { static int dbg = -1; if (dbg < 0) { const char* e = getenv("FF_TC_DBG"); dbg = e ? atoi(e) : 0; } prm.dbg = dbg; }
+#endif
     const int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
     return tc_launch_k32(mode, epi, grid, p->smem_bytes, s, p->mapA, p->mapB, prm);
 }

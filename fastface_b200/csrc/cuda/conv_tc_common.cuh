@@ -13,13 +13,16 @@
 //   Out-of-bounds rows/columns are zero-filled by TMA (= the conv's zero padding);
 //   stride-2 convs use the tensor map's element strides.
 // * B is the weight matrix repacked [Cout][kh][kw][Cin], a 2-D TMA box {KC, BN}.
-// * tcgen05.mma kind::i8, cta_group::1, M=128, N=BN, K=32 per instruction;
-//   accumulators double-buffered in TMEM so the epilogue of tile i overlaps the
-//   MMAs of tile i+1.
+// * tcgen05.mma kind::i8, M=128 per CTA (cta_group::1) or M=256 per CTA pair
+//   (cta_group::2), N=BN, K=32 per instruction; a ring of 512/BN accumulators in
+//   TMEM so the epilogue of one tile overlaps the MMAs of the next ones.
 // * Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (+TMEM alloc),
-//   warps 2..9 = epilogue (tcgen05.ld -> exact fp32 chain -> int8 NHWC stores).
+//   warps 2..17 = epilogue, two sets of eight (tcgen05.ld -> exact fp32 chain ->
+//   int8 NHWC stores), warp 18 = second MMA issuer in the kernels whose tiles are
+//   a handful of MMAs (weight-stationary and stem kernels).
 // * Every wait is bounded; on expiry the kernel records an error word, drains
-//   and frees its TMEM, and returns.  No cluster launch, no multicast.
+//   and frees its TMEM, and returns.  The CTA-pair kernel is a cluster of two;
+//   no TMA load is multicast.
 
 #pragma once
 #include "ffcu_internal.cuh"
@@ -69,12 +72,14 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
 
 __device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity);
 // Bounded wait.  Returns false (and raises the CTA-wide abort flag + the global error
-// word) when the barrier did not flip within TC_WAIT_CYCLES SM cycles (about 2 s) or another
-// role already aborted.  The clock is only consulted after a burst of failed polls, so a
-// wait that succeeds quickly costs nothing but the polls.
+// word) when the barrier did not flip within `limit` SM cycles (TC_WAIT_CYCLES, about 2 s,
+// unless the launch says otherwise) or another role already aborted.  The clock is only
+// consulted after a burst of failed polls, so a wait that succeeds quickly costs nothing
+// but the polls.
 #define TC_WAIT_CYCLES 4000000000ll
 template <bool CLUSTER>
-__device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code)
+__device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code,
+                                               long long limit)
 {
 #pragma unroll 1
     for (int i = 0; i < 256; i++)
@@ -85,7 +90,7 @@ __device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, vo
         if (CLUSTER ? mbar_try_cluster(bar, parity) : mbar_try(bar, parity)) return true;
         if ((spin & 255u) == 0) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > TC_WAIT_CYCLES) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = 1;
                 atomicCAS(err, 0, code);
                 return false;
@@ -94,14 +99,16 @@ __device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, vo
     }
 }
 __device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity);
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code,
+                                          long long limit = TC_WAIT_CYCLES)
 {
-    return mbar_wait_impl<false>(bar, parity, abort_flag, err, code);
+    return mbar_wait_impl<false>(bar, parity, abort_flag, err, code, limit);
 }
 // Same, for a barrier that CTAs of the pair arrive on remotely (cluster-scope acquire).
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code)
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code,
+                                                  long long limit = TC_WAIT_CYCLES)
 {
-    return mbar_wait_impl<true>(bar, parity, abort_flag, err, code);
+    return mbar_wait_impl<true>(bar, parity, abort_flag, err, code, limit);
 }
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
@@ -326,12 +333,19 @@ struct TcParams {
     int stages;
     int lut_bytes;           // shared-memory bytes of the fused BN's table (BN * 256, or 0)
     int group;               // K blocks per pipeline stage (one barrier hand-shake per `group` blocks)
-    int x2;                  // contract-mode epilogue with two-lane fp32 instructions (fma / mul / add .f32x2)
-    int issuers;             // MMA issuer warps that take alternate tiles (1 or 2; 2 needs a ring of >= two tiles' stages)
     int ntab;                // per-channel tables held in shared memory: 5, or 9 when the fused BN is computed arithmetically
-    int na, a_stride;        // tap-shift kernel: activation-slice buffers in the ring, bytes per buffer
-    int dbg;                 // timing experiments only ($FF_TC_DBG): bit 0 = skip the TMA loads, bit 1 = skip the MMAs, bit 2 = no global memory in the epilogue, bit 3 = no epilogue arithmetic
+    long long full_wait;     // cycle limit of the MMA issuer's wait for a pipeline stage's data (TC_WAIT_CYCLES)
+    int drop_stage;          // >= 0: the producer neither arms nor loads this K step of its first tile, so the
+                             // issuer's wait for it must run out (ffcu_test_arm_timeout; -1 in every other launch)
+#ifdef FF_TC_TIMING
+    int dbg;                 // timing experiments: bit 0 = skip the TMA loads, bit 1 = skip the MMAs, bit 2 = no global memory in the epilogue, bit 3 = no epilogue arithmetic
+#endif
 };
+#ifdef FF_TC_TIMING
+#define TC_DBG(p, bit) ((p).dbg & (bit))
+#else
+#define TC_DBG(p, bit) 0
+#endif
 
 // Epilogue variants.  All but EPI_RUNTIME fix the presence of PReLU / residual / fused BN at
 // compile time, which turns the per-element code into one straight-line block the scheduler
@@ -340,7 +354,6 @@ struct TcParams {
 enum { EPI_RUNTIME = 0, EPI_PLAIN = 1, EPI_SLOPE = 2, EPI_RES_BN = 3, EPI_RES = 4, EPI_SLOPE_BN = 5 };
 
 #define TC_MAX_STAGES 8
-#define TC_MAX_ABUF 4
 #define TC_NTAB 9          // most tables a kernel holds: w_scale, bias, slope, res_scale, inv_out | fused BN without a byte table: in_scale, scale, offset, inv_out (TcParams::ntab is the count in use)
 #ifndef TC_EPI_WARPS
 #define TC_EPI_WARPS 8     // epilogue warps per set: two per TMEM lane quarter, each takes half of the tile's columns
@@ -369,8 +382,6 @@ struct TcShared {                 // lives after the stage ring and the tables
     uint64_t empty[TC_MAX_STAGES];
     uint64_t acc_full[TC_MAX_ACC];
     uint64_t acc_empty[TC_MAX_ACC];
-    uint64_t a_full[TC_MAX_ABUF]; // tap-shift kernel: activation-slice ring
-    uint64_t a_empty[TC_MAX_ABUF];
     uint64_t w_full;              // weight-stationary kernel: weights have landed
     uint32_t tmem_base;
     int abort_flag;
@@ -461,19 +472,12 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
         const float4 iv = *(const float4*)&tab[4 * TC_MAX_COUT + cb + 4 * g];
         const int r = rw[g];
         int q0, q1, q2, q3;
-        if (CONTRACT && !CHECK && p.x2) {
-            ffcu_conv_q2(v[4 * g + 0], v[4 * g + 1], ws.x, ws.y, bi.x, bi.y, has_res, (int)(int8_t)(r & 0xff), (int)(int8_t)((r >> 8) & 0xff),
-                         rs.x, rs.y, has_slope, sl.x, sl.y, iv.x, iv.y, q0, q1);
-            ffcu_conv_q2(v[4 * g + 2], v[4 * g + 3], ws.z, ws.w, bi.z, bi.w, has_res, (int)(int8_t)((r >> 16) & 0xff), (int)(int8_t)((r >> 24) & 0xff),
-                         rs.z, rs.w, has_slope, sl.z, sl.w, iv.z, iv.w, q2, q3);
-        } else {
         float f0 = ffcu_conv_fp<CONTRACT>(v[4 * g + 0], ws.x, bi.x, has_res, (int)(int8_t)(r & 0xff), rs.x, has_slope, sl.x);
         float f1 = ffcu_conv_fp<CONTRACT>(v[4 * g + 1], ws.y, bi.y, has_res, (int)(int8_t)((r >> 8) & 0xff), rs.y, has_slope, sl.y);
         float f2 = ffcu_conv_fp<CONTRACT>(v[4 * g + 2], ws.z, bi.z, has_res, (int)(int8_t)((r >> 16) & 0xff), rs.z, has_slope, sl.z);
         float f3 = ffcu_conv_fp<CONTRACT>(v[4 * g + 3], ws.w, bi.w, has_res, (int)(int8_t)((r >> 24) & 0xff), rs.w, has_slope, sl.w);
         q0 = ffcu_requant_nosat<CHECK>(f0, iv.x); q1 = ffcu_requant_nosat<CHECK>(f1, iv.y);
         q2 = ffcu_requant_nosat<CHECK>(f2, iv.z); q3 = ffcu_requant_nosat<CHECK>(f3, iv.w);
-        }
         ow_[g] = ffcu_pack4(q0, q1, q2, q3);
         if (has_bn2 && !p.lut_bytes) {
             // BN of the four int8 results by arithmetic (the wide tiles: their byte tables would take 32 - 64 KB
@@ -500,7 +504,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float
             ow2_[g] = 0;
         }
     }
-    if ((p.dbg & 4) && ow_[0] != 0x12345679) return;      // timing experiment: no global stores
+    if (TC_DBG(p, 4) && ow_[0] != 0x12345679) return;      // timing experiment: no global stores
     if (CW == 32) {
         const int w0[8] = {ow_[0], ow_[1], ow_[2], ow_[3], ow_[NG - 4], ow_[NG - 3], ow_[NG - 2], ow_[NG - 1]};
         st_global_32B((int8_t*)p.out + o, w0);
@@ -578,8 +582,9 @@ __device__ __forceinline__ void walk_next(TileWalk& w, const TcParams& p)
     w.tb += w.db + c;
 }
 
-// Epilogue role shared by both kernels.  Warps 2..9: warp w reads TMEM lanes
-// [32*(w%4), +32) (the hardware's per-warp lane window) and the column group (w-2)/4.
+// Epilogue role shared by all kernels.  Warps 2..17: warp w reads TMEM lanes
+// [32*(w%4), +32) (the hardware's per-warp lane window), the column group ((w-2)%8)/4,
+// for the tiles of its set (w-2)/8.
 template <int BN, bool CONTRACT, bool OUT_F32, int EPI>
 __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float* tab, const uint8_t* lut, TcShared* sh,
                                                  uint32_t tmem_base, volatile int* abort_flag, int warp, int lane,
@@ -625,7 +630,7 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
 #pragma unroll
         for (int g = 0; g < CW / 4; g++) rw[g] = 0;
         const size_t o0 = pix * p.Cout + n0 + cg * PER * CW;
-        if (has_res && valid && !(p.dbg & 4)) {
+        if (has_res && valid && !TC_DBG(p, 4)) {
             if (CW == 32) { int t8[8]; ld_global_32B(p.res + o0, t8); for (int g = 0; g < CW / 4; g++) rw[g] = t8[g]; }
             else { const int4 t4 = *(const int4*)(p.res + o0); rw[0] = t4.x; rw[1] = t4.y; rw[2] = t4.z; rw[3] = t4.w; }
         }
@@ -639,7 +644,7 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
             int v[CW];
             tmem_ld(taddr + (uint32_t)(j * CW), v);
             if (!valid) continue;
-            if (p.dbg & 8) {                              // timing experiment: no arithmetic
+            if (TC_DBG(p, 8)) {                              // timing experiment: no arithmetic
                 int x = 0;
 #pragma unroll
                 for (int i = 0; i < CW; i++) x ^= v[i];
@@ -649,7 +654,7 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
             int rn[CW / 4];
 #pragma unroll
             for (int g = 0; g < CW / 4; g++) rn[g] = 0;
-            if (has_res && jj + 1 < PER && !(p.dbg & 4)) {
+            if (has_res && jj + 1 < PER && !TC_DBG(p, 4)) {
                 if (CW == 32) { int t8[8]; ld_global_32B(p.res + o0 + (size_t)(jj + 1) * CW, t8); for (int g = 0; g < CW / 4; g++) rn[g] = t8[g]; }
                 else { const int4 t4 = *(const int4*)(p.res + o0 + (size_t)(jj + 1) * CW); rn[0] = t4.x; rn[1] = t4.y; rn[2] = t4.z; rn[3] = t4.w; }
             }
@@ -714,10 +719,6 @@ __device__ __forceinline__ void tc_teardown(volatile int* abort_flag, uint32_t t
 // epi is an EPI_* value; f32 selects the FC epilogue (f32 output, no requantisation).
 int tc_launch_generic(int bn, int kc, int mode, int epi, bool f32, int grid, int smem, cudaStream_t s,
                       const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
-int tc_launch_shift(int bn, int mode, int epi, int grid, int smem, cudaStream_t s,
-                    const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
-int tc_launch_ws2(int bn, int mode, int epi, int grid, int smem, cudaStream_t s,
-                  const CUtensorMap& mapA, const CUtensorMap& mapB_half, const TcParams& prm);
 int tc_launch_k32(int mode, int epi, int grid, int smem, cudaStream_t s,
                   const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
 int tc_launch_ws(int bn, int mode, int epi, int grid, int smem, cudaStream_t s,

@@ -78,7 +78,7 @@ conv_k32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                 if (!ok) break;
             }
             if (!ready_f) {
-                ok = mbar_wait(smem_u32(&sh->full[stage]), phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
+                ok = mbar_wait(smem_u32(&sh->full[stage]), phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT, p.full_wait);
                 if (!ok) break;
             }
             {
@@ -89,7 +89,7 @@ conv_k32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
             const uint64_t da = smem_desc_sw32(smem_u32(s_a + (size_t)stage * K32_A_BYTES));
-            if (!(p.dbg & 2)) umma_i8_w(leader, d_tmem, da, dw, IDESC, 0u);
+            if (!TC_DBG(p, 2)) umma_i8_w(leader, d_tmem, da, dw, IDESC, 0u);
             umma_commit_w(leader, smem_u32(&sh->empty[stage]));
             umma_commit_w(leader, smem_u32(&sh->acc_full[a]));
         }

@@ -99,7 +99,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                 for (int it = 0; it < n_steps; it++) {
                     ok = mbar_wait(empty0 + stage * 8, phase ^ 1, abort_flag, p.err, FFCU_ERR_EMPTY_TIMEOUT);
                     if (!ok) break;
-                    if (p.dbg & 1) { if (rank == 0 && lane == 0) mbar_arrive(full0 + stage * 8); }
+                    if (TC_DBG(p, 1)) { if (rank == 0 && lane == 0) mbar_arrive(full0 + stage * 8); }
                     else {
                         if (rank == 0 && lane == 0) mbar_expect_tx(full0 + stage * 8, 2 * G * SUB_BYTES);
                         __syncwarp();                           // the byte count is armed before any copy can land
@@ -113,19 +113,13 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                 }
             }
         }
-    } else if (warp == 1 || warp == TC_ISSUER2_WARP) {
+    } else if (warp == 1) {
         const int G = p.group;
         const int n_steps = kblocks / G;
-        // With p.issuers == 2 and a ring that holds two tiles' stages, two issuer warps take alternate tiles.
-        const bool two = p.issuers == 2 && p.stages >= 2 * n_steps;
-        const int me = (warp == 1) ? 0 : 1;
-        if (rank == 0 && (me == 0 || two)) {
+        if (rank == 0) {
             // MMA issuer (leader CTA): the warp loops and waits together, lane 0 issues
-            const int lstep = two ? 2 : 1;
-            const int skip = two ? n_steps : 0;          // stages of the other issuer's tile between two of mine
             int stage = 0; uint32_t phase = 0;
-            { int adv = me * n_steps; while (adv >= p.stages) { adv -= p.stages; phase ^= 1; } stage = adv; }
-            int local = me;
+            int local = 0;
             bool ok = true;
             const int stage_bytes = G * SUB_BYTES;
             const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
@@ -133,7 +127,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             const uint64_t db0 = smem_desc<KC>(smem_u32(smem) + A_BYTES);
             const uint32_t leader = (lane == 0) ? 1u : 0u;
             uint32_t ready = 0;                          // answer of the early test for the upcoming stage
-            for (int tile = pair_id + me * n_pairs; tile < total && ok; tile += lstep * n_pairs, local += lstep) {
+            for (int tile = pair_id; tile < total && ok; tile += n_pairs, local++) {
                 const int a = local % TC_NACC(BN);
                 const uint32_t aphase = (uint32_t)(local / TC_NACC(BN)) & 1;
                 ok = mbar_wait_cluster(smem_u32(&sh->acc_empty[a]), aphase ^ 1, abort_flag, p.err, FFCU_ERR_TMEM_TIMEOUT);
@@ -142,18 +136,17 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                 const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
                 for (int it = 0; it < n_steps; it++) {
                     if (!ready) {
-                        ok = mbar_wait_cluster(full0 + stage * 8, phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
+                        ok = mbar_wait_cluster(full0 + stage * 8, phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT, p.full_wait);
                         if (!ok) break;
                     }
-                    // test this issuer's next stage now, use the answer next round (after a tile's last step
-                    // it lies beyond the other issuer's tile)
-                    int ns = stage + ((it + 1 < n_steps) ? 1 : 1 + skip); uint32_t np = phase;
-                    while (ns >= p.stages) { ns -= p.stages; np ^= 1; }
+                    // test the next stage now, use the answer next round
+                    int ns = stage + 1; uint32_t np = phase;
+                    if (ns == p.stages) { ns = 0; np ^= 1; }
                     ready = mbar_test_cluster(full0 + ns * 8, np);
                     tc_fence_after();
                     {
                         uint32_t soff = (uint32_t)((stage * stage_bytes) >> 4);
-                        if (!(p.dbg & 2))
+                        if (!TC_DBG(p, 2))
                         for (int g = 0; g < G; g++, soff += (uint32_t)(SUB_BYTES >> 4)) {
 #pragma unroll
                             for (int k = 0; k < KC / 32; k++)

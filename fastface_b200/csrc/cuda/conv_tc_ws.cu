@@ -7,11 +7,12 @@
 // shared-memory fill traffic).
 //   * all 9 weight taps ([tap][BN rows][64 B], 36 KB or 72 KB) are loaded once per CTA
 //     and stay in shared memory for every tile the CTA processes;
-//   * output tile = 8 wide x 16 high pixels of one image.  Per tile three boxes
-//     {64 B, 8, 18, 1} are loaded, one per kw, each holding rows y0-1 .. y0+16: an 8-row
-//     swizzle group is one image row of the box, so the three kh taps are the same box
-//     read at group offsets 0, 1, 2 (descriptor start + kh * 512 B).  Activation bytes
-//     fetched per tile drop from 9 x 128 to 3 x 144 rows.
+//   * output tile = 8 wide x 16 high pixels of one image.  Per tile ONE box
+//     {64 B, 10, 18, 1} is loaded: columns x0-1 .. x0+8, rows y0-1 .. y0+16.  An 8-row
+//     swizzle group of the A operand is one image row of the tile, groups are 10 lines
+//     (640 B) apart, and tap (kh, kw) is the same buffer read from descriptor start
+//     + (kh * 10 + kw) * 64 B.  Activation bytes fetched per tile drop from 9 x 128 to
+//     180 rows of 64 B.
 // ---------------------------------------------------------------------------
 
 template <int BN, bool CONTRACT, int EPI>
@@ -46,7 +47,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 
     if (warp == 0) {
         {
-            // the warp loops and waits together (lanes stay converged); lanes 0..2 issue one box each
+            // the warp loops and waits together (lanes stay converged); lanes 0..8 fetch one weight tap each, lane 0 the boxes
             const uint32_t wbar = smem_u32(&sh->w_full);
             if (lane == 0) mbar_expect_tx(wbar, W_BYTES);
             __syncwarp();
@@ -61,7 +62,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 if (!ok) break;
                 const uint32_t bar = smem_u32(&sh->full[stage]);
                 const uint32_t sa = smem_u32(s_a + (size_t)stage * WS_A_BYTES);
-                if (p.dbg & 1) { if (lane == 0) mbar_arrive(bar); if (++stage == p.stages) { stage = 0; phase ^= 1; } continue; }
+                if (TC_DBG(p, 1)) { if (lane == 0) mbar_arrive(bar); if (++stage == p.stages) { stage = 0; phase ^= 1; } continue; }
                 if (lane == 0) {
                     mbar_expect_tx(bar, WS_BOX_ROWS * 64);
                     tma_load_4d(sa, &mapA, bar, 0, tw * WS_TW - 1, th * WS_TH - 1, b);
@@ -92,7 +93,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     if (!ok) break;
                 }
                 if (!ready_f) {
-                    ok = mbar_wait(smem_u32(&sh->full[stage]), phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
+                    ok = mbar_wait(smem_u32(&sh->full[stage]), phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT, p.full_wait);
                     if (!ok) break;
                 }
                 {   // test the barriers of this issuer's next tile now, use the answers next round
@@ -104,12 +105,12 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
                 const uint64_t da0 = smem_desc_sbo<KC>(smem_u32(s_a + (size_t)stage * WS_A_BYTES), WS_PITCH * 64);
                 {
-                if (!(p.dbg & 2))
+                if (!TC_DBG(p, 2))
 #pragma unroll
                 for (int kw = 0; kw < 3; kw++)
 #pragma unroll
                     for (int kh = 0; kh < 3; kh++) {
-                        // box kw, image rows kh .. kh+15: start = kw * 9216 + kh * 512 bytes (>> 4)
+                        // tap (kh, kw): start = (kh * pitch + kw) lines of 64 B (>> 4)
                         const uint64_t da = da0 + (uint64_t)(((kh * WS_PITCH + kw) * 64) >> 4);
                         const uint64_t db = dw + (uint64_t)(((kh * 3 + kw) * W_TAP_BYTES) >> 4);
 #pragma unroll

@@ -16,6 +16,10 @@
 //     calls that can overlap on the GPU (different streams, different host threads) race on it;
 //   * the first call on a device looks up the array's device address (a one-time set-up with
 //     that device current).  Make that first call outside any stream capture.
+//   * the kernel reads act and w sixteen bytes at a time: both pointers must be 16-byte aligned,
+//     K a positive multiple of 16 (so every row keeps that alignment) and N a multiple of 8;
+//     w_scale, bias and out must be 4-byte aligned.  All of this is checked on the host before
+//     anything is launched: a sliced or offset buffer is refused (-1), never faulted on.
 
 #include "ffcu_internal.cuh"
 
@@ -52,6 +56,18 @@ extern "C" int ffcu_fc_small_noalloc(const int8_t* act, const int8_t* w, const f
         return -2;
     }
     if (mode != 0 && mode != 1) { ffcu_set_error("ffcu_fc_small_noalloc: mode must be 0 or 1"); return -1; }
+    if (K < 16 || K % 16 != 0 || N % 8 != 0) {
+        ffcu_set_error("ffcu_fc_small_noalloc: K = %d must be a positive multiple of 16 and N = %d a multiple of 8", K, N);
+        return -1;
+    }
+    if ((((uintptr_t)act | (uintptr_t)w) & 15u) != 0) {
+        ffcu_set_error("ffcu_fc_small_noalloc: act and w must be 16-byte aligned (the kernel reads them 16 bytes at a time)");
+        return -1;
+    }
+    if ((((uintptr_t)w_scale | (uintptr_t)bias | (uintptr_t)out) & 3u) != 0) {
+        ffcu_set_error("ffcu_fc_small_noalloc: w_scale, bias and out must be 4-byte aligned");
+        return -1;
+    }
     int dev = -1;
     FFCU_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= FC_NOALLOC_MAX_DEVICES) { ffcu_set_error("ffcu_fc_small_noalloc: device ordinal %d not supported", dev); return -3; }

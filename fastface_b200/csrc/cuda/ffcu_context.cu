@@ -28,7 +28,8 @@ struct DevLayer {
     int8_t* w = nullptr;
     float* tab[12] = {};   // w_scale,bias,slope,res_scale,inv_out | in_scale,bn_scale,bn_offset | bn2 in,scale,offset,inv
     EpiTables epi{};
-    TcPlan* tc = nullptr;  // non-NULL: tensor-core implicit GEMM takes this layer
+    TcPlan* tc = nullptr;  // non-NULL: tensor-core implicit GEMM takes this layer (plan with the widest column tile)
+    TcPlan* tc_bn[3] = {}; // plans for column tiles of 64 / 128 / 256 channels, made when a call first needs them
     int8_t* bn_lut = nullptr;  // device copy of the fused BN's table
     bool fused_stem = false;   // conv that also does the input quantisation (reads the fp32 input)
     bool skip = false;         // quantise layer absorbed by the fused stem
@@ -63,9 +64,10 @@ struct ffcu_ctx {
     int no_fc_small = 0;         // FF_FC_SMALL=0: small batches take the large-batch FC path too
     int launches = 0;
     bool finalized = false;
-    // Small batches are launch-bound (55 short kernels): their forward is captured once per
-    // (batch, mode, input/output slot) into a CUDA graph and replayed.
-    int graph_max_batch = 64;    // FF_GRAPH=0 disables (0)
+    // The forward is captured once per (batch, mode, input kind, input/output slot) into a CUDA
+    // graph and replayed: small batches are launch-bound (55 short kernels), large ones still
+    // save the host's launch work.  FF_GRAPH=0 disables (0), FF_GRAPH_MAX_BATCH caps the batch.
+    int graph_max_batch = 1 << 30;
     std::map<long long, cudaGraphExec_t> graphs;
     std::map<long long, int> graph_launches;
 };
@@ -83,7 +85,7 @@ static float* upload_f32(const float* src, int n)
     if (!src) return nullptr;
     float* d = nullptr;
     if (cudaMalloc(&d, (size_t)n * sizeof(float)) != cudaSuccess) return nullptr;
-    cudaMemcpy(d, src, (size_t)n * sizeof(float), cudaMemcpyHostToDevice);
+    if (cudaMemcpy(d, src, (size_t)n * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) { cudaFree(d); return nullptr; }
     return d;
 }
 
@@ -122,6 +124,7 @@ extern "C" ffcu_ctx* ffcu_create(int device, int max_batch, int n_bufs, size_t b
     const char* impl = getenv("FF_CONV_IMPL");
     c->force_simt = (impl && strcmp(impl, "simt") == 0) ? 1 : 0;
     { const char* e = getenv("FF_FC_SMALL"); c->no_fc_small = (e && e[0] == '0') ? 1 : 0; }
+    { const char* e = getenv("FF_GRAPH_MAX_BATCH"); if (e && atoi(e) > 0) c->graph_max_batch = atoi(e); }
     { const char* e = getenv("FF_GRAPH"); if (e && e[0] == '0') c->graph_max_batch = 0; }
     if (!ok) {
         ffcu_set_error("device allocation failed on device %d: %s", device, cudaGetErrorString(cudaGetLastError()));
@@ -130,6 +133,8 @@ extern "C" ffcu_ctx* ffcu_create(int device, int max_batch, int n_bufs, size_t b
     }
     return c;
 }
+
+static void free_layer_memory(DevLayer& L);
 
 extern "C" void ffcu_destroy(ffcu_ctx* c)
 {
@@ -140,11 +145,9 @@ extern "C" void ffcu_destroy(ffcu_ctx* c)
     if (c->s_out) cudaStreamSynchronize(c->s_out);
     for (auto& g : c->graphs) cudaGraphExecDestroy(g.second);
     for (auto& L : c->layers) {
-        cudaFree(L.w); cudaFree(L.bn_lut);
-        for (float* t : L.tab) cudaFree(t);
-        ffcu_tc_free(L.tc);
+        for (TcPlan* q : L.tc_bn) if (q) ffcu_tc_free(q);      // L.tc is one of them
         if (L.stem_tc) ffcu_stem_tc_free(L.stem_tc);
-        cudaFree(L.wk32);
+        free_layer_memory(L);
     }
     for (int i = 0; i < FFCU_MAX_BUFS; i++) cudaFree(c->bufs[i]);
     for (int k = 0; k < 2; k++) {
@@ -189,6 +192,14 @@ static bool epilogue_cannot_overflow(const ffcu_layer* l)
     return true;
 }
 
+static void free_layer_memory(DevLayer& L)
+{
+    cudaFree(L.w); L.w = nullptr;
+    cudaFree(L.bn_lut); L.bn_lut = nullptr;
+    for (float*& t : L.tab) { cudaFree(t); t = nullptr; }
+    cudaFree(L.wk32); L.wk32 = nullptr;
+}
+
 extern "C" int ffcu_add_layer(ffcu_ctx* c, const ffcu_layer* l)
 {
     if (!c || !l || c->finalized) { ffcu_set_error("ffcu_add_layer: bad state"); return -1; }
@@ -196,21 +207,22 @@ extern "C" int ffcu_add_layer(ffcu_ctx* c, const ffcu_layer* l)
     DevLayer L;
     L.d = *l;
     const int C = l->Cout;
+    // every early return below goes through fail(): nothing uploaded for this layer stays allocated
+    auto fail = [&](const char* what) { ffcu_set_error("%s", what); free_layer_memory(L); cudaGetLastError(); return -1; };
+    if (l->bn2_dst_buf >= 0 && !(l->bn2_in_scale && l->bn2_scale && l->bn2_offset && l->bn2_inv_out))
+        return fail("fused BN output without its tables");
     if (l->w && l->w_bytes) {
-        if (cudaMalloc(&L.w, l->w_bytes + 1024) != cudaSuccess) { ffcu_set_error("weight allocation failed"); return -1; }
-        cudaMemset(L.w, 0, l->w_bytes + 1024);
-        cudaMemcpy(L.w, l->w, l->w_bytes, cudaMemcpyHostToDevice);
+        if (cudaMalloc(&L.w, l->w_bytes + 1024) != cudaSuccess) return fail("weight allocation failed");
+        if (cudaMemset(L.w, 0, l->w_bytes + 1024) != cudaSuccess ||
+            cudaMemcpy(L.w, l->w, l->w_bytes, cudaMemcpyHostToDevice) != cudaSuccess) return fail("weight upload failed");
     }
     const float* src[12] = {l->w_scale, l->bias, l->slope, l->res_scale, l->inv_out, l->in_scale, l->bn_scale, l->bn_offset,
                             l->bn2_in_scale, l->bn2_scale, l->bn2_offset, l->bn2_inv_out};
-    if (l->bn2_dst_buf >= 0 && !(l->bn2_in_scale && l->bn2_scale && l->bn2_offset && l->bn2_inv_out)) {
-        ffcu_set_error("fused BN output without its tables"); return -1;
-    }
     for (int k = 0; k < 12; k++) {
         int n = (l->kind == FFCU_QUANT) ? 3 : C;
         if (src[k]) {
             L.tab[k] = upload_f32(src[k], n);
-            if (!L.tab[k]) { ffcu_set_error("table allocation failed"); return -1; }
+            if (!L.tab[k]) return fail("table allocation or upload failed");
         }
     }
     L.epi.w_scale = L.tab[0]; L.epi.bias = L.tab[1]; L.epi.slope = L.tab[2];
@@ -220,8 +232,8 @@ extern "C" int ffcu_add_layer(ffcu_ctx* c, const ffcu_layer* l)
         std::vector<int8_t> lut((size_t)C * 256);
         if (l->bn2_lut) memcpy(lut.data(), l->bn2_lut, lut.size());
         else ff_bn_lut_build(l->bn2_in_scale, l->bn2_scale, l->bn2_offset, l->bn2_inv_out, C, lut.data());
-        if (cudaMalloc(&L.bn_lut, lut.size()) != cudaSuccess) { ffcu_set_error("BN table allocation failed"); return -1; }
-        cudaMemcpy(L.bn_lut, lut.data(), lut.size(), cudaMemcpyHostToDevice);
+        if (cudaMalloc(&L.bn_lut, lut.size()) != cudaSuccess) return fail("BN table allocation failed");
+        if (cudaMemcpy(L.bn_lut, lut.data(), lut.size(), cudaMemcpyHostToDevice) != cudaSuccess) return fail("BN table upload failed");
     }
     L.epi.bn_lut = L.bn_lut;
     L.epi.no_overflow = epilogue_cannot_overflow(l) ? 1 : 0;
@@ -230,7 +242,7 @@ extern "C" int ffcu_add_layer(ffcu_ctx* c, const ffcu_layer* l)
     L.d.w = nullptr;
     L.d.w_scale = L.d.bias = L.d.slope = L.d.res_scale = L.d.inv_out = nullptr;
     L.d.in_scale = L.d.bn_scale = L.d.bn_offset = nullptr;
-    if (cudaGetLastError() != cudaSuccess) { ffcu_set_error("upload failed"); return -1; }
+    if (cudaGetLastError() != cudaSuccess) return fail("upload failed");
     c->layers.push_back(L);
     return (int)c->layers.size() - 1;
 }
@@ -242,7 +254,9 @@ extern "C" int ffcu_finalize(ffcu_ctx* c)
     for (auto& L : c->layers) {
         if ((L.d.kind == FFCU_CONV || L.d.kind == FFCU_FC) && !c->force_simt) {
             if (L.d.src_buf < 0 || L.d.src_buf >= c->n_bufs) { ffcu_set_error("layer source buffer out of range"); return -1; }
-            L.tc = ffcu_tc_plan(L.d, c->max_batch, c->bufs[L.d.src_buf], L.w, c->device);
+            const int bn = L.d.Cout >= 256 ? 256 : L.d.Cout;
+            L.tc = ffcu_tc_plan(L.d, c->max_batch, c->bufs[L.d.src_buf], L.w, c->device, bn);
+            if (L.tc) L.tc_bn[bn == 64 ? 0 : bn == 128 ? 1 : 2] = L.tc;
         }
     }
     // [quantise, conv3x3 3->64 s1 p1 at 112x112] -> one fused stem kernel
@@ -283,6 +297,21 @@ extern "C" int ffcu_launches_per_forward(const ffcu_ctx* c) { return c ? c->laun
 // forward
 // ---------------------------------------------------------------------------
 
+// The layer's plan for a call of n faces: the column tile follows the batch of the CALL (one face
+// through a context made for 256 gets the narrow tiles that spread a layer over the SMs), so the
+// reference's create + embed sequence needs no hint about the batch it will see.
+static TcPlan* tc_plan_for(ffcu_ctx* c, DevLayer& L, int n)
+{
+    if (!L.tc) return nullptr;
+    const int bn = ffcu_tc_pick_bn(L.d, n, c->device);
+    const int slot = bn == 64 ? 0 : bn == 128 ? 1 : 2;
+    if (!L.tc_bn[slot]) {
+        L.tc_bn[slot] = ffcu_tc_plan(L.d, c->max_batch, c->bufs[L.d.src_buf], L.w, c->device, bn);
+        if (!L.tc_bn[slot]) return L.tc;
+    }
+    return L.tc_bn[slot];
+}
+
 // Launch layer k for n faces.  acc_dbg (optional) receives the conv's int32 accumulators;
 // unfused = dump-point mode: the stem runs as separate quantise + conv launches.
 static int launch_layer(ffcu_ctx* c, size_t k, int n, int32_t* acc_dbg, bool unfused = false)
@@ -305,7 +334,7 @@ static int launch_layer(ffcu_ctx* c, size_t k, int n, int32_t* acc_dbg, bool unf
         }
         if (L.fused_stem && !unfused)
             return ffcu_launch_stem(c->d_in, c->in_u8 ? 1 : 0, c->layers[0].tab[4], L.w, L.epi, n, c->mode, c->bufs[d.dst_buf], out2, nullptr, s);
-        if (L.tc) return ffcu_tc_launch(L.tc, n, c->mode, L.epi, res, acc_dbg, c->bufs[d.dst_buf], out2, c->d_err, s);
+        if (L.tc) return ffcu_tc_launch(tc_plan_for(c, L, n), n, c->mode, L.epi, res, acc_dbg, c->bufs[d.dst_buf], out2, c->d_err, s);
         return ffcu_launch_conv_simt(d, n, c->mode, c->bufs[d.src_buf], L.w, L.epi, res, acc_dbg, c->bufs[d.dst_buf], out2, s);
     }
     case FFCU_BN:
@@ -315,7 +344,7 @@ static int launch_layer(ffcu_ctx* c, size_t k, int n, int32_t* acc_dbg, bool unf
         if (n <= FFCU_FC_SMALL_MAX_BATCH && d.Cout <= 512 && !c->no_fc_small)
             return ffcu_launch_fc_small(c->bufs[d.src_buf], L.w, L.epi.w_scale, L.epi.bias, n, d.Cout, d.Cin, c->mode,
                                         c->d_fc_scratch, c->d_out, s);
-        if (L.tc) return ffcu_tc_launch(L.tc, n, c->mode, L.epi, nullptr, nullptr, c->d_out, nullptr, c->d_err, s);
+        if (L.tc) return ffcu_tc_launch(tc_plan_for(c, L, n), n, c->mode, L.epi, nullptr, nullptr, c->d_out, nullptr, c->d_err, s);
         return ffcu_launch_fc_simt(c->bufs[d.src_buf], L.w, L.epi.w_scale, L.epi.bias, n, d.Cout, d.Cin,
                                    c->mode, c->d_out, s);
     }
@@ -356,6 +385,7 @@ static int run_forward(ffcu_ctx* c, int n, int slot)
         if (rc == 0) c->graph_launches[key] = c->launches;
         return rc;
     }
+    if (c->graphs.size() >= 64) return launch_forward(c, n);   // a serving loop with many distinct batch sizes: stay eager beyond 64 graphs
     cudaGraph_t graph = nullptr;
     FFCU_CHECK(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
     int rc = launch_forward(c, n);
@@ -441,8 +471,11 @@ extern "C" int ffcu_trace(ffcu_ctx* c, const float* host_in, int n, float* host_
     std::vector<uint8_t> host(max_elems * 4);
     int32_t* d_acc = nullptr;
     FFCU_CHECK(cudaMalloc(&d_acc, max_elems * sizeof(int32_t)));
-    FFCU_CHECK(cudaMemcpyAsync(c->d_in, host_in, (size_t)n * 37632 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
     int rc = 0;
+    {
+        cudaError_t e = cudaMemcpyAsync(c->d_in, host_in, (size_t)n * 37632 * sizeof(float), cudaMemcpyHostToDevice, c->stream);
+        if (e != cudaSuccess) { ffcu_set_error("ffcu_trace: input copy failed: %s", cudaGetErrorString(e)); cudaFree(d_acc); return -100; }
+    }
     for (size_t k = 0; k < c->layers.size() && rc == 0; k++) {
         const ffcu_layer& d = c->layers[k].d;
         rc = launch_layer(c, k, n, d.kind == FFCU_CONV ? d_acc : nullptr, true);
@@ -540,67 +573,119 @@ extern "C" int ffcu_bench_layers(ffcu_ctx* c, const float* host_in, int n, int i
 // ---------------------------------------------------------------------------
 // one conv layer on caller-supplied host tensors (single-layer parity tests)
 // ---------------------------------------------------------------------------
-extern "C" int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mode, int impl,
-                              const int8_t* in, const int8_t* res, int32_t* acc_out, int8_t* out, int8_t* out_bn2)
+static int conv_once_impl(int device, const ffcu_layer* l, int batch, int mode, int impl,
+                          const int8_t* in, const int8_t* res, int32_t* acc_out, int8_t* out, int8_t* out_bn2,
+                          int iters, float* ms)
 {
     if (!l || !in || batch < 1 || l->kind != FFCU_CONV) { ffcu_set_error("ffcu_conv_once: bad arguments"); return -1; }
     FFCU_CHECK(cudaSetDevice(device));
-    size_t in_bytes = (size_t)batch * l->H * l->W * l->Cin_pad;
-    size_t out_elems = (size_t)batch * l->Ho * l->Wo * l->Cout;
-    int8_t *d_in = nullptr, *d_res = nullptr, *d_out = nullptr, *d_w = nullptr, *d_out2 = nullptr;
+    const size_t in_bytes = (size_t)batch * l->H * l->W * l->Cin_pad;
+    const size_t out_elems = (size_t)batch * l->Ho * l->Wo * l->Cout;
+    int8_t *d_in = nullptr, *d_res = nullptr, *d_out = nullptr, *d_w = nullptr, *d_out2 = nullptr, *d_lut = nullptr;
     int32_t* d_acc = nullptr; int* d_err = nullptr;
     float* tab[9] = {};
+    cudaStream_t s = nullptr;
+    TcPlan* plan = nullptr;
     const bool bn2 = out_bn2 && l->bn2_in_scale && l->bn2_scale && l->bn2_offset && l->bn2_inv_out;
-    if (bn2) FFCU_CHECK(cudaMalloc(&d_out2, out_elems + 1024));
-    FFCU_CHECK(cudaMalloc(&d_in, in_bytes + 1024));
-    FFCU_CHECK(cudaMalloc(&d_out, out_elems + 1024));
-    FFCU_CHECK(cudaMalloc(&d_w, l->w_bytes + 1024));
-    FFCU_CHECK(cudaMalloc(&d_err, sizeof(int)));
-    FFCU_CHECK(cudaMemset(d_err, 0, sizeof(int)));
-    FFCU_CHECK(cudaMemset(d_w, 0, l->w_bytes + 1024));
-    FFCU_CHECK(cudaMemset(d_out, 0x55, out_elems + 1024));
-    if (acc_out) FFCU_CHECK(cudaMalloc(&d_acc, out_elems * 4));
-    if (res) { FFCU_CHECK(cudaMalloc(&d_res, out_elems)); FFCU_CHECK(cudaMemcpy(d_res, res, out_elems, cudaMemcpyHostToDevice)); }
-    FFCU_CHECK(cudaMemcpy(d_in, in, in_bytes, cudaMemcpyHostToDevice));
-    FFCU_CHECK(cudaMemcpy(d_w, l->w, l->w_bytes, cudaMemcpyHostToDevice));
+    int rc = 0;
+    // one exit: everything allocated so far is released whatever step failed
+#define ONCE_TRY(expr)                                                                           \
+    do {                                                                                         \
+        cudaError_t _e = (expr);                                                                 \
+        if (_e != cudaSuccess && rc == 0) {                                                      \
+            ffcu_set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+            rc = -100;                                                                           \
+        }                                                                                        \
+    } while (0)
+    if (bn2) ONCE_TRY(cudaMalloc(&d_out2, out_elems + 1024));
+    ONCE_TRY(cudaMalloc(&d_in, in_bytes + 1024));
+    ONCE_TRY(cudaMalloc(&d_out, out_elems + 1024));
+    ONCE_TRY(cudaMalloc(&d_w, l->w_bytes + 1024));
+    ONCE_TRY(cudaMalloc(&d_err, sizeof(int)));
+    if (acc_out) ONCE_TRY(cudaMalloc(&d_acc, out_elems * 4));
+    if (res) ONCE_TRY(cudaMalloc(&d_res, out_elems));
+    if (rc == 0) {
+        ONCE_TRY(cudaMemset(d_err, 0, sizeof(int)));
+        ONCE_TRY(cudaMemset(d_w, 0, l->w_bytes + 1024));
+        ONCE_TRY(cudaMemset(d_out, 0x55, out_elems + 1024));
+        if (res) ONCE_TRY(cudaMemcpy(d_res, res, out_elems, cudaMemcpyHostToDevice));
+        ONCE_TRY(cudaMemcpy(d_in, in, in_bytes, cudaMemcpyHostToDevice));
+        ONCE_TRY(cudaMemcpy(d_w, l->w, l->w_bytes, cudaMemcpyHostToDevice));
+    }
     const float* src[9] = {l->w_scale, l->bias, l->slope, l->res_scale, l->inv_out,
                            bn2 ? l->bn2_in_scale : nullptr, bn2 ? l->bn2_scale : nullptr,
                            bn2 ? l->bn2_offset : nullptr, bn2 ? l->bn2_inv_out : nullptr};
-    for (int k = 0; k < 9; k++) if (src[k]) tab[k] = upload_f32(src[k], l->Cout);
-    int8_t* d_lut = nullptr;
-    if (bn2) {
+    for (int k = 0; k < 9 && rc == 0; k++)
+        if (src[k]) {
+            tab[k] = upload_f32(src[k], l->Cout);
+            if (!tab[k]) { ffcu_set_error("ffcu_conv_once: table allocation or upload failed"); rc = -100; }
+        }
+    if (bn2 && rc == 0) {
         std::vector<int8_t> lut((size_t)l->Cout * 256);
         ff_bn_lut_build(l->bn2_in_scale, l->bn2_scale, l->bn2_offset, l->bn2_inv_out, l->Cout, lut.data());
-        FFCU_CHECK(cudaMalloc(&d_lut, lut.size()));
-        FFCU_CHECK(cudaMemcpy(d_lut, lut.data(), lut.size(), cudaMemcpyHostToDevice));
+        ONCE_TRY(cudaMalloc(&d_lut, lut.size()));
+        if (rc == 0) ONCE_TRY(cudaMemcpy(d_lut, lut.data(), lut.size(), cudaMemcpyHostToDevice));
     }
-    EpiTables t{tab[0], tab[1], tab[2], tab[3], tab[4], tab[5], tab[6], tab[7], tab[8], d_lut};
-    t.no_overflow = epilogue_cannot_overflow(l) ? 1 : 0;
-    cudaStream_t s; FFCU_CHECK(cudaStreamCreate(&s));
-    int rc = 0;
-    if (impl == 0) {
-        TcPlan* p = ffcu_tc_plan(*l, batch, d_in, d_w, device);
-        if (!p) { ffcu_set_error("layer shape is not covered by the tensor-core kernel"); rc = -2; }
-        else { rc = ffcu_tc_launch(p, batch, mode, t, d_res, d_acc, d_out, d_out2, d_err, s); }
-        if (rc == 0) { cudaStreamSynchronize(s); }
-        ffcu_tc_free(p);
-    } else {
-        rc = ffcu_launch_conv_simt(*l, batch, mode, d_in, d_w, t, d_res, d_acc, d_out, d_out2, s);
+    if (rc == 0) ONCE_TRY(cudaStreamCreate(&s));
+    if (rc == 0) {
+        EpiTables t{tab[0], tab[1], tab[2], tab[3], tab[4], tab[5], tab[6], tab[7], tab[8], d_lut};
+        t.no_overflow = epilogue_cannot_overflow(l) ? 1 : 0;
+        if (impl == 0) {
+            plan = ffcu_tc_plan(*l, batch, d_in, d_w, device, ffcu_tc_pick_bn(*l, batch, device));
+            if (!plan) { ffcu_set_error("layer shape is not covered by the tensor-core kernel"); rc = -2; }
+            else rc = ffcu_tc_launch(plan, batch, mode, t, d_res, d_acc, d_out, d_out2, d_err, s);
+        } else {
+            rc = ffcu_launch_conv_simt(*l, batch, mode, d_in, d_w, t, d_res, d_acc, d_out, d_out2, s);
+        }
     }
     if (rc == 0) {
         cudaError_t e = cudaStreamSynchronize(s);
         if (e != cudaSuccess) { ffcu_set_error("kernel failed: %s", cudaGetErrorString(e)); rc = -100; }
     }
+    if (rc == 0 && iters > 0 && ms) {
+        // timing: `iters` more launches of the same layer between two events on its stream
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        ONCE_TRY(cudaEventCreate(&e0));
+        ONCE_TRY(cudaEventCreate(&e1));
+        EpiTables t{tab[0], tab[1], tab[2], tab[3], tab[4], tab[5], tab[6], tab[7], tab[8], d_lut};
+        t.no_overflow = epilogue_cannot_overflow(l) ? 1 : 0;
+        if (rc == 0) ONCE_TRY(cudaEventRecord(e0, s));
+        for (int it = 0; it < iters && rc == 0; it++)
+            rc = impl == 0 ? ffcu_tc_launch(plan, batch, mode, t, d_res, d_acc, d_out, d_out2, d_err, s)
+                           : ffcu_launch_conv_simt(*l, batch, mode, d_in, d_w, t, d_res, d_acc, d_out, d_out2, s);
+        if (rc == 0) ONCE_TRY(cudaEventRecord(e1, s));
+        if (rc == 0) ONCE_TRY(cudaEventSynchronize(e1));
+        float total = 0;
+        if (rc == 0) ONCE_TRY(cudaEventElapsedTime(&total, e0, e1));
+        if (rc == 0) *ms = total / iters;
+        if (e0) cudaEventDestroy(e0);
+        if (e1) cudaEventDestroy(e1);
+    }
     if (rc == 0) {
         int herr = 0;
-        cudaMemcpy(&herr, d_err, sizeof(int), cudaMemcpyDeviceToHost);
-        if (herr) { ffcu_set_error("device reported error word %d", herr); rc = 1000 + herr; }
+        ONCE_TRY(cudaMemcpy(&herr, d_err, sizeof(int), cudaMemcpyDeviceToHost));
+        if (rc == 0 && herr) { ffcu_set_error("device reported error word %d (a bounded wait inside a kernel ran out)", herr); rc = 1000 + herr; }
     }
-    if (rc == 0 && acc_out) cudaMemcpy(acc_out, d_acc, out_elems * 4, cudaMemcpyDeviceToHost);
-    if (rc == 0 && out) cudaMemcpy(out, d_out, out_elems, cudaMemcpyDeviceToHost);
-    if (rc == 0 && bn2) cudaMemcpy(out_bn2, d_out2, out_elems, cudaMemcpyDeviceToHost);
-    cudaStreamDestroy(s);
+    if (rc == 0 && acc_out) ONCE_TRY(cudaMemcpy(acc_out, d_acc, out_elems * 4, cudaMemcpyDeviceToHost));
+    if (rc == 0 && out) ONCE_TRY(cudaMemcpy(out, d_out, out_elems, cudaMemcpyDeviceToHost));
+    if (rc == 0 && bn2) ONCE_TRY(cudaMemcpy(out_bn2, d_out2, out_elems, cudaMemcpyDeviceToHost));
+#undef ONCE_TRY
+    if (plan) ffcu_tc_free(plan);
+    if (s) cudaStreamDestroy(s);
     cudaFree(d_lut); cudaFree(d_in); cudaFree(d_res); cudaFree(d_out); cudaFree(d_out2); cudaFree(d_w); cudaFree(d_acc); cudaFree(d_err);
     for (float* q : tab) cudaFree(q);
     return rc;
+}
+
+extern "C" int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mode, int impl,
+                              const int8_t* in, const int8_t* res, int32_t* acc_out, int8_t* out, int8_t* out_bn2)
+{
+    return conv_once_impl(device, l, batch, mode, impl, in, res, acc_out, out, out_bn2, 0, nullptr);
+}
+
+extern "C" int ffcu_conv_bench(int device, const ffcu_layer* l, int batch, int mode, int impl,
+                               const int8_t* in, const int8_t* res, int8_t* out, int8_t* out_bn2, int iters, float* ms)
+{
+    if (iters < 1 || !ms) { ffcu_set_error("ffcu_conv_bench: bad arguments"); return -1; }
+    return conv_once_impl(device, l, batch, mode, impl, in, res, nullptr, out, out_bn2, iters, ms);
 }

@@ -118,65 +118,6 @@ __device__ __forceinline__ float ffcu_conv_fp(int acc, float ws, float bias, boo
     return t;
 }
 
-// Two-lane fp32 arithmetic (sm_100: fma / mul / add .f32x2).  Each lane is the IEEE operation with
-// round-to-nearest-even, i.e. exactly __fmaf_rn / __fmul_rn / __fadd_rn on that lane: one issued
-// instruction instead of two in the epilogue's per-element chain.
-__device__ __forceinline__ unsigned long long ffcu_pack2(float x, float y)
-{
-    unsigned long long r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
-    return r;
-}
-__device__ __forceinline__ void ffcu_unpack2(unsigned long long v, float& x, float& y)
-{
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(v));
-}
-__device__ __forceinline__ unsigned long long ffcu_fma2(unsigned long long a, unsigned long long b, unsigned long long c)
-{
-    unsigned long long d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ unsigned long long ffcu_mul2(unsigned long long a, unsigned long long b)
-{
-    unsigned long long d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ unsigned long long ffcu_add2(unsigned long long a, unsigned long long b)
-{
-    unsigned long long d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-
-// Contract-mode epilogue of two adjacent channels, unchecked conversion (layers with the
-// overflow proof): the same operations, in the same order, as ffcu_conv_fp<true> followed by
-// ffcu_requant_nosat<false>, with the fma / mul / add steps done two lanes at a time.
-__device__ __forceinline__ void ffcu_conv_q2(int acc0, int acc1, float ws0, float ws1, float bi0, float bi1,
-                                             bool has_res, int res0, int res1, float rs0, float rs1,
-                                             bool has_slope, float sl0, float sl1, float iv0, float iv1,
-                                             int& q0, int& q1)
-{
-    unsigned long long t = ffcu_fma2(ffcu_pack2(__int2float_rn(acc0), __int2float_rn(acc1)), ffcu_pack2(ws0, ws1), ffcu_pack2(bi0, bi1));
-    if (has_res) t = ffcu_fma2(ffcu_pack2(__int2float_rn(res0), __int2float_rn(res1)), ffcu_pack2(rs0, rs1), t);
-    float t0, t1;
-    ffcu_unpack2(t, t0, t1);
-    if (has_slope) {
-        if (t0 < 0.0f) t0 = __fmul_rn(t0, sl0);
-        if (t1 < 0.0f) t1 = __fmul_rn(t1, sl1);
-    }
-    const unsigned long long q = ffcu_mul2(ffcu_pack2(t0, t1), ffcu_pack2(iv0, iv1));
-    float qa, qb;
-    ffcu_unpack2(q, qa, qb);
-    const float h0 = __int_as_float(0x3f000000 | (__float_as_int(qa) & 0x80000000));
-    const float h1 = __int_as_float(0x3f000000 | (__float_as_int(qb) & 0x80000000));
-    float r0, r1;
-    ffcu_unpack2(ffcu_add2(q, ffcu_pack2(h0, h1)), r0, r1);
-    q0 = __float2int_rz(r0);
-    q1 = __float2int_rz(r1);
-}
-
 // Standalone BN pass (reference kernels/int8_epilogue.c:272-303): explicit fma in the source.
 __device__ __forceinline__ int ffcu_bn_q(int a, float in_scale, float bn_scale, float bn_offset, float inv)
 {
@@ -218,7 +159,6 @@ int ffcu_launch_fc_small(const int8_t* act, const int8_t* w, const float* w_scal
 // Tensor-core implicit GEMM (conv_tc.cu)
 // ---------------------------------------------------------------------------
 struct TcPlan;   // opaque: tile shape, TMA descriptors, launch geometry for one layer
-// NULL when the layer shape is not covered by the tensor-core kernel.
 int ffcu_launch_stem_pack(const void* in_any, int in_u8, const float* inv3, int batch, int8_t* col, cudaStream_t s);
 int ffcu_stem_weight_k32(const int8_t* d_w, int8_t* d_wk, int Cout, cudaStream_t s);
 // Tensor-core stem: plan over the im2col buffer d_col [max_batch * 12544][32] and the repacked weights d_wk [64][32]
@@ -227,7 +167,10 @@ StemTcPlan* ffcu_stem_tc_plan(int max_batch, const int8_t* d_col, const int8_t* 
 void ffcu_stem_tc_free(StemTcPlan* p);
 int ffcu_stem_tc_launch(const StemTcPlan* p, int batch, int mode, const EpiTables& t, int8_t* out, int8_t* out_bn2,
                         int* d_err, cudaStream_t s);
-TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, const int8_t* d_w, int device);
+// Column-tile width (64 / 128 / 256) for a call of `batch` faces, and the plan for one width.
+int     ffcu_tc_pick_bn(const ffcu_layer& L, int batch, int device);
+// NULL when the layer shape is not covered by the tensor-core kernels.
+TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, const int8_t* d_w, int device, int bn);
 void    ffcu_tc_free(TcPlan* p);
 int     ffcu_tc_launch(const TcPlan* p, int batch, int mode, const EpiTables& t, const int8_t* res,
                        int32_t* acc_out, void* out, int8_t* out_bn2, int* d_err, cudaStream_t s);

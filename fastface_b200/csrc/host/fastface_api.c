@@ -97,6 +97,12 @@ FastFace* fastface_create_ex(const char* ffw4_path, const int* device_ids, int n
     }
 
     FastFace* ff = (FastFace*)calloc(1, sizeof(FastFace));
+    if (!ff) {
+        api_error("out of memory");
+        fprintf(stderr, "fastface: %s\n", g_api_err);
+        ff_plan_free(&plan); ff_model_free(&model);
+        return NULL;
+    }
     ff->n_dev = n_devices; ff->max_batch = max_batch; ff->n_ops = model.n_ops;
     int mode = FF_EPILOGUE_CONTRACT;
     const char* em = getenv("FF_EPILOGUE");
@@ -145,6 +151,7 @@ void fastface_destroy(FastFace* ff)
 typedef struct {
     ffcu_ctx* ctx; const float* in; float* out; int n; int max_batch; int rc;
     const uint8_t* in_u8;      /* non-NULL: 8-bit pixel input instead of `in` */
+    char err[256];             /* the CUDA side's message, copied on the thread that ran the job */
 } dev_job;
 
 static void* dev_job_run(void* arg)
@@ -161,6 +168,9 @@ static void* dev_job_run(void* arg)
     }
     int rc = ffcu_wait(j->ctx);
     if (j->rc == 0) j->rc = rc;
+    /* the CUDA side keeps its last message per thread: take it here, where it was set */
+    j->err[0] = 0;
+    if (j->rc != 0) snprintf(j->err, sizeof j->err, "%s", ffcu_last_error());
     return NULL;
 }
 
@@ -200,15 +210,19 @@ static int embed_batch_any(FastFace* ff, const float* input_hwc, const uint8_t* 
     for (int d = 0; d < used; d++)
         jobs[d] = (dev_job){ ff->dev[d], input_hwc ? input_hwc + (size_t)starts[d] * FASTFACE_INPUT_N : NULL,
                              out_emb + (size_t)starts[d] * FASTFACE_OUTPUT_N, counts[d], ff->max_batch, 0,
-                             pixels_hwc ? pixels_hwc + (size_t)starts[d] * FASTFACE_INPUT_N : NULL };
+                             pixels_hwc ? pixels_hwc + (size_t)starts[d] * FASTFACE_INPUT_N : NULL, {0} };
     if (used == 1) {
         dev_job_run(&jobs[0]);
     } else {
-        for (int d = 0; d < used; d++) pthread_create(&th[d], NULL, dev_job_run, &jobs[d]);
-        for (int d = 0; d < used; d++) pthread_join(th[d], NULL);
+        int started[FF_MAX_DEVICES];
+        for (int d = 0; d < used; d++) started[d] = pthread_create(&th[d], NULL, dev_job_run, &jobs[d]) == 0;
+        for (int d = 0; d < used; d++) {
+            if (started[d]) pthread_join(th[d], NULL);
+            else dev_job_run(&jobs[d]);          /* no thread to be had: run this device's share here */
+        }
     }
     for (int d = 0; d < used; d++)
-        if (jobs[d].rc != 0) return jobs[d].rc;
+        if (jobs[d].rc != 0) { api_error(jobs[d].err); return jobs[d].rc; }
     return 0;
 }
 

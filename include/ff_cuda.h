@@ -123,6 +123,31 @@ int ffcu_layer_info(const ffcu_ctx* c, int k, ffcu_layer* out, int* uses_tc);
 int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mode, int impl,
                    const int8_t* in, const int8_t* res, int32_t* acc_out, int8_t* out, int8_t* out_bn2);
 
+/* The same layer, timed: after one run (whose int8 output is returned), `iters` more launches between
+ * two CUDA events on the layer's stream; *ms = mean milliseconds per launch.  The single-layer
+ * microbenchmark (the reference's bench_batched_conv.c measures its CPU kernels the same way). */
+int ffcu_conv_bench(int device, const ffcu_layer* l, int batch, int mode, int impl,
+                    const int8_t* in, const int8_t* res, int8_t* out, int8_t* out_bn2, int iters, float* ms);
+
+/* 3x3 stride-1 pad-1 convolution by exact-integer Winograd F(2,3) on the CUDA cores (reference
+ * kernels/winograd_int8_ref.c:117-179; int16 transformed operands, which the int8 tensor cores
+ * cannot take): host tensors in int8 [B][H][W][Cin], w int8 OIHW -> out int32 [B][H][W][Cout],
+ * equal to 4 x the direct convolution's accumulators (:237-259).  *ms = mean CUDA-event time of
+ * `iters` runs of the convolution kernel (the weight transform is a load-time step and not timed).
+ * Needs H, W multiples of 8, Cin a multiple of 16 (<= 128), Cout a multiple of 64.  Kept as the
+ * measured alternative to the implicit GEMM; the forward pass does not use it. */
+int ffcu_winograd_f23_once(int device, const int8_t* in, const int8_t* w_oihw, int B, int H, int W, int Cin,
+                           int Cout, int iters, int32_t* out, float* ms);
+
+/* Test hook for the bounded waits (no counterpart in the reference): arms the NEXT launch of the
+ * one-CTA per-tap convolution kernel so that its TMA producer leaves out K step `drop_stage` of
+ * its first tile, and the MMA issuer's wait for that step's data gives up after
+ * `full_wait_cycles` SM cycles instead of the default two seconds.  The kernel then takes its
+ * abort path: it records the error word, every role leaves its loop, tensor memory is freed and
+ * the launch returns; ffcu_conv_once / ffcu_wait report 1000 + the error word.  Nothing faults,
+ * traps or spins without a limit, and the hook disarms itself after that one launch. */
+void ffcu_test_arm_timeout(int drop_stage, long long full_wait_cycles);
+
 /* Small-batch FC (batch <= 16, N <= 512) that allocates nothing: no counterpart in the
  * reference.  For callers that hold device buffers but cannot call cudaMalloc -- a serving loop
  * that cannot afford an allocation's device-wide synchronisation, a plug-in given buffers but no
@@ -130,6 +155,8 @@ int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mode, int imp
  * needs is a fixed 32 KiB array inside the library's device image.  act int8 [batch][K],
  * w int8 [N][K], w_scale / bias f32 [N], out f32 [batch][N]: all DEVICE pointers; stream is a
  * cudaStream_t (NULL = default stream).  Sizes beyond the limit return -2 with a message.
+ * act and w must be 16-byte aligned, K a positive multiple of 16, N a multiple of 8, and
+ * w_scale / bias / out 4-byte aligned; anything else returns -1 before a kernel is launched.
  * Every call on a device shares the one array (cleared at the start of each call): calls that
  * can overlap on the GPU race.  The first call on a device resolves the array's address; make
  * it outside any stream capture.  Computes out = bias + (float)dot * w_scale exactly as the FC
@@ -137,13 +164,13 @@ int ffcu_conv_once(int device, const ffcu_layer* l, int batch, int mode, int imp
 int ffcu_fc_small_noalloc(const int8_t* act, const int8_t* w, const float* w_scale, const float* bias,
                           int batch, int N, int K, int mode, float* out, void* stream);
 
-/* Dense INT8 tensor-core throughput (TOP/s, 2 ops per MAC) measured with operands already in
- * shared memory: M=128, N=bn (64/128/256), all SMs busy, `iters` rounds of four K=32 MMAs.
- * The practical ceiling the convolution kernels are compared against. */
 /* Cosine-similarity matrix out[n][m] of host embeddings a[n][512], b[m][512] with the float64
  * accumulation of the reference's Go wrapper (go/fastface/fastface.go:157-168), bit for bit. */
 int ffcu_cos_sim_matrix(int device, const float* a, int n, const float* b, int m, float* out);
 
+/* Dense INT8 tensor-core throughput (TOP/s, 2 ops per MAC) measured with operands already in
+ * shared memory: M=128, N=bn (64/128/256), all SMs busy, `iters` rounds of four K=32 MMAs.
+ * The practical ceiling the convolution kernels are compared against. */
 int ffcu_i8_mma_peak(int device, int bn, int iters, float* tops, float* ms);
 
 const char* ffcu_last_error(void);

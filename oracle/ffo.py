@@ -184,6 +184,45 @@ class RefLib:
             self.h = None
 
 
+def ref_embed_many(model_root: str, ffw4: str, faces: np.ndarray, batch: int = 32, threads: Optional[int] = None) -> np.ndarray:
+    """Embeddings of any number of faces from the reference's batched CLI through its --server
+    protocol (arcface_forward_int8_batched.c:531-553), `batch` faces per request; the last
+    request is padded with copies of the last face.  The reference treats the faces of a batch
+    independently, so the batch size of the requests does not change a face's result."""
+    exe = os.path.join(REF_DIR, "fastface_int8_batched")
+    faces = np.ascontiguousarray(faces, dtype=np.float32).reshape(-1, 112, 112, 3)
+    n = faces.shape[0]
+    env = dict(os.environ)
+    env.pop("OPSC2_PATH", None)
+    if threads:
+        env["OMP_NUM_THREADS"] = str(threads)
+    p = subprocess.Popen([exe, os.path.abspath(ffw4), "--batch", str(batch), "--server"], cwd=model_root, env=env,
+                         stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, bufsize=0)
+    out = np.empty((n, 512), np.float32)
+    try:
+        for k in range(0, n, batch):
+            chunk = faces[k:k + batch]
+            if chunk.shape[0] < batch:
+                chunk = np.concatenate([chunk, np.repeat(chunk[-1:], batch - chunk.shape[0], 0)])
+            p.stdin.write(chunk.tobytes())
+            p.stdin.flush()
+            need, buf = batch * 512 * 4, b""
+            while len(buf) < need:
+                part = p.stdout.read(need - len(buf))
+                if not part:
+                    raise RuntimeError("reference server closed its pipe")
+                buf += part
+            emb = np.frombuffer(buf, np.float32).reshape(batch, 512)
+            out[k:k + batch] = emb[:min(batch, n - k)]
+    finally:
+        try:
+            p.stdin.close()
+            p.wait(timeout=30)
+        except Exception:
+            p.kill()
+    return out
+
+
 def run_ref_trace(model_root: str, ffw4: str, faces: np.ndarray, strict: bool = False,
                   dump_dir: Optional[str] = None, threads: Optional[int] = None):
     """Run the traced reference CLI on the given faces (arcface_forward_int8_batched.c

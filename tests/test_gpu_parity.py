@@ -122,6 +122,69 @@ def test_single_layer_vs_oracle(built_lib, case, impl, monkeypatch):
         assert not msg, msg
 
 
+
+# Row geometries and tile counts that only large batches reach.  The 128-pixel row tile is
+# {TW, TH, TB} = 16x8x1 on 112x112, 8x8x2 on 56x56, 4x4x8 on 28x28, 2x2x32 on 14x14 and 1x1x128 on
+# 7x7 once the batch is large enough, and a CTA (or CTA pair) then walks many tiles: more than
+# twice its accumulator ring, with the stage ring's phase flipping many times on the way.
+BIG_LAYER_CASES = [
+    # name, B, H, Cin, Cout, k, stride, slope, res
+    ("big_s1_512_512_7_add_B128", 128, 7, 512, 512, 3, 1, False, True),
+    ("big_s1_256_256_14_prelu_B64", 64, 14, 256, 256, 3, 1, True, False),
+    ("big_s1_256_256_14_add_B392", 392, 14, 256, 256, 3, 1, False, True),
+    ("big_s1_256_512_14_prelu_B64", 64, 14, 256, 512, 3, 1, True, False),
+    ("big_s1_256_256_14_add_B33", 33, 14, 256, 256, 3, 1, False, True),
+    ("big_s1_128_128_28_add_B16", 16, 28, 128, 128, 3, 1, False, True),
+    ("big_s1_128_128_28_prelu_B200", 200, 28, 128, 128, 3, 1, True, False),
+    ("big_s1_128_256_28_prelu_B40", 40, 28, 128, 256, 3, 1, True, False),
+    ("big_s1_64_64_56_prelu_B100", 100, 56, 64, 64, 3, 1, True, False),
+    ("big_s1_64_64_56_add_B37", 37, 56, 64, 64, 3, 1, False, True),
+    ("big_s1_64_128_56_prelu_B24", 24, 56, 64, 128, 3, 1, True, False),
+    ("big_s1_64_64_112_prelu_B24", 24, 112, 64, 64, 3, 1, True, False),
+    ("big_s2_64_64_112_B20", 20, 112, 64, 64, 3, 2, False, False),
+    ("big_s2_128_128_56_B33", 33, 56, 128, 128, 3, 2, False, False),
+    ("big_s2_256_256_28_B64", 64, 28, 256, 256, 3, 2, False, False),
+    ("big_s2_512_512_14_B130", 130, 14, 512, 512, 3, 2, False, False),
+    ("big_sc_64_64_112_add_B20", 20, 112, 64, 64, 1, 2, False, True),
+    ("big_sc_64_128_56_add_B33", 33, 56, 64, 128, 1, 2, False, True),
+    ("big_sc_128_256_28_add_B64", 64, 28, 128, 256, 1, 2, False, True),
+    ("big_sc_256_512_14_add_B130", 130, 14, 256, 512, 1, 2, False, True),
+]
+
+
+@pytest.mark.parametrize("case", BIG_LAYER_CASES, ids=[c[0] for c in BIG_LAYER_CASES])
+def test_single_layer_large_batch_vs_oracle(built_lib, case):
+    """The kernels and tilings large batches run (no override: the library picks them from the batch),
+    with the fused BN second output on the residual layers as in the network."""
+    name, B, H, Cin, Cout, k, stride, sl, rs = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
+    bn2 = None
+    if rs:
+        in_scale = (np.float32(1) / L["inv"]).astype(np.float32)
+        bn_s = rng.uniform(0.5, 1.5, Cout).astype(np.float32)
+        bn_o = (rng.standard_normal(Cout) * 0.1).astype(np.float32)
+        bn_inv = (np.float32(1) / (rng.uniform(0.005, 0.05, Cout).astype(np.float32) + np.float32(1e-9))).astype(np.float32)
+        bn2 = (in_scale, bn_s, bn_o, bn_inv)
+    got = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
+                       slope=L["slope"], res=L["res"], res_scale=L["rs"], impl="tc", bn2=bn2)
+    acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
+                               L["res"], L["rs"], ffo.CONTRACT)
+    msg = describe_mismatch("int32 accumulators", got[0], acc_o)
+    assert not msg, msg
+    msg = describe_mismatch("int8 output", got[1], out_o)
+    assert not msg, msg
+    if bn2:
+        lib = _libffo()
+        want2 = np.zeros_like(out_o)
+        lib.ffo_bn_requant.argtypes = [C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                       C.c_float, C.c_void_p, C.c_int, C.c_int]
+        lib.ffo_bn_requant(out_o.ctypes.data, 1.0, bn2[0].ctypes.data, bn2[1].ctypes.data, bn2[2].ctypes.data, None,
+                           bn2[3].ctypes.data, 1.0, want2.ctypes.data, out_o.size // Cout, Cout)
+        msg = describe_mismatch("fused BN output", got[2], want2)
+        assert not msg, msg
+
+
 @pytest.mark.parametrize("impl", ["tc", "simt"])
 def test_requant_out_of_range_matches_x86_conversion(built_lib, impl):
     """With a requant scale so large that t * inv leaves the int32 range, the reference's
@@ -232,82 +295,6 @@ def test_fused_bn_by_arithmetic(built_lib, case, monkeypatch):
     assert not msg, msg
 
 
-@pytest.mark.parametrize("case", [LAYER_CASES[4], LAYER_CASES[9], LAYER_CASES[13]], ids=lambda c: c[0])
-def test_two_issuer_warps_option(built_lib, case, monkeypatch):
-    """FF_TC_ISSUERS=2 lets two warps issue the MMAs of alternate tiles in the per-tap kernels (an option that
-    measured no faster there; the weight-stationary and stem kernels always use two).  Same bytes."""
-    monkeypatch.setenv("FF_TC_ISSUERS", "2")
-    name, B, H, Cin, Cout, k, stride, sl, rs = case
-    force_wide_tiles(monkeypatch, Cout)
-    rng = np.random.default_rng(zlib.crc32(name.encode()) + 13)
-    L = random_layer(rng, B * 3, H, Cin, Cout, k, stride, sl, rs)
-    acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
-                            slope=L["slope"], res=L["res"], res_scale=L["rs"], impl="tc")
-    acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
-                               L["res"], L["rs"], ffo.CONTRACT)
-    msg = describe_mismatch("int32 accumulators", acc, acc_o)
-    assert not msg, msg
-    msg = describe_mismatch("int8 output", out, out_o)
-    assert not msg, msg
-
-
-@pytest.mark.parametrize("case", [LAYER_CASES[0], LAYER_CASES[2], LAYER_CASES[6], LAYER_CASES[13]], ids=lambda c: c[0])
-def test_two_lane_fp32_epilogue_option(built_lib, case, monkeypatch):
-    """FF_TC_X2=1 evaluates the contract-mode epilogue with fma / mul / add .f32x2 (two channels per
-    instruction, each lane the same IEEE operation); same bytes as the oracle."""
-    monkeypatch.setenv("FF_TC_X2", "1")
-    name, B, H, Cin, Cout, k, stride, sl, rs = case
-    force_wide_tiles(monkeypatch, Cout)
-    rng = np.random.default_rng(zlib.crc32(name.encode()) + 19)
-    L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
-    acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
-                            slope=L["slope"], res=L["res"], res_scale=L["rs"], impl="tc")
-    acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
-                               L["res"], L["rs"], ffo.CONTRACT)
-    msg = describe_mismatch("int8 output", out, out_o)
-    assert not msg, msg
-
-
-@pytest.mark.parametrize("case", LAYER_CASES[:4], ids=lambda c: c[0])
-def test_weight_stationary_pair_kernel(built_lib, case, monkeypatch):
-    """FF_TC_WS2=1 runs the 64-input-channel 3x3 stride-1 layers on the CTA-pair form of the
-    weight-stationary kernel (cta_group::2, half the weights per CTA); same bytes as the oracle,
-    including an odd number of tiles (the pair's second CTA then works on a tile past the batch)."""
-    monkeypatch.setenv("FF_TC_WS2", "1")
-    name, B, H, Cin, Cout, k, stride, sl, rs = case
-    force_wide_tiles(monkeypatch, Cout)
-    rng = np.random.default_rng(zlib.crc32(name.encode()) + 17)
-    L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
-    acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
-                            slope=L["slope"], res=L["res"], res_scale=L["rs"], impl="tc")
-    acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
-                               L["res"], L["rs"], ffo.CONTRACT)
-    msg = describe_mismatch("int32 accumulators", acc, acc_o)
-    assert not msg, msg
-    msg = describe_mismatch("int8 output", out, out_o)
-    assert not msg, msg
-
-
-@pytest.mark.parametrize("case", LAYER_CASES[4:8], ids=lambda c: c[0])
-def test_tap_shift_kernel(built_lib, case, monkeypatch):
-    """FF_TC_SHIFT=1 routes the 3x3 stride-1 layers on 14x14 / 28x28 maps through the CTA-pair
-    kernel that keeps the activation patch in shared memory for all nine taps (each tap is the
-    same buffer read from a shifted descriptor start address); same bytes as the oracle."""
-    monkeypatch.setenv("FF_TC_SHIFT", "1")
-    name, B, H, Cin, Cout, k, stride, sl, rs = case
-    force_wide_tiles(monkeypatch, Cout)
-    rng = np.random.default_rng(zlib.crc32(name.encode()) + 5)
-    L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
-    acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
-                            slope=L["slope"], res=L["res"], res_scale=L["rs"], impl="tc")
-    acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
-                               L["res"], L["rs"], ffo.CONTRACT)
-    msg = describe_mismatch("int32 accumulators", acc, acc_o)
-    assert not msg, msg
-    msg = describe_mismatch("int8 output", out, out_o)
-    assert not msg, msg
-
-
 @pytest.mark.parametrize("case", [c for c in LAYER_CASES if c[3] >= 128], ids=lambda c: c[0])
 def test_wide_layers_on_the_single_cta_kernel(built_lib, case, monkeypatch):
     """FF_TC_PAIR=0 routes the >=128-input-channel layers through the one-CTA kernel instead of
@@ -322,6 +309,36 @@ def test_wide_layers_on_the_single_cta_kernel(built_lib, case, monkeypatch):
     acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
                                L["res"], L["rs"], ffo.CONTRACT)
     assert np.array_equal(acc, acc_o) and np.array_equal(out, out_o)
+
+
+@pytest.mark.parametrize("shape", [(8, 56, 64, 64), (3, 112, 64, 64), (2, 56, 64, 128), (5, 24, 128, 128), (2, 8, 16, 64)],
+                         ids=lambda s: "B%d_H%d_%dto%d" % s)
+def test_integer_winograd_f23_equals_four_times_direct(built_lib, shape):
+    """The exact-integer Winograd F(2,3) kernel (the measured alternative for the 3x3 stride-1 layers): its
+    int32 output must equal 4 x the direct convolution's accumulators, the property the reference's own
+    Winograd self-test checks (kernels/winograd_int8_ref.c:237-259); the first shape is the single-layer
+    case of the benchmark configuration, 56x56 64->64 batch 8, with full-range int8 operands."""
+    B, H, Cin, Cout = shape
+    rng = np.random.default_rng(B * 1000 + H + Cin)
+    x = rng.integers(-127, 128, size=(B, H, H, Cin), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(Cout, Cin, 3, 3), dtype=np.int8)
+    lib = _libffo()
+    acc = np.zeros((B, H, H, Cout), np.int32)
+    lib.ffo_conv_i32(x.ctypes.data_as(C.c_void_p), B, Cin, H, H, w.ctypes.data_as(C.c_void_p), Cout, 3, 3, 1, 1, H, H,
+                     acc.ctypes.data_as(C.c_void_p))
+    y4, ms = ff.winograd_f23(x, w, iters=2)
+    msg = describe_mismatch("Winograd output vs 4 x direct", y4, acc * 4)
+    assert not msg, msg
+    assert ms > 0
+
+
+def test_layer_microbench_reports_both_kernels(built_lib):
+    """python -m fastface_b200.layer_bench: the single-layer case (56x56, 64->64, batch 8) on the tensor-core
+    implicit GEMM with the Winograd kernel timed beside it on the same tensors."""
+    from fastface_b200 import layer_bench
+    line = layer_bench.run("conv56", 8, 5, False, True)
+    assert line["winograd_f23"]["equals_4x_direct"] is True
+    assert line["ms_per_launch"] > 0 and line["winograd_f23"]["ms_per_launch"] > 0
 
 
 def test_stem_conv_simt_vs_oracle(built_lib):
@@ -408,6 +425,123 @@ def test_network_layers_vs_oracle(engine, oracle, B):
     assert np.array_equal(emb, oracle.forward(faces, ffo.CONTRACT))
 
 
+def _spread(n, k=40):
+    """Indices over a batch of n: the ends, both sides of every 128-face boundary, and a seeded sample."""
+    idx = {0, 1, n - 2, n - 1}
+    for b in range(128, n, 128):
+        idx.update((b - 1, b))
+    rng = np.random.default_rng(n)
+    idx.update(int(i) for i in rng.integers(0, n, size=k))
+    return sorted(i for i in idx if 0 <= i < n)
+
+
+@pytest.mark.parametrize("B", [64, 256, 1024])
+def test_network_at_the_benchmark_batches(built_lib, model_root, ffw4, oracle, B):
+    """The launch lists the benchmark times: a context created for batch 64 / 256 / 1024 with no override, so
+    the row tile, the column tile, the tensor-core FC and the CUDA-graph replay are the ones those batches
+    get.  Embeddings bit for bit against the unmodified reference's batched CLI where it can run (every
+    face), else against the C port on faces spread over the batch (the reference treats the faces of a
+    batch independently, arcface_forward_int8_batched.c:402-410)."""
+    faces = synth.faces(B, seed=300 + B)
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=B) as e:
+        first = e.embed_batch(faces)            # eager launches
+        e.embed_batch(faces)                    # second call on the other slot
+        got = e.embed_batch(faces)              # third call: the captured graph
+        part = e.embed_batch(faces[:B - 7])     # a ragged batch through the same context
+    assert np.array_equal(first, got)
+    assert np.array_equal(part, got[:B - 7])
+    if ffo.ref_available():
+        want = ffo.ref_embed_many(model_root, ffw4, faces, batch=32)
+        bad = np.flatnonzero((got != want).any(axis=1))
+        assert bad.size == 0, f"{bad.size} of {B} faces differ from the reference, first {bad[:8].tolist()}"
+    else:
+        idx = _spread(B)
+        want = oracle.forward(faces[idx], ffo.CONTRACT)
+        bad = [i for j, i in enumerate(idx) if not np.array_equal(got[i], want[j])]
+        assert not bad, f"faces {bad[:8]} differ from the oracle"
+
+
+@pytest.mark.parametrize("mode,strict", [(ff.EPILOGUE_CONTRACT, False), (ff.EPILOGUE_STRICT, True)])
+def test_network_trace_at_batch_64(built_lib, model_root, ffw4, oracle, mode, strict):
+    """Every dump point (int32 accumulators, int8 activations, embeddings) at batch 64, in both epilogue
+    orders, against the reference's traced driver run on the same faces (the C port where it cannot run)."""
+    faces = synth.faces(64, seed=64)
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=64) as e:
+        e.set_epilogue_mode(mode)
+        emb, recs = gpu_crc_trace(e, faces)
+    if ffo.ref_available():
+        want, gold = ffo.run_ref_trace(model_root, ffw4, faces, strict=strict)
+    else:
+        want, gold = oracle.forward_crc(faces, mode)
+    bad = [(g, r) for g, r in zip(gold, recs) if g != r]
+    assert len(recs) == len(gold) and not bad, f"first mismatching dump points (want, got): {bad[:4]}"
+    assert np.array_equal(emb, want)
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_network_other_model_seeds(built_lib, tmp_path_factory, seed):
+    """Synthetic models of seeds 1 and 2 (other weights, scales and calibration tables): every dump
+    point at batch 3 against the C port, embeddings at batch 8 and 40 against port and live reference."""
+    root = str(tmp_path_factory.mktemp(f"ffmodel_seed{seed}"))
+    path = synth.materialize(root, seed)
+    orc = ffo.Oracle(path, os.path.join(root, "models", "op_scales.bin"), os.path.join(root, "models", "op_scales_v2.bin"))
+    faces = synth.faces(40, seed=500 + seed)
+    want = {}
+    orc.forward(faces[:3], ffo.CONTRACT, lambda op, kind, arr: want.__setitem__((op, ffo.KIND_LETTER[kind]), arr.copy()))
+    first = []
+
+    def fn(op, kind, arr):
+        if not np.array_equal(arr, want[(op, kind)]) and len(first) < 3:
+            first.append(f"op {op} kind {kind}: {(arr != want[(op, kind)]).sum()}/{arr.size} differ")
+
+    with ff.FastFace(path, cwd=root, max_batch=40) as e:
+        e.trace(faces[:3], fn)
+        assert not first, "; ".join(first)
+        got8 = e.embed_batch(faces[:8])
+        got40 = e.embed_batch(faces)
+    assert np.array_equal(got8, orc.forward(faces[:8], ffo.CONTRACT))
+    assert np.array_equal(got40[:8], got8)
+    if ffo.ref_available():
+        assert np.array_equal(got40, ffo.ref_embed_many(root, path, faces, batch=8))
+    else:
+        assert np.array_equal(got40[32:], orc.forward(faces[32:], ffo.CONTRACT))
+
+
+def test_default_context_picks_the_tiling_from_the_call(built_lib, model_root, ffw4, oracle):
+    """fastface_create's default context (room for 256 faces) must give one face, eight faces and a full
+    batch each the tiling of that batch; results stay those of the oracle whichever plan runs."""
+    faces = synth.faces(70, seed=17)
+    want = oracle.forward(faces[:9], ffo.CONTRACT)
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=256) as e:
+        assert np.array_equal(e.embed(faces[0]), want[0])
+        assert np.array_equal(e.embed_batch(faces[:9]), want)
+        big = e.embed_batch(faces)
+        assert np.array_equal(big[:9], want)
+        for _ in range(3):                       # batch 1 again, now from its captured graph
+            assert np.array_equal(e.embed(faces[4]), want[4])
+
+
+def test_bounded_wait_runs_out_and_the_device_stays_usable(built_lib):
+    """The timeout path of the tensor-core kernels, exercised without faulting anything: the test hook
+    makes the TMA producer of ONE one-CTA launch leave out a K step, and shortens the issuer's wait for
+    that step to two million cycles (about a millisecond).  The wait must give up, every role must leave
+    its loop, tensor memory must be freed and the call must return 1000 + FFCU_ERR_TMA_TIMEOUT (1); the
+    same call, not armed, must then be bit-exact."""
+    lib = ff.load_library()
+    lib.ffcu_test_arm_timeout.restype = None
+    lib.ffcu_test_arm_timeout.argtypes = [C.c_int, C.c_longlong]
+    rng = np.random.default_rng(4242)
+    L = random_layer(rng, 1, 8, 64, 64, 3, 1, True, False)     # 64 pixels x 64 channels: one tile, one CTA
+    acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], 1, 1, L["slope"], None, None, ffo.CONTRACT)
+    lib.ffcu_test_arm_timeout(1, 2_000_000)
+    with pytest.raises(RuntimeError) as ei:
+        ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=1, pad=1, slope=L["slope"], impl="tc")
+    assert "rc=1001" in str(ei.value), str(ei.value)
+    for _ in range(2):                                          # the hook disarmed itself; the device is fine
+        acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=1, pad=1, slope=L["slope"], impl="tc")
+        assert np.array_equal(acc, acc_o) and np.array_equal(out, out_o)
+
+
 def test_embed_and_embed_batch_agree_with_oracle(engine, oracle):
     faces = synth.faces(8, seed=99)
     want = oracle.forward(faces, ffo.CONTRACT)
@@ -471,7 +605,7 @@ def test_stem_on_cuda_cores_agrees(built_lib, model_root, ffw4, oracle, monkeypa
 
 
 def test_network_with_the_large_batch_tiling(built_lib, model_root, ffw4, oracle, monkeypatch):
-    """A context for a small batch picks narrow column tiles; FF_TC_BN=wide pins the tiling large batches get
+    """A small batch picks narrow column tiles; FF_TC_BN=wide pins the column tiling large batches get
     (CTA-pair kernels at BN = 256 / 128, weight-stationary kernel at 64 -> 128), here checked end to end."""
     monkeypatch.setenv("FF_TC_BN", "wide")
     faces = synth.faces(5, seed=31)

@@ -120,3 +120,41 @@ def test_synth_model_is_the_177_op_sequence():
             h = ho
     macs += 25088 * 512
     assert abs(macs / 1e9 - 6.3093) < 1e-3
+
+
+def _rss_kb():
+    for line in open("/proc/self/status"):
+        if line.startswith("VmRSS:"):
+            return int(line.split()[1])
+    return 0
+
+
+def test_failing_create_does_not_leak(built_lib, tmp_path):
+    """fastface_create that fails late (whole model parsed and planned, then no usable device, or a model
+    refused by the planner) must hand back everything it allocated: a loop of failures leaves the
+    resident set where it was.  The 43.7 MB synthetic model makes a leak of the model or the plan visible
+    after a few rounds."""
+    from fastface_b200 import synth
+    root = str(tmp_path / "leak")
+    ffw4 = synth.materialize(root, 0)
+    lib = ff.load_library()
+    have_gpu = lib.ffcu_device_count() > 0
+    old = os.getcwd()
+    os.chdir(root)
+    try:
+        env_old = os.environ.get("FASTFACE_DEVICES")
+        os.environ["FASTFACE_DEVICES"] = "63"            # no such ordinal: fails after load + plan on any host
+        for _ in range(3):
+            assert lib.fastface_create(ffw4.encode()) is None
+        base = _rss_kb()
+        for _ in range(12):
+            assert lib.fastface_create(ffw4.encode()) is None
+        grown = _rss_kb() - base
+    finally:
+        os.chdir(old)
+        if env_old is None:
+            os.environ.pop("FASTFACE_DEVICES", None)
+        else:
+            os.environ["FASTFACE_DEVICES"] = env_old
+    # one leaked model would be >= 43 MB per round; allow a few MB of allocator noise
+    assert grown < 20 * 1024, f"resident set grew by {grown} kB over 12 failing creates (gpu present: {have_gpu})"
