@@ -18,7 +18,8 @@ from typing import Callable, List, Optional, Sequence, Tuple
 import numpy as np
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libfastface_b200.so")
+# $FASTFACE_B200_LIB names another build of the same library (for side-by-side comparisons of two builds)
+LIB_PATH = os.environ.get("FASTFACE_B200_LIB") or os.path.join(_PKG, "libfastface_b200.so")
 
 FACE_SHAPE = (112, 112, 3)
 FACE_NELEMS = 112 * 112 * 3

@@ -221,6 +221,19 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
 
 void ffcu_tc_free(TcPlan* p) { delete p; }
 
+// Epilogue warps per set for a launch whose CTAs each see about tiles_per_cta tiles of bn columns.
+// Narrow tiles at large batch: four (per-tile bookkeeping spread over twice the elements); otherwise
+// eight (half the tile latency).  $FF_TC_WPS64 / $FF_TC_WPS128 = 4 or 8 override.
+static int tc_epi_wps(int bn, int tiles_per_cta)
+{
+    static int w64 = -1, w128 = -1;
+    if (w64 < 0) { const char* e = getenv("FF_TC_WPS64"); w64 = (e && (atoi(e) == 4 || atoi(e) == 8)) ? atoi(e) : 0; }
+    if (w128 < 0) { const char* e = getenv("FF_TC_WPS128"); w128 = (e && (atoi(e) == 4 || atoi(e) == 8)) ? atoi(e) : 0; }
+    if (bn == 64) return w64 ? w64 : (tiles_per_cta >= 8 ? 4 : 8);
+    if (bn == 128) return w128 ? w128 : 8;
+    return 8;
+}
+
 int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, const int8_t* res,
                    int32_t* acc_out, void* out, int8_t* out_bn2, int* d_err, cudaStream_t s)
 {
@@ -237,6 +250,9 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
     else if (has_slope && !has_res && !has_bn2) epi = EPI_SLOPE;
     else if (has_res && has_bn2 && !has_slope) epi = EPI_RES_BN;
     else if (has_res && !has_bn2 && !has_slope) epi = EPI_RES;
+    // the specialised variants carry no accumulator dump, no out-of-range conversion check and no
+    // arithmetic fused BN: a launch that needs one of those takes the general variant
+    if (!p->out_f32 && (acc_out || !t.no_overflow || (has_bn2 && !p->lut_bytes))) epi = EPI_RUNTIME;
     if (p->ws) {
         TcParams prm = {};
         prm.t = t; prm.res = res; prm.acc_out = acc_out; prm.out = out; prm.err = d_err;
@@ -252,6 +268,7 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
         prm.dbg = dbg;
 #endif
         int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
+        prm.epi_wps = tc_epi_wps(p->BN, prm.total_tiles / grid);
         return tc_launch_ws(p->BN, mode, epi, grid, p->ws_smem_bytes, s, p->mapA_ws, p->mapB, prm);
     }
     int TW, TH, TB;
@@ -290,10 +307,12 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
         int npairs = pairs < max_pairs ? pairs : max_pairs;
         if (npairs > prm.tiles_n) npairs -= npairs % prm.tiles_n;      // a pair keeps one column tile (its BN table)
         const int pgrid = 2 * npairs;
+        prm.epi_wps = tc_epi_wps(p->BN, pairs / npairs);
         return tc_launch_pair(p->BN, mode, epi, p->out_f32, pgrid, p->pair_smem_bytes, s, g->mapA, p->mapB_half, prm);
     }
     int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
     if (grid > prm.tiles_n) grid -= grid % prm.tiles_n;                // a CTA keeps one column tile (its BN table)
+    prm.epi_wps = tc_epi_wps(p->BN, prm.total_tiles / grid);
     if (g_test_drop_stage >= 0) {                                      // armed for this one launch by the timeout test
         prm.drop_stage = g_test_drop_stage;
         if (g_test_full_wait > 0) prm.full_wait = g_test_full_wait;
@@ -365,5 +384,6 @@ int ffcu_stem_tc_launch(const StemTcPlan* p, int batch, int mode, const EpiTable
     { static int dbg = -1; if (dbg < 0) { const char* e = getenv("FF_TC_DBG"); dbg = e ? atoi(e) : 0; } prm.dbg = dbg; }
 #endif
     const int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
+    prm.epi_wps = tc_epi_wps(64, prm.total_tiles / grid);
     return tc_launch_k32(mode, epi, grid, p->smem_bytes, s, p->mapA, p->mapB, prm);
 }

@@ -29,6 +29,7 @@
 
 #include <stdio.h>
 #include <string.h>
+#include <type_traits>
 
 #define TC_TILE_M 128
 #define TC_MAX_COUT 512
@@ -334,6 +335,7 @@ struct TcParams {
     int lut_bytes;           // shared-memory bytes of the fused BN's table (BN * 256, or 0)
     int group;               // K blocks per pipeline stage (one barrier hand-shake per `group` blocks)
     int ntab;                // per-channel tables held in shared memory: 5, or 9 when the fused BN is computed arithmetically
+    int epi_wps;             // epilogue warps per set, 4 or 8 (16 / epi_wps sets take alternate tiles)
     long long full_wait;     // cycle limit of the MMA issuer's wait for a pipeline stage's data (TC_WAIT_CYCLES)
     int drop_stage;          // >= 0: the producer neither arms nor loads this K step of its first tile, so the
                              // issuer's wait for it must run out (ffcu_test_arm_timeout; -1 in every other launch)
@@ -355,27 +357,15 @@ enum { EPI_RUNTIME = 0, EPI_PLAIN = 1, EPI_SLOPE = 2, EPI_RES_BN = 3, EPI_RES = 
 
 #define TC_MAX_STAGES 8
 #define TC_NTAB 9          // most tables a kernel holds: w_scale, bias, slope, res_scale, inv_out | fused BN without a byte table: in_scale, scale, offset, inv_out (TcParams::ntab is the count in use)
-#ifndef TC_EPI_WARPS
-#define TC_EPI_WARPS 8     // epilogue warps per set: two per TMEM lane quarter, each takes half of the tile's columns
-#endif
-#define TC_EPI_COLGROUPS (TC_EPI_WARPS / 4)
 // Accumulator ring in TMEM: 512 columns hold 512 / BN tiles.  With short K loops (the
 // 64-channel layers) a tile's MMAs take less time than the hand-shake round trip to the
 // epilogue warps and back, so the issuer must be able to run several tiles ahead.
 #define TC_MAX_ACC 8
 #define TC_NACC(BN) (512 / (BN) > TC_MAX_ACC ? TC_MAX_ACC : 512 / (BN))
-// epilogue warps that actually have columns to process for a BN-wide tile (a chunk is 32 columns)
-#define TC_EPI_ACTIVE(BN) (4 * ((BN) / 16 < TC_EPI_COLGROUPS ? (BN) / 16 : TC_EPI_COLGROUPS))
-// Epilogue warp sets: set s takes the CTA's tiles s, s + SETS, ... (whole tiles, so a warp's work
-// per tile and the barrier counts stay as with one set, while twice the warps are in flight to
-// cover each other's fixed-latency and TMEM-load stalls).
-#ifndef TC_EPI_SETS
-#define TC_EPI_SETS 2
-#endif
-// Warp 0: TMA producer, warp 1: MMA issuer, warps 2 .. 2 + EPI_WARPS * SETS - 1: epilogue,
-// last warp: second MMA issuer (weight-stationary kernel only, idle elsewhere).
-#define TC_ISSUER2_WARP (2 + TC_EPI_WARPS * TC_EPI_SETS)
-#define TC_THREADS (32 * (3 + TC_EPI_WARPS * TC_EPI_SETS))
+// Warp 0: TMA producer, warp 1: MMA issuer, warps 2 .. 17: epilogue, warp 18: second MMA issuer
+// (weight-stationary and stem kernels, idle elsewhere).
+#define TC_ISSUER2_WARP 18
+#define TC_THREADS (32 * 19)
 
 struct TcShared {                 // lives after the stage ring and the tables
     uint64_t full[TC_MAX_STAGES];
@@ -389,6 +379,7 @@ struct TcShared {                 // lives after the stage ring and the tables
 
 __device__ __forceinline__ void tc_load_tables(float* tab, const TcParams& p)
 {
+#pragma unroll 1
     for (int i = threadIdx.x; i < p.Cout; i += TC_THREADS) {
         tab[0 * TC_MAX_COUT + i] = p.t.w_scale[i];
         tab[1 * TC_MAX_COUT + i] = p.t.bias[i];
@@ -411,6 +402,7 @@ __device__ __forceinline__ void tc_load_lut(uint8_t* lut, const TcParams& p, int
     if (!p.out2 || !p.lut_bytes) return;
     const int4* src = (const int4*)(p.t.bn_lut + (size_t)c0 * 256);
     int4* dst = (int4*)lut;
+#pragma unroll 1
     for (int i = threadIdx.x; i < bn * 16; i += TC_THREADS) dst[i] = __ldg(src + i);
 }
 
@@ -427,94 +419,125 @@ __device__ __forceinline__ void ld_global_32B(const void* ptr, int (&w)[8])
                  : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "l"(ptr));
 }
 
-// One 32-column chunk of one accumulator row: v[32] int32 -> outputs at element offset o
-// (= pixel * Cout + first channel cb).  Replaces fused_epilogue_int8 for those 32 values
-// (reference kernels/int8_epilogue.c:25-112), optionally followed by the next BN pass
-// (:253-318) as a second output.
-template <bool CONTRACT, bool OUT_F32, int EPI, int CW, bool CHECK>
-__device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const float* tab, const uint8_t* lutc,
-                                                  const int (&v)[CW], const int (&rw)[CW / 4], int cb, size_t o,
-                                                  bool rt_res, bool rt_slope, bool rt_bn2)
+// ---------------------------------------------------------------------------
+// Epilogue.  Replaces fused_epilogue_int8 (reference kernels/int8_epilogue.c:25-112), optionally
+// followed by the next BN pass (:253-318) as a second output.
+// ---------------------------------------------------------------------------
+
+// Compile-time loop: f(std::integral_constant<int, 0>{}) ... f(integral_constant<N-1>), so the index
+// can feed template arguments and immediate operands.
+template <int N>
+struct TcUnroll {
+    template <typename F>
+    __device__ __forceinline__ static void run(F&& f)
+    {
+        TcUnroll<N - 1>::run(f);
+        f(std::integral_constant<int, N - 1>{});
+    }
+};
+template <>
+struct TcUnroll<0> {
+    template <typename F>
+    __device__ __forceinline__ static void run(F&&) {}
+};
+
+// TMEM -> registers, 16 columns of this warp's 32 lanes.  The load is asynchronous: the
+// registers hold the data only after tmem_ld_wait, which names them as in/out operands so that
+// no use of them can be scheduled above it.
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, int (&v)[16])
 {
-    constexpr int NG = CW / 4;                            // groups of four channels
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(int (&v)[16])
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                   "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+                 :: "memory");
+}
+
+// One entry of the fused BN's byte table: entry (uint8_t)q of the row ROW rows past the one at
+// shared-memory address lut_base.  The table is 256-byte aligned, so a row's address with the
+// index byte dropped into its low byte IS the entry's address: one byte-permute instead of an
+// extract and an add.  K = which byte of the packed word w holds q.
+template <int K, int ROW>
+__device__ __forceinline__ uint32_t tc_lut_byte(uint32_t w, uint32_t lut_base)
+{
+    uint32_t addr, r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(addr) : "r"(w), "r"(lut_base), "n"(0x7650 | K));
+    asm("ld.shared.u8 %0, [%1 + %2];" : "=r"(r) : "r"(addr), "n"(ROW * 256));
+    return r;
+}
+
+// Sixteen columns of one accumulator row: v[16] int32 at channels cb .. cb + 15 -> four packed
+// int8 words (and four more for the fused BN's output).  CI = 0 / 1: first or second chunk of the
+// pair whose 32 table rows start at shared-memory address lut_pr.
+template <bool CONTRACT, int EPI, bool CHECK, int CI>
+__device__ __forceinline__ void tc_epilogue16(const TcParams& p, const float* tab, uint32_t lut_pr,
+                                              const int (&v)[16], const int* rw, int cb,
+                                              bool rt_res, bool rt_slope, bool rt_bn2, int (&ow)[4], int (&ow2)[4])
+{
     const bool has_res = (EPI == EPI_RUNTIME) ? rt_res : (EPI == EPI_RES_BN || EPI == EPI_RES);
     const bool has_slope = (EPI == EPI_RUNTIME) ? rt_slope : (EPI == EPI_SLOPE || EPI == EPI_SLOPE_BN);
     const bool has_bn2 = (EPI == EPI_RUNTIME) ? rt_bn2 : (EPI == EPI_RES_BN || EPI == EPI_SLOPE_BN);
-    if (p.acc_out) {                                      // dump-point mode: raw accumulators
-#pragma unroll
-        for (int g = 0; g < CW / 8; g++) {
-            const int w8[8] = {v[8 * g], v[8 * g + 1], v[8 * g + 2], v[8 * g + 3], v[8 * g + 4], v[8 * g + 5], v[8 * g + 6], v[8 * g + 7]};
-            st_global_32B(p.acc_out + o + 8 * g, w8);
-        }
-    }
-    if (OUT_F32) {
-        float4* dst = (float4*)((float*)p.out + o);
-#pragma unroll
-        for (int g = 0; g < NG; g++) {
-            const float4 ws = *(const float4*)&tab[0 * TC_MAX_COUT + cb + 4 * g];
-            const float4 bi = *(const float4*)&tab[1 * TC_MAX_COUT + cb + 4 * g];
-            float4 r;
-            r.x = ffcu_fc_fp<CONTRACT>(v[4 * g + 0], ws.x, bi.x);
-            r.y = ffcu_fc_fp<CONTRACT>(v[4 * g + 1], ws.y, bi.y);
-            r.z = ffcu_fc_fp<CONTRACT>(v[4 * g + 2], ws.z, bi.z);
-            r.w = ffcu_fc_fp<CONTRACT>(v[4 * g + 3], ws.w, bi.w);
-            dst[g] = r;
-        }
-        return;
-    }
-    int ow_[NG], ow2_[NG];
-#pragma unroll
-    for (int g = 0; g < NG; g++) {
+    TcUnroll<4>::run([&](auto gc) {
+        constexpr int g = decltype(gc)::value;
         const float4 ws = *(const float4*)&tab[0 * TC_MAX_COUT + cb + 4 * g];
         const float4 bi = *(const float4*)&tab[1 * TC_MAX_COUT + cb + 4 * g];
         const float4 sl = *(const float4*)&tab[2 * TC_MAX_COUT + cb + 4 * g];
         const float4 rs = *(const float4*)&tab[3 * TC_MAX_COUT + cb + 4 * g];
         const float4 iv = *(const float4*)&tab[4 * TC_MAX_COUT + cb + 4 * g];
-        const int r = rw[g];
-        int q0, q1, q2, q3;
-        float f0 = ffcu_conv_fp<CONTRACT>(v[4 * g + 0], ws.x, bi.x, has_res, (int)(int8_t)(r & 0xff), rs.x, has_slope, sl.x);
-        float f1 = ffcu_conv_fp<CONTRACT>(v[4 * g + 1], ws.y, bi.y, has_res, (int)(int8_t)((r >> 8) & 0xff), rs.y, has_slope, sl.y);
-        float f2 = ffcu_conv_fp<CONTRACT>(v[4 * g + 2], ws.z, bi.z, has_res, (int)(int8_t)((r >> 16) & 0xff), rs.z, has_slope, sl.z);
-        float f3 = ffcu_conv_fp<CONTRACT>(v[4 * g + 3], ws.w, bi.w, has_res, (int)(int8_t)((r >> 24) & 0xff), rs.w, has_slope, sl.w);
-        q0 = ffcu_requant_nosat<CHECK>(f0, iv.x); q1 = ffcu_requant_nosat<CHECK>(f1, iv.y);
-        q2 = ffcu_requant_nosat<CHECK>(f2, iv.z); q3 = ffcu_requant_nosat<CHECK>(f3, iv.w);
-        ow_[g] = ffcu_pack4(q0, q1, q2, q3);
-        if (has_bn2 && !p.lut_bytes) {
-            // BN of the four int8 results by arithmetic (the wide tiles: their byte tables would take 32 - 64 KB
-            // from the stage ring and their lookups compete with the tensor core for shared-memory bandwidth)
+        const int r = has_res ? rw[g] : 0;
+        const float f0 = ffcu_conv_fp<CONTRACT>(v[4 * g + 0], ws.x, bi.x, has_res, (int)(int8_t)(r & 0xff), rs.x, has_slope, sl.x);
+        const float f1 = ffcu_conv_fp<CONTRACT>(v[4 * g + 1], ws.y, bi.y, has_res, (int)(int8_t)((r >> 8) & 0xff), rs.y, has_slope, sl.y);
+        const float f2 = ffcu_conv_fp<CONTRACT>(v[4 * g + 2], ws.z, bi.z, has_res, (int)(int8_t)((r >> 16) & 0xff), rs.z, has_slope, sl.z);
+        const float f3 = ffcu_conv_fp<CONTRACT>(v[4 * g + 3], ws.w, bi.w, has_res, r >> 24, rs.w, has_slope, sl.w);
+        const int w = ffcu_pack4(ffcu_requant_nosat<CHECK>(f0, iv.x), ffcu_requant_nosat<CHECK>(f1, iv.y),
+                                 ffcu_requant_nosat<CHECK>(f2, iv.z), ffcu_requant_nosat<CHECK>(f3, iv.w));
+        ow[g] = w;
+        if (EPI == EPI_RUNTIME && has_bn2 && !p.lut_bytes) {
+            // BN of the four int8 results by arithmetic (no byte table in shared memory)
             const float4 b_in = *(const float4*)&tab[5 * TC_MAX_COUT + cb + 4 * g];
             const float4 b_sc = *(const float4*)&tab[6 * TC_MAX_COUT + cb + 4 * g];
             const float4 b_of = *(const float4*)&tab[7 * TC_MAX_COUT + cb + 4 * g];
             const float4 b_iv = *(const float4*)&tab[8 * TC_MAX_COUT + cb + 4 * g];
-            const int w = ow_[g];
             const int a0 = (int)(int8_t)(w & 0xff), a1 = (int)(int8_t)((w >> 8) & 0xff);
             const int a2 = (int)(int8_t)((w >> 16) & 0xff), a3 = w >> 24;
-            ow2_[g] = ffcu_pack4(ffcu_bn_q_nosat<CHECK>(a0, b_in.x, b_sc.x, b_of.x, b_iv.x),
-                                 ffcu_bn_q_nosat<CHECK>(a1, b_in.y, b_sc.y, b_of.y, b_iv.y),
-                                 ffcu_bn_q_nosat<CHECK>(a2, b_in.z, b_sc.z, b_of.z, b_iv.z),
-                                 ffcu_bn_q_nosat<CHECK>(a3, b_in.w, b_sc.w, b_of.w, b_iv.w));
+            ow2[g] = ffcu_pack4(ffcu_bn_q_nosat<CHECK>(a0, b_in.x, b_sc.x, b_of.x, b_iv.x),
+                                ffcu_bn_q_nosat<CHECK>(a1, b_in.y, b_sc.y, b_of.y, b_iv.y),
+                                ffcu_bn_q_nosat<CHECK>(a2, b_in.z, b_sc.z, b_of.z, b_iv.z),
+                                ffcu_bn_q_nosat<CHECK>(a3, b_in.w, b_sc.w, b_of.w, b_iv.w));
         } else if (has_bn2) {
             // BN of the four int8 results just packed: one table row per channel, indexed by the byte
-            const uint8_t* lc = lutc + (4 * g) * 256;
-            const unsigned w = (unsigned)ow_[g];
-            const unsigned b0 = lc[w & 0xffu], b1 = lc[256 + ((w >> 8) & 0xffu)];
-            const unsigned b2 = lc[512 + ((w >> 16) & 0xffu)], b3 = lc[768 + (w >> 24)];
-            ow2_[g] = (int)(b0 | (b1 << 8) | (b2 << 16) | (b3 << 24));
+            constexpr int R = CI * 16 + 4 * g;
+            const uint32_t b0 = tc_lut_byte<0, R + 0>((uint32_t)w, lut_pr), b1 = tc_lut_byte<1, R + 1>((uint32_t)w, lut_pr);
+            const uint32_t b2 = tc_lut_byte<2, R + 2>((uint32_t)w, lut_pr), b3 = tc_lut_byte<3, R + 3>((uint32_t)w, lut_pr);
+            ow2[g] = (int)__byte_perm(__byte_perm(b0, b1, 0x1140), __byte_perm(b2, b3, 0x1140), 0x5410);
         } else {
-            ow2_[g] = 0;
+            ow2[g] = 0;
         }
-    }
-    if (TC_DBG(p, 4) && ow_[0] != 0x12345679) return;      // timing experiment: no global stores
-    if (CW == 32) {
-        const int w0[8] = {ow_[0], ow_[1], ow_[2], ow_[3], ow_[NG - 4], ow_[NG - 3], ow_[NG - 2], ow_[NG - 1]};
-        st_global_32B((int8_t*)p.out + o, w0);
-        if (has_bn2) {
-            const int w1[8] = {ow2_[0], ow2_[1], ow2_[2], ow2_[3], ow2_[NG - 4], ow2_[NG - 3], ow2_[NG - 2], ow2_[NG - 1]};
-            st_global_32B(p.out2 + o, w1);
-        }
-    } else {
-        *(int4*)((int8_t*)p.out + o) = make_int4(ow_[0], ow_[1], ow_[2], ow_[3]);
-        if (has_bn2) *(int4*)(p.out2 + o) = make_int4(ow2_[0], ow2_[1], ow2_[2], ow2_[3]);
+    });
+}
+
+// FC variant: sixteen f32 outputs, out = fmaf((float)dot, w_scale, bias) (or the unfused order).
+template <bool CONTRACT>
+__device__ __forceinline__ void tc_fc16(const TcParams& p, const float* tab, const int (&v)[16], int cb, size_t o)
+{
+    float4* dst = (float4*)((float*)p.out + o);
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+        const float4 ws = *(const float4*)&tab[0 * TC_MAX_COUT + cb + 4 * g];
+        const float4 bi = *(const float4*)&tab[1 * TC_MAX_COUT + cb + 4 * g];
+        float4 r;
+        r.x = ffcu_fc_fp<CONTRACT>(v[4 * g + 0], ws.x, bi.x);
+        r.y = ffcu_fc_fp<CONTRACT>(v[4 * g + 1], ws.y, bi.y);
+        r.z = ffcu_fc_fp<CONTRACT>(v[4 * g + 2], ws.z, bi.z);
+        r.w = ffcu_fc_fp<CONTRACT>(v[4 * g + 3], ws.w, bi.w);
+        dst[g] = r;
     }
 }
 
@@ -582,9 +605,21 @@ __device__ __forceinline__ void walk_next(TileWalk& w, const TcParams& p)
     w.tb += w.db + c;
 }
 
-// Epilogue role shared by all kernels.  Warps 2..17: warp w reads TMEM lanes
-// [32*(w%4), +32) (the hardware's per-warp lane window), the column group ((w-2)%8)/4,
-// for the tiles of its set (w-2)/8.
+// Epilogue warps: sixteen (warps 2..17), organised as 16 / wps sets of wps warps (TcParams::epi_wps,
+// 4 or 8).  Set s takes the CTA's tiles s, s + sets, ...; within a set, warp e covers the TMEM lane
+// quarter its index gives it (hardware: warp w reads lanes [32*(w%4), +32)) and column group e / 4 of
+// wps / 4.  With four warps per set each warp walks all columns of its 32 rows, so the per-tile
+// bookkeeping (tile walk, addresses, two barrier operations) is spread over twice the elements: the
+// choice for narrow tiles at large batch.  Eight warps per set halve a tile's latency: the choice
+// when a CTA sees only a few tiles.  The sets never exceed the accumulator ring.
+#define TC_EPI_TOTAL_WARPS 16
+
+// Epilogue role shared by all kernels.  A warp walks its column range in pairs of 16-column chunks:
+// the tcgen05.ld of the next chunk is in flight while the current one is computed, each pair ends in
+// 32-byte global stores, the residual's bytes are fetched one pair ahead.  The specialised variants
+// (EPI != EPI_RUNTIME) assume what their launcher guarantees: the layer has the no-overflow proof, a
+// fused BN comes with its byte table, no accumulator dump is asked for; everything else runs the
+// EPI_RUNTIME variant.
 template <int BN, bool CONTRACT, bool OUT_F32, int EPI>
 __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float* tab, const uint8_t* lut, TcShared* sh,
                                                  uint32_t tmem_base, volatile int* abort_flag, int warp, int lane,
@@ -592,15 +627,13 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
                                                  uint32_t remote_acc_empty /* 0: local barrier */)
 {
     if (warp >= TC_ISSUER2_WARP) return;                  // not an epilogue warp
+    const int wps = p.epi_wps;
+    const int sets = TC_EPI_TOTAL_WARPS / wps;
+    const int cols = BN / (wps >> 2);                     // columns this warp covers
+    const int n_pairs = cols >> 5;                        // pairs of 16-column chunks
     const int q = warp & 3;
-    const int set = (warp - 2) / TC_EPI_WARPS;            // which of the CTA's tiles this warp takes
-    const int cg = ((warp - 2) % TC_EPI_WARPS) >> 2;      // column group of this warp
-    // chunk width: 32 columns, or 16 for the narrow (BN = 64) tiles so all column groups have work
-    constexpr int CW = (BN / 32 >= TC_EPI_COLGROUPS) ? 32 : 16;
-    constexpr int CHUNKS = BN / CW;
-    constexpr int GROUPS = CHUNKS < TC_EPI_COLGROUPS ? CHUNKS : TC_EPI_COLGROUPS;
-    constexpr int PER = CHUNKS / GROUPS;
-    if (cg >= GROUPS) return;
+    const int set = (warp - 2) / wps;                     // which of the CTA's tiles this warp takes
+    const int cg = ((warp - 2) % wps) >> 2;               // column group of this warp
     const int row = q * 32 + lane;
     const int iw = row % p.TW;
     const int ih = (row / p.TW) % p.TH;
@@ -608,67 +641,85 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
     const bool has_res = (EPI == EPI_RUNTIME) ? ((p.res != nullptr) && (p.t.res_scale != nullptr))
                                               : (EPI == EPI_RES_BN || EPI == EPI_RES);
     const bool has_slope = p.t.slope != nullptr;
-    const bool has_bn2 = p.out2 != nullptr;
+    const bool has_bn2 = (EPI == EPI_RUNTIME) ? (p.out2 != nullptr) : (EPI == EPI_RES_BN || EPI == EPI_SLOPE_BN);
+    const bool check = (EPI == EPI_RUNTIME) && !p.t.no_overflow;
+    const bool dump = (EPI == EPI_RUNTIME) && p.acc_out != nullptr;
     int local = set;
     bool ok = true;
     const int tn = first % p.tiles_n;
+    const int c0 = tn * BN + cg * cols;                   // first channel of this warp's range
+    const uint32_t lut0 = smem_u32(lut) + (uint32_t)(cg * cols) * 256u;
     first += set * step;
-    step *= TC_EPI_SETS;
+    step *= sets;
     TileWalk wk;
     walk_init(wk, p, (first / p.tiles_n) * m_mul + m_off, (step / p.tiles_n) * m_mul);
-    for (int tile = first; tile < total && ok; tile += step, local += TC_EPI_SETS, walk_next(wk, p)) {
-        const int tw = wk.tw, th = wk.th, tb = wk.tb;
-        const int ow = tw * p.TW + iw, oh = th * p.TH + ih, b = tb * p.TB + ib;
+    for (int tile = first; tile < total && ok; tile += step, local += sets, walk_next(wk, p)) {
+        const int ow = wk.tw * p.TW + iw, oh = wk.th * p.TH + ih, b = wk.tb * p.TB + ib;
         const bool valid = (ow < p.Wo) && (oh < p.Ho) && (b < p.batch);
-        const size_t pix = ((size_t)b * p.Ho + oh) * p.Wo + ow;
-        const int n0 = tn * BN;
+        const size_t o0 = (((size_t)b * p.Ho + oh) * p.Wo + ow) * p.Cout + c0;
         const int a = local % TC_NACC(BN);
         const uint32_t aphase = (uint32_t)(local / TC_NACC(BN)) & 1;
-        // the residual operand does not depend on the accumulator: fetch the first chunk's
-        // bytes before waiting for the MMAs, the next chunk's while computing this one
-        int rw[CW / 4];
+        // the residual operand does not depend on the accumulator: the first 32 channels' bytes are
+        // fetched before waiting for the MMAs, the next 32 while these are computed
+        int rw[8], rn[8];
 #pragma unroll
-        for (int g = 0; g < CW / 4; g++) rw[g] = 0;
-        const size_t o0 = pix * p.Cout + n0 + cg * PER * CW;
-        if (has_res && valid && !TC_DBG(p, 4)) {
-            if (CW == 32) { int t8[8]; ld_global_32B(p.res + o0, t8); for (int g = 0; g < CW / 4; g++) rw[g] = t8[g]; }
-            else { const int4 t4 = *(const int4*)(p.res + o0); rw[0] = t4.x; rw[1] = t4.y; rw[2] = t4.z; rw[3] = t4.w; }
-        }
+        for (int g = 0; g < 8; g++) { rw[g] = 0; rn[g] = 0; }
+        if (has_res && valid && !TC_DBG(p, 4)) ld_global_32B(p.res + o0, rw);
         ok = mbar_wait(smem_u32(&sh->acc_full[a]), aphase, abort_flag, p.err, FFCU_ERR_EPI_TIMEOUT);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t taddr = tmem_base + (uint32_t)(a * BN) + ((uint32_t)(q * 32) << 16);
+        const uint32_t taddr = tmem_base + (uint32_t)(a * BN + cg * cols) + ((uint32_t)(q * 32) << 16);
+        int v0[16], v1[16];
+        tmem_ld16_issue(taddr, v0);
+        tmem_ld_wait(v0);
 #pragma unroll 1
-        for (int jj = 0; jj < PER; jj++) {
-            const int j = cg * PER + jj;
-            int v[CW];
-            tmem_ld(taddr + (uint32_t)(j * CW), v);
-            if (!valid) continue;
-            if (TC_DBG(p, 8)) {                              // timing experiment: no arithmetic
-                int x = 0;
-#pragma unroll
-                for (int i = 0; i < CW; i++) x ^= v[i];
-                if (x == 0x12345679) *(int*)((int8_t*)p.out + o0) = x;
-                continue;
+        for (int pr = 0; pr < n_pairs; pr++) {
+            const bool more = pr + 1 < n_pairs;
+            const int cb = c0 + pr * 32;
+            const size_t o = o0 + pr * 32;
+            const uint32_t lut_pr = lut0 + (uint32_t)pr * (32u * 256u);
+            tmem_ld16_issue(taddr + (uint32_t)(pr * 32 + 16), v1);            // lands while v0 is computed
+            if (has_res && more && valid && !TC_DBG(p, 4)) ld_global_32B(p.res + o + 32, rn);
+            int w0[4], w0b[4], w1[4], w1b[4];
+            if (valid && !TC_DBG(p, 8)) {
+                if (dump) {
+                    const int d0[8] = {v0[0], v0[1], v0[2], v0[3], v0[4], v0[5], v0[6], v0[7]};
+                    const int d1[8] = {v0[8], v0[9], v0[10], v0[11], v0[12], v0[13], v0[14], v0[15]};
+                    st_global_32B(p.acc_out + o, d0);
+                    st_global_32B(p.acc_out + o + 8, d1);
+                }
+                if (OUT_F32) tc_fc16<CONTRACT>(p, tab, v0, cb, o);
+                else if (check) tc_epilogue16<CONTRACT, EPI, true, 0>(p, tab, lut_pr, v0, rw, cb, has_res, has_slope, has_bn2, w0, w0b);
+                else            tc_epilogue16<CONTRACT, EPI, false, 0>(p, tab, lut_pr, v0, rw, cb, has_res, has_slope, has_bn2, w0, w0b);
             }
-            int rn[CW / 4];
-#pragma unroll
-            for (int g = 0; g < CW / 4; g++) rn[g] = 0;
-            if (has_res && jj + 1 < PER && !TC_DBG(p, 4)) {
-                if (CW == 32) { int t8[8]; ld_global_32B(p.res + o0 + (size_t)(jj + 1) * CW, t8); for (int g = 0; g < CW / 4; g++) rn[g] = t8[g]; }
-                else { const int4 t4 = *(const int4*)(p.res + o0 + (size_t)(jj + 1) * CW); rn[0] = t4.x; rn[1] = t4.y; rn[2] = t4.z; rn[3] = t4.w; }
+            tmem_ld_wait(v1);
+            if (more) tmem_ld16_issue(taddr + (uint32_t)(pr * 32 + 32), v0);  // lands while v1 is computed
+            if (valid && !TC_DBG(p, 8)) {
+                if (dump) {
+                    const int d0[8] = {v1[0], v1[1], v1[2], v1[3], v1[4], v1[5], v1[6], v1[7]};
+                    const int d1[8] = {v1[8], v1[9], v1[10], v1[11], v1[12], v1[13], v1[14], v1[15]};
+                    st_global_32B(p.acc_out + o + 16, d0);
+                    st_global_32B(p.acc_out + o + 24, d1);
+                }
+                if (OUT_F32) tc_fc16<CONTRACT>(p, tab, v1, cb + 16, o + 16);
+                else {
+                    if (check) tc_epilogue16<CONTRACT, EPI, true, 1>(p, tab, lut_pr, v1, rw + 4, cb + 16, has_res, has_slope, has_bn2, w1, w1b);
+                    else       tc_epilogue16<CONTRACT, EPI, false, 1>(p, tab, lut_pr, v1, rw + 4, cb + 16, has_res, has_slope, has_bn2, w1, w1b);
+                    if (!TC_DBG(p, 4)) {
+                        const int w8[8] = {w0[0], w0[1], w0[2], w0[3], w1[0], w1[1], w1[2], w1[3]};
+                        st_global_32B((int8_t*)p.out + o, w8);
+                        if (has_bn2) {
+                            const int w8b[8] = {w0b[0], w0b[1], w0b[2], w0b[3], w1b[0], w1b[1], w1b[2], w1b[3]};
+                            st_global_32B(p.out2 + o, w8b);
+                        }
+                    }
+                }
             }
-            const int cb = n0 + j * CW;
-            if (p.t.no_overflow)
-                tc_epilogue_chunk<CONTRACT, OUT_F32, EPI, CW, false>(p, tab, lut + (size_t)(j * CW) * 256, v, rw, cb, pix * p.Cout + cb,
-                                                                     has_res, has_slope, has_bn2);
-            else
-                tc_epilogue_chunk<CONTRACT, OUT_F32, EPI, CW, true>(p, tab, lut + (size_t)(j * CW) * 256, v, rw, cb, pix * p.Cout + cb,
-                                                                    has_res, has_slope, has_bn2);
 #pragma unroll
-            for (int g = 0; g < CW / 4; g++) rw[g] = rn[g];
+            for (int g = 0; g < 8; g++) rw[g] = rn[g];
+            if (more) tmem_ld_wait(v0);
         }
-        // this warp's TMEM reads are complete (tcgen05.wait::ld inside tmem_ld)
+        // this warp's TMEM reads are complete (the last tcgen05.wait::ld has returned)
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
@@ -705,6 +756,7 @@ __device__ __forceinline__ void tc_teardown(volatile int* abort_flag, uint32_t t
     if (*abort_flag && threadIdx.x == 0) {
         // a wait ran out: give bulk copies still in flight time to land before the
         // shared memory is handed back (bounded: about 1 ms)
+#pragma unroll 1
         for (int i = 0; i < 1000; i++) __nanosleep(1000);
     }
     __syncthreads();

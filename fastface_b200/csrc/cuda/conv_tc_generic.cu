@@ -29,7 +29,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 
     tc_load_tables(tab, p);
     tc_load_lut(lut, p, (int)(blockIdx.x % p.tiles_n) * BN, BN);
-    tc_setup(sh, p.stages, TMEM_COLS, warp, TC_EPI_ACTIVE(BN));
+    tc_setup(sh, p.stages, TMEM_COLS, warp, p.epi_wps);
     tc_pdl_sync();
     const uint32_t tmem_base = sh->tmem_base;
     volatile int* abort_flag = &sh->abort_flag;

@@ -36,7 +36,7 @@ conv_k32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
 
     tc_load_tables(tab, p);
     tc_load_lut(lut, p, 0, BN);
-    tc_setup(sh, p.stages, TMEM_COLS, warp, TC_EPI_ACTIVE(BN));
+    tc_setup(sh, p.stages, TMEM_COLS, warp, p.epi_wps);
     tc_pdl_sync();
     const uint32_t tmem_base = sh->tmem_base;
     volatile int* abort_flag = &sh->abort_flag;

@@ -46,7 +46,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     tc_load_lut(lut, p, (int)(pair_id % p.tiles_n) * BN, BN);
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; s++) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), 1); }
-        for (int a = 0; a < TC_MAX_ACC; a++) { mbar_init(smem_u32(&sh->acc_full[a]), 1); mbar_init(smem_u32(&sh->acc_empty[a]), 2 * TC_EPI_ACTIVE(BN)); }
+        for (int a = 0; a < TC_MAX_ACC; a++) { mbar_init(smem_u32(&sh->acc_full[a]), 1); mbar_init(smem_u32(&sh->acc_empty[a]), 2 * p.epi_wps); }
         mbar_init(smem_u32(&sh->w_full), 1);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -169,6 +169,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     if (*abort_flag && threadIdx.x == 0) {
+#pragma unroll 1
         for (int i = 0; i < 1000; i++) __nanosleep(1000);
     }
     __syncthreads();

@@ -123,6 +123,10 @@ def test_synth_model_is_the_177_op_sequence():
 
 
 def _rss_kb():
+    try:
+        C.CDLL("libc.so.6").malloc_trim(0)      # hand free heap pages back first: what stays is what is still allocated
+    except OSError:
+        pass
     for line in open("/proc/self/status"):
         if line.startswith("VmRSS:"):
             return int(line.split()[1])
@@ -156,5 +160,5 @@ def test_failing_create_does_not_leak(built_lib, tmp_path):
             os.environ.pop("FASTFACE_DEVICES", None)
         else:
             os.environ["FASTFACE_DEVICES"] = env_old
-    # one leaked model would be >= 43 MB per round; allow a few MB of allocator noise
-    assert grown < 20 * 1024, f"resident set grew by {grown} kB over 12 failing creates (gpu present: {have_gpu})"
+    # one leaked model would be >= 43 MB per round (516 MB over the loop); allow allocator noise
+    assert grown < 40 * 1024, f"resident set grew by {grown} kB over 12 failing creates (gpu present: {have_gpu})"
