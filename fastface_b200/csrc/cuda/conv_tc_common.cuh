@@ -79,8 +79,8 @@ __device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity);
 // but the polls.
 #define TC_WAIT_CYCLES 4000000000ll
 template <bool CLUSTER>
-__device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code,
-                                               long long limit)
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code,
+                                            long long limit)
 {
 #pragma unroll 1
     for (int i = 0; i < 256; i++)
@@ -98,6 +98,16 @@ __device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, vo
             }
         }
     }
+}
+// The first polls are inline (a wait that is already satisfied, or nearly, costs a few instructions);
+// the long form with the clock and the abort flag is one shared function, not a copy per wait site.
+template <bool CLUSTER>
+__device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code,
+                                               long long limit)
+{
+    if (CLUSTER ? mbar_try_cluster(bar, parity) : mbar_try(bar, parity)) return true;
+    if (CLUSTER ? mbar_try_cluster(bar, parity) : mbar_try(bar, parity)) return true;
+    return mbar_wait_slow<CLUSTER>(bar, parity, abort_flag, err, code, limit);
 }
 __device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity);
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code,

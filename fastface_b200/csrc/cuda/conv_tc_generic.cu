@@ -65,6 +65,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 // this lane's first block: kb = g
                 int c0 = g * KC, kw = 0, kh = 0;
                 while (c0 >= p.Cp) { c0 -= p.Cp; if (++kw == p.Kw) { kw = 0; kh++; } }
+#pragma unroll 1
                 for (int it = 0; it < n_steps; it++) {
                     ok = mbar_wait(empty0 + stage * 8, phase ^ 1, abort_flag, p.err, FFCU_ERR_EMPTY_TIMEOUT);
                     if (!ok) break;
@@ -105,6 +106,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
+#pragma unroll 1
                 for (int it = 0; it < n_steps; it++) {
                     if (!ready) {
                         ok = mbar_wait(full0 + stage * 8, phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT, p.full_wait);
@@ -118,6 +120,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     {
                         uint32_t soff = (uint32_t)((stage * stage_bytes) >> 4);
                         if (!TC_DBG(p, 2))
+#pragma unroll 1
                         for (int g = 0; g < G; g++, soff += (uint32_t)(SUB_BYTES >> 4)) {
 #pragma unroll
                             for (int k = 0; k < KC / 32; k++)

@@ -507,6 +507,20 @@ def test_network_other_model_seeds(built_lib, tmp_path_factory, seed):
         assert np.array_equal(got40[32:], orc.forward(faces[32:], ffo.CONTRACT))
 
 
+def test_model_from_the_weight_producer(built_lib, tmp_path_factory):
+    """A model written by fastface_b200.producer (fp32 network -> calibration -> folds -> FFW4 + OPSC2 + OPSC)
+    runs through the CUDA path with the oracle's bytes: real calibrated scales (not the synthetic
+    generator's) reach every epilogue and table."""
+    from fastface_b200 import producer as P
+    root = str(tmp_path_factory.mktemp("produced_gpu"))
+    path = P.write_model(root, P.synth_float_model(seed=11), synth.faces(2, seed=910))
+    orc = ffo.Oracle(path, os.path.join(root, "models", "op_scales.bin"), os.path.join(root, "models", "op_scales_v2.bin"))
+    faces = synth.faces(6, seed=911)
+    with ff.FastFace(path, cwd=root, max_batch=6) as e:
+        got = e.embed_batch(faces)
+    assert np.array_equal(got, orc.forward(faces, ffo.CONTRACT))
+
+
 def test_default_context_picks_the_tiling_from_the_call(built_lib, model_root, ffw4, oracle):
     """fastface_create's default context (room for 256 faces) must give one face, eight faces and a full
     batch each the tiling of that batch; results stay those of the oracle whichever plan runs."""
