@@ -40,6 +40,9 @@ struct TcPlan {
     bool pair;               // CTA-pair kernel (cta_group::2) for >= 128 input channels
     CUtensorMap mapB_half;   // box {128, BN/2}
     int pair_stages, pair_smem_bytes;
+    bool wsp;                // flat-pitch weight-stationary pair kernel (128 -> 128 3x3 stride-1 layers, 28x28 maps)
+    CUtensorMap mapA_wsp;    // box {128, W + 2, 8, 1}
+    int wsp_P, wsp_tiles_per_image, wsp_stages, wsp_smem_bytes;
     bool ws;                 // weight-stationary kernel (64-channel 3x3 stride-1 layers)
     CUtensorMap mapA_ws;     // box {64, 8, 18, 1}
     int ws_stages, ws_smem_bytes;
@@ -196,6 +199,38 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
             if (st >= 2) { p->pair = true; p->pair_stages = st; p->pair_smem_bytes = st * p->pair_group * sb + fixed; }
         }
     }
+    // flat-pitch weight-stationary pair variant: all nine taps of a 128 -> 128 layer resident, one box per tile
+    p->wsp = false;
+    const char* wsp_env = getenv("FF_TC_WSP");
+    if (p->pair && L.kind == FFCU_CONV && Cp == 128 && L.Cout == 128 && p->BN == 128 && L.Kh == 3 && L.Kw == 3 &&
+        L.stride == 1 && L.pad == 1 && !(wsp_env && wsp_env[0] == '0')) {
+        const int P = L.W + 2;
+        const int rows_needed = (TC_TILE_M - 1 + P - 1) / P + 1 + 2;       // rows a tile's lines span, plus one above and below
+        if (rows_needed <= WSP_BOX_ROWS && P <= 256) {
+            cuuint64_t adims[4] = {128, (cuuint64_t)L.W, (cuuint64_t)L.H, (cuuint64_t)max_batch};
+            cuuint64_t astr[3] = {128, (cuuint64_t)128 * L.W, (cuuint64_t)128 * L.W * L.H};
+            cuuint32_t abox[4] = {128, (cuuint32_t)P, WSP_BOX_ROWS, 1};
+            cuuint32_t aes[4] = {1, 1, 1, 1};
+            r = enc(&p->mapA_wsp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d_in, adims, astr, abox, aes,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r == CUDA_SUCCESS) {
+                const int a_stride = (WSP_GUARD_BYTES + P * WSP_BOX_ROWS * 128 + 1023) & ~1023;
+                const int wbytes = 9 * (p->BN / 2) * 128;
+                int st = (232448 - wbytes - fixed) / a_stride;
+                if (st > 4) st = 4;
+                // Two issuer warps take alternate tiles and find their ring slot from the tile's index: with an
+                // odd ring a warp's "this slot's data has landed" test would look at a slot the OTHER warp's
+                // previous tile may still be waiting on, and a parity test cannot tell "one fill behind" from
+                // "this fill done".  An even ring keeps every slot a warp tests behind one of its own tiles.
+                st &= ~1;
+                if (st >= 2) {
+                    p->wsp = true; p->wsp_P = P; p->wsp_tiles_per_image = (L.H * P + TC_TILE_M - 1) / TC_TILE_M;
+                    p->wsp_stages = st; p->wsp_smem_bytes = wbytes + st * a_stride + fixed;
+                }
+            }
+        }
+    }
     // weight-stationary variant
     p->ws = false;
     const char* ws_env = getenv("FF_TC_WS");
@@ -213,6 +248,7 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
             const int wbytes = 9 * p->BN * 64;
             int st = (232448 - wbytes - fixed) / WS_A_BYTES;
             if (st > TC_MAX_STAGES) st = TC_MAX_STAGES;
+            st &= ~1;                                     // two issuer warps on alternate tiles: the ring must be even (see above)
             if (st >= 2) { p->ws = true; p->ws_stages = st; p->ws_smem_bytes = wbytes + st * WS_A_BYTES + fixed; }
         }
     }
@@ -270,6 +306,27 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
         int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
         prm.epi_wps = tc_epi_wps(p->BN, prm.total_tiles / grid);
         return tc_launch_ws(p->BN, mode, epi, grid, p->ws_smem_bytes, s, p->mapA_ws, p->mapB, prm);
+    }
+    if (p->wsp) {
+        TcParams prm = {};
+        prm.t = t; prm.res = res; prm.acc_out = acc_out; prm.out = out; prm.err = d_err;
+        prm.out2 = (out_bn2 && t.bn_in) ? out_bn2 : nullptr;
+        prm.batch = batch; prm.Ho = d.Ho; prm.Wo = d.Wo; prm.Cout = d.Cout;
+        prm.taps = 9; prm.Kw = 3; prm.Cp = 128; prm.cin_blocks = 1; prm.stride = 1; prm.pad = 1;
+        prm.TW = TC_TILE_M; prm.TH = 1; prm.TB = 1;        // not used for the mapping: flat_P is set
+        prm.flat_P = p->wsp_P;
+        const int images = (batch + 1) & ~1;               // a pair takes one tile of two consecutive images
+        prm.tiles_w = images; prm.tiles_h = p->wsp_tiles_per_image; prm.tiles_b = 1; prm.tiles_n = 1;
+        prm.total_tiles = (images / 2) * p->wsp_tiles_per_image;
+        prm.stages = p->wsp_stages; prm.group = 1; prm.lut_bytes = p->lut_bytes; prm.ntab = p->ntab;
+        prm.full_wait = TC_WAIT_CYCLES; prm.drop_stage = -1;
+#ifdef FF_TC_TIMING
+        prm.dbg = dbg;
+#endif
+        const int max_pairs = p->n_sm / 2;
+        const int npairs = prm.total_tiles < max_pairs ? prm.total_tiles : max_pairs;
+        prm.epi_wps = tc_epi_wps(p->BN, prm.total_tiles / npairs);
+        return tc_launch_wsp(mode, epi, 2 * npairs, p->wsp_smem_bytes, s, p->mapA_wsp, p->mapB_half, prm);
     }
     int TW, TH, TB;
     pick_geometry(d.Wo, d.Ho, batch, &TW, &TH, &TB);

@@ -345,6 +345,9 @@ struct TcParams {
     int lut_bytes;           // shared-memory bytes of the fused BN's table (BN * 256, or 0)
     int group;               // K blocks per pipeline stage (one barrier hand-shake per `group` blocks)
     int ntab;                // per-channel tables held in shared memory: 5, or 9 when the fused BN is computed arithmetically
+    int flat_P;              // > 0: flat-pitch tiles (weight-stationary pair kernel): a tile is 128 consecutive lines of
+                             // an image laid out with a row pitch of flat_P = W + 2 lines (one zero column either side);
+                             // the tile walk's digits are then (image, tile-in-image) instead of (w, h, batch) tiles
     int epi_wps;             // epilogue warps per set, 4 or 8 (16 / epi_wps sets take alternate tiles)
     long long full_wait;     // cycle limit of the MMA issuer's wait for a pipeline stage's data (TC_WAIT_CYCLES)
     int drop_stage;          // >= 0: the producer neither arms nor loads this K step of its first tile, so the
@@ -664,8 +667,20 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
     TileWalk wk;
     walk_init(wk, p, (first / p.tiles_n) * m_mul + m_off, (step / p.tiles_n) * m_mul);
     for (int tile = first; tile < total && ok; tile += step, local += sets, walk_next(wk, p)) {
-        const int ow = wk.tw * p.TW + iw, oh = wk.th * p.TH + ih, b = wk.tb * p.TB + ib;
-        const bool valid = (ow < p.Wo) && (oh < p.Ho) && (b < p.batch);
+        int ow, oh, b;
+        bool valid;
+        if (p.flat_P) {
+            // line l = tile * 128 + row of the image's padded-pitch layout: row l / P, column l % P - 1;
+            // the pitch's two extra columns and the lines past the last row are positions without an output
+            const int l = wk.th * TC_TILE_M + row;
+            oh = l / p.flat_P;
+            ow = l - oh * p.flat_P - 1;
+            b = wk.tw;
+            valid = (ow >= 0) && (ow < p.Wo) && (oh < p.Ho) && (b < p.batch);
+        } else {
+            ow = wk.tw * p.TW + iw; oh = wk.th * p.TH + ih; b = wk.tb * p.TB + ib;
+            valid = (ow < p.Wo) && (oh < p.Ho) && (b < p.batch);
+        }
         const size_t o0 = (((size_t)b * p.Ho + oh) * p.Wo + ow) * p.Cout + c0;
         const int a = local % TC_NACC(BN);
         const uint32_t aphase = (uint32_t)(local / TC_NACC(BN)) & 1;
@@ -787,6 +802,12 @@ int tc_launch_ws(int bn, int mode, int epi, int grid, int smem, cudaStream_t s,
                  const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
 int tc_launch_pair(int bn, int mode, int epi, bool f32, int grid, int smem, cudaStream_t s,
                    const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
+int tc_launch_wsp(int mode, int epi, int grid, int smem, cudaStream_t s,
+                  const CUtensorMap& mapA, const CUtensorMap& mapB_half, const TcParams& prm);
+
+// Flat-pitch weight-stationary pair kernel: activation buffer = guard + box of WSP_BOX_ROWS image rows
+#define WSP_GUARD_BYTES 1024
+#define WSP_BOX_ROWS 8
 
 #define WS_TW 8
 #define WS_TH 16

@@ -136,6 +136,7 @@ BIG_LAYER_CASES = [
     ("big_s1_256_256_14_add_B33", 33, 14, 256, 256, 3, 1, False, True),
     ("big_s1_128_128_28_add_B16", 16, 28, 128, 128, 3, 1, False, True),
     ("big_s1_128_128_28_prelu_B200", 200, 28, 128, 128, 3, 1, True, False),
+    ("big_s1_128_128_28_add_B37", 37, 28, 128, 128, 3, 1, False, True),
     ("big_s1_128_256_28_prelu_B40", 40, 28, 128, 256, 3, 1, True, False),
     ("big_s1_64_64_56_prelu_B100", 100, 56, 64, 64, 3, 1, True, False),
     ("big_s1_64_64_56_add_B37", 37, 56, 64, 64, 3, 1, False, True),
@@ -339,6 +340,23 @@ def test_layer_microbench_reports_both_kernels(built_lib):
     line = layer_bench.run("conv56", 8, 5, False, True)
     assert line["winograd_f23"]["equals_4x_direct"] is True
     assert line["ms_per_launch"] > 0 and line["winograd_f23"]["ms_per_launch"] > 0
+
+
+@pytest.mark.parametrize("case", [c for c in BIG_LAYER_CASES if (c[2], c[3], c[4], c[6]) == (28, 128, 128, 1)] + [LAYER_CASES[4]],
+                         ids=lambda c: c[0])
+def test_128_channel_layers_on_the_per_tap_pair_kernel(built_lib, case, monkeypatch):
+    """FF_TC_WSP=0 routes the 128 -> 128 3x3 layers through the per-tap CTA-pair kernel instead of the
+    flat-pitch weight-stationary one; both must give the oracle's bytes."""
+    monkeypatch.setenv("FF_TC_WSP", "0")
+    monkeypatch.setenv("FF_TC_BN", "wide")
+    name, B, H, Cin, Cout, k, stride, sl, rs = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()) + 3)
+    L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
+    acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
+                            slope=L["slope"], res=L["res"], res_scale=L["rs"], impl="tc")
+    acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
+                               L["res"], L["rs"], ffo.CONTRACT)
+    assert np.array_equal(acc, acc_o) and np.array_equal(out, out_o)
 
 
 def test_stem_conv_simt_vs_oracle(built_lib):
