@@ -47,8 +47,8 @@ METRIC = "faces/sec (IR-ResNet50 INT8, 112x112)"
 # constant, valid while that kernel's memory behaviour is unchanged (algorithmic bytes: 206.1 MB)
 DOMINANT_TRAFFIC_BYTES = 170.3e6
 DOMINANT_TRAFFIC_SOURCE = "constant from profiles/conv_tc_kernels_single_layer_cases_ncu_full.md (ncu, not measured in this run)"
-# stem: 150 528 B fp32 face in + 2 x 802 816 B int8 out + the 401 408 B im2col rows written and read back
-STEM_BYTES_PER_FACE = 150528 + 2 * 802816 + 2 * 401408
+# stem (one launch): 150 528 B fp32 face in + 2 x 802 816 B int8 out (conv output and its fused BN)
+STEM_BYTES_PER_FACE = 150528 + 2 * 802816
 GOP_PER_FACE = 12.619          # 6.3093 GMAC: 53 convs + FC, real K, no padding
 FACE_BYTES = 112 * 112 * 3 * 4
 EMB_BYTES = 512 * 4
@@ -468,9 +468,8 @@ def run_own_arm(args, rank, local_rank, world):
             roof_stem = {"bound": "hbm", "achieved": round(stem_gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(stem_gbs / peaks["hbm_gbs"], 4), "ms": round(stem_ms, 4),
                          "bytes_per_face": STEM_BYTES_PER_FACE,
-                         "note": f"algorithmic bytes of the stem's launches (fp32 face read, two int8 112x112x64 outputs "
-                                 f"written, plus any intermediate the launches exchange through HBM) / CUDA-event time, "
-                                 f"against the {peaks['source']} copy bandwidth"}
+                         "note": f"algorithmic bytes of the stem's launch (fp32 face read, two int8 112x112x64 outputs "
+                                 f"written) / CUDA-event time, against the {peaks['source']} copy bandwidth"}
         all_tc = tc_ops / (tc_ms * 1e-3) / 1e12 if tc_ms > 0 else 0.0
         roof_all = {"achieved": round(all_tc, 1), "frac": round(all_tc / peak, 4), "peak": round(peak, 1), "unit": "TOP/s",
                     "note": f"all {len(tc)} tensor-core launches of a forward: {tc_ops / 1e9:.1f} GOP in {tc_ms:.3f} ms "

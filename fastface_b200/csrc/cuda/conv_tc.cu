@@ -380,61 +380,54 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
 
 
 // ---------------------------------------------------------------------------
-// Tensor-core stem (K = 32 GEMM over the im2col rows written by stem_pack_kernel)
+// Tensor-core stem (conv_tc_stem.cu): plan = the weights' tensor map and the launch geometry
 // ---------------------------------------------------------------------------
 struct StemTcPlan {
-    CUtensorMap mapA, mapB;
+    CUtensorMap mapB;
     int max_batch, n_sm, stages, smem_bytes, lut_bytes;
 };
 
-StemTcPlan* ffcu_stem_tc_plan(int max_batch, const int8_t* d_col, const int8_t* d_wk, bool has_bn2, int device)
+StemTcPlan* ffcu_stem_tc_plan(int max_batch, const int8_t* d_wk, bool has_bn2, int device)
 {
     encode_tiled_fn enc = get_encode();
     if (!enc) { ffcu_set_error("cuTensorMapEncodeTiled is not available"); return nullptr; }
     StemTcPlan* p = new StemTcPlan();
     p->max_batch = max_batch;
     cudaDeviceGetAttribute(&p->n_sm, cudaDevAttrMultiProcessorCount, device);
-    const cuuint64_t rows = (cuuint64_t)max_batch * 112 * 112;
-    cuuint64_t adims[4] = {32, rows, 1, 1};
-    cuuint64_t astr[3] = {32, 32 * rows, 32 * rows};
-    cuuint32_t abox[4] = {32, TC_TILE_M, 1, 1};
     cuuint32_t es[4] = {1, 1, 1, 1};
-    CUresult r = enc(&p->mapA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d_col, adims, astr, abox, es,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     cuuint64_t bdims[4] = {32, 64, 1, 1};
     cuuint64_t bstr[3] = {32, 32 * 64, 32 * 64};
     cuuint32_t bbox[4] = {32, 64, 1, 1};
-    if (r == CUDA_SUCCESS)
-        r = enc(&p->mapB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d_wk, bdims, bstr, bbox, es,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = enc(&p->mapB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d_wk, bdims, bstr, bbox, es,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { ffcu_set_error("cuTensorMapEncodeTiled(stem) failed: %d", (int)r); delete p; return nullptr; }
     p->lut_bytes = has_bn2 ? 64 * 256 : 0;
-    p->stages = TC_MAX_STAGES;
+    p->stages = TC_MAX_STAGES;                             // even: two producer warps take alternate tiles
     p->smem_bytes = 64 * 32 + p->stages * TC_TILE_M * 32 + 5 * TC_MAX_COUT * 4 + p->lut_bytes + (int)sizeof(TcShared) + 2048;
     return p;
 }
 
 void ffcu_stem_tc_free(StemTcPlan* p) { delete p; }
 
-int ffcu_stem_tc_launch(const StemTcPlan* p, int batch, int mode, const EpiTables& t, int8_t* out, int8_t* out_bn2,
-                        int* d_err, cudaStream_t s)
+// One-launch stem (conv_tc_stem.cu): the producers read the network input themselves.
+int ffcu_stem_fused_launch(const StemTcPlan* p, const void* in_any, int in_u8, const float* inv3, int batch, int mode,
+                           const EpiTables& t, int8_t* out, int8_t* out_bn2, int* d_err, cudaStream_t s)
 {
     if (batch < 1 || batch > p->max_batch) { ffcu_set_error("stem launch: batch out of range"); return -1; }
     const bool has_slope = t.slope != nullptr, has_bn2 = out_bn2 && t.bn_in && t.bn_lut && p->lut_bytes;
     int epi = EPI_RUNTIME;
     if (has_slope && has_bn2) epi = EPI_SLOPE_BN;
     else if (has_slope && !out_bn2) epi = EPI_SLOPE;
-    const int n_pix = batch * 112 * 112;                   // a multiple of 128
+    if (!t.no_overflow) epi = EPI_RUNTIME;
     TcParams prm = {};
     prm.t = t; prm.res = nullptr; prm.acc_out = nullptr; prm.out = out; prm.err = d_err;
     prm.out2 = has_bn2 ? out_bn2 : nullptr;
-    prm.batch = 1; prm.Ho = 1; prm.Wo = n_pix; prm.Cout = 64;
+    prm.batch = batch; prm.Ho = 112; prm.Wo = 112; prm.Cout = 64;
     prm.taps = 1; prm.Kw = 1; prm.Cp = 32; prm.cin_blocks = 1; prm.stride = 1; prm.pad = 0;
-    prm.TW = TC_TILE_M; prm.TH = 1; prm.TB = 1;
-    prm.tiles_w = n_pix / TC_TILE_M; prm.tiles_h = 1; prm.tiles_b = 1; prm.tiles_n = 1;
-    prm.total_tiles = prm.tiles_w;
+    prm.TW = 16; prm.TH = 8; prm.TB = 1;
+    prm.tiles_w = 112 / 16; prm.tiles_h = 112 / 8; prm.tiles_b = batch; prm.tiles_n = 1;
+    prm.total_tiles = prm.tiles_w * prm.tiles_h * batch;
     prm.stages = p->stages; prm.group = 1; prm.lut_bytes = has_bn2 ? p->lut_bytes : 0; prm.ntab = 5;
     prm.full_wait = TC_WAIT_CYCLES; prm.drop_stage = -1;
 #ifdef FF_TC_TIMING
@@ -442,5 +435,5 @@ int ffcu_stem_tc_launch(const StemTcPlan* p, int batch, int mode, const EpiTable
 #endif
     const int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
     prm.epi_wps = tc_epi_wps(64, prm.total_tiles / grid);
-    return tc_launch_k32(mode, epi, grid, p->smem_bytes, s, p->mapA, p->mapB, prm);
+    return tc_launch_stem(mode, epi, in_u8, grid, p->smem_bytes, s, p->mapB, prm, in_any, inv3);
 }

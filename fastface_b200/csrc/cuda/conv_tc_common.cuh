@@ -684,12 +684,15 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
         const size_t o0 = (((size_t)b * p.Ho + oh) * p.Wo + ow) * p.Cout + c0;
         const int a = local % TC_NACC(BN);
         const uint32_t aphase = (uint32_t)(local / TC_NACC(BN)) & 1;
-        // the residual operand does not depend on the accumulator: the first 32 channels' bytes are
-        // fetched before waiting for the MMAs, the next 32 while these are computed
+        // the residual operand does not depend on the accumulator: the first 64 channels' bytes are
+        // fetched before waiting for the MMAs, further ones two chunk pairs ahead of their use
         int rw[8], rn[8];
 #pragma unroll
         for (int g = 0; g < 8; g++) { rw[g] = 0; rn[g] = 0; }
-        if (has_res && valid && !TC_DBG(p, 4)) ld_global_32B(p.res + o0, rw);
+        if (has_res && valid && !TC_DBG(p, 4)) {
+            ld_global_32B(p.res + o0, rw);
+            if (n_pairs > 1) ld_global_32B(p.res + o0 + 32, rn);
+        }
         ok = mbar_wait(smem_u32(&sh->acc_full[a]), aphase, abort_flag, p.err, FFCU_ERR_EPI_TIMEOUT);
         if (!ok) break;
         tc_fence_after();
@@ -704,7 +707,6 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
             const size_t o = o0 + pr * 32;
             const uint32_t lut_pr = lut0 + (uint32_t)pr * (32u * 256u);
             tmem_ld16_issue(taddr + (uint32_t)(pr * 32 + 16), v1);            // lands while v0 is computed
-            if (has_res && more && valid && !TC_DBG(p, 4)) ld_global_32B(p.res + o + 32, rn);
             int w0[4], w0b[4], w1[4], w1b[4];
             if (valid && !TC_DBG(p, 8)) {
                 if (dump) {
@@ -742,6 +744,7 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
             }
 #pragma unroll
             for (int g = 0; g < 8; g++) rw[g] = rn[g];
+            if (has_res && pr + 2 < n_pairs && valid && !TC_DBG(p, 4)) ld_global_32B(p.res + o + 64, rn);   // two pairs ahead
             if (more) tmem_ld_wait(v0);
         }
         // this warp's TMEM reads are complete (the last tcgen05.wait::ld has returned)
@@ -796,12 +799,12 @@ __device__ __forceinline__ void tc_teardown(volatile int* abort_flag, uint32_t t
 // epi is an EPI_* value; f32 selects the FC epilogue (f32 output, no requantisation).
 int tc_launch_generic(int bn, int kc, int mode, int epi, bool f32, int grid, int smem, cudaStream_t s,
                       const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
-int tc_launch_k32(int mode, int epi, int grid, int smem, cudaStream_t s,
-                  const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
 int tc_launch_ws(int bn, int mode, int epi, int grid, int smem, cudaStream_t s,
                  const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
 int tc_launch_pair(int bn, int mode, int epi, bool f32, int grid, int smem, cudaStream_t s,
                    const CUtensorMap& mapA, const CUtensorMap& mapB, const TcParams& prm);
+int tc_launch_stem(int mode, int epi, int in_u8, int grid, int smem, cudaStream_t s, const CUtensorMap& mapB,
+                   const TcParams& prm, const void* in_any, const float* inv3);
 int tc_launch_wsp(int mode, int epi, int grid, int smem, cudaStream_t s,
                   const CUtensorMap& mapA, const CUtensorMap& mapB_half, const TcParams& prm);
 

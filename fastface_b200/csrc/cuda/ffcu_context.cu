@@ -33,7 +33,7 @@ struct DevLayer {
     int8_t* bn_lut = nullptr;  // device copy of the fused BN's table
     bool fused_stem = false;   // conv that also does the input quantisation (reads the fp32 input)
     bool skip = false;         // quantise layer absorbed by the fused stem
-    StemTcPlan* stem_tc = nullptr; // fused stem on tensor cores: pack kernel + K = 32 GEMM (else the dp4a stem kernel)
+    StemTcPlan* stem_tc = nullptr; // fused stem on tensor cores, one launch (else the dp4a stem kernel)
     int8_t* wk32 = nullptr;        // its weights repacked [64][32]
 };
 
@@ -47,7 +47,6 @@ struct ffcu_ctx {
     // overlap the kernels of step k (copy-in, compute and copy-out streams).
     float* in_slot[2] = {};      // [max_batch][112][112][3] f32
     float* out_slot[2] = {};     // [max_batch][512] f32
-    int8_t* d_col = nullptr;     // tensor-core stem: im2col rows [max_batch * 12544][32]
     float* d_in = nullptr;       // slot the next launch_forward reads
     bool in_u8 = false;          // that slot holds 8-bit pixels [n][112][112][3] instead of fp32
     float* d_out = nullptr;      // slot the next launch_forward writes
@@ -156,7 +155,7 @@ extern "C" void ffcu_destroy(ffcu_ctx* c)
         if (c->ev_compute_done[k]) cudaEventDestroy(c->ev_compute_done[k]);
         if (c->ev_out_copied[k]) cudaEventDestroy(c->ev_out_copied[k]);
     }
-    cudaFree(c->d_err); cudaFree(c->d_fc_scratch); cudaFree(c->d_col);
+    cudaFree(c->d_err); cudaFree(c->d_fc_scratch);
     if (c->h_err) cudaFreeHost(c->h_err);
     if (c->stream) cudaStreamDestroy(c->stream);
     if (c->s_in) cudaStreamDestroy(c->s_in);
@@ -267,19 +266,18 @@ extern "C" int ffcu_finalize(ffcu_ctx* c)
             s.d.Cin_pad == 4 && s.d.Cout == 64 && s.d.Kh == 3 && s.d.Kw == 3 && s.d.stride == 1 && s.d.pad == 1 &&
             s.d.H == 112 && s.d.W == 112 && s.d.res_buf < 0) {
             s.fused_stem = true; q.skip = true;
-            // tensor-core form: a pack pass writes 32-byte im2col rows, a K = 32 GEMM does the rest
+            // tensor-core form: im2col rows built in shared memory, K = 32 GEMM, all in one launch
             const char* st = getenv("FF_STEM_TC");
             if (!(st && st[0] == '0') && s.epi.no_overflow && s.epi.slope) {
-                const size_t col_bytes = (size_t)c->max_batch * 112 * 112 * 32;
-                if (cudaMalloc(&c->d_col, col_bytes + 1024) == cudaSuccess && cudaMalloc(&s.wk32, 64 * 32) == cudaSuccess &&
+                if (cudaMalloc(&s.wk32, 64 * 32) == cudaSuccess &&
                     ffcu_stem_weight_k32(s.w, s.wk32, 64, c->stream) == 0 && cudaStreamSynchronize(c->stream) == cudaSuccess)
-                    s.stem_tc = ffcu_stem_tc_plan(c->max_batch, c->d_col, s.wk32, s.d.bn2_dst_buf >= 0, c->device);
-                if (!s.stem_tc) { cudaFree(c->d_col); c->d_col = nullptr; cudaFree(s.wk32); s.wk32 = nullptr; cudaGetLastError(); }
+                    s.stem_tc = ffcu_stem_tc_plan(c->max_batch, s.wk32, s.d.bn2_dst_buf >= 0, c->device);
+                if (!s.stem_tc) { cudaFree(s.wk32); s.wk32 = nullptr; cudaGetLastError(); }
             }
         }
     }
     c->launches = 0;
-    for (auto& L : c->layers) { if (!L.skip) c->launches++; if (L.stem_tc) c->launches++; }
+    for (auto& L : c->layers) if (!L.skip) c->launches++;
     c->finalized = true;
     return 0;
 }
@@ -327,11 +325,9 @@ static int launch_layer(ffcu_ctx* c, size_t k, int n, int32_t* acc_dbg, bool unf
         return ffcu_launch_quant(c->d_in, n * d.H * d.W, L.tab[4], c->bufs[d.dst_buf], s);
     case FFCU_CONV: {
         const int8_t* res = d.res_buf >= 0 ? c->bufs[d.res_buf] : nullptr;
-        if (L.fused_stem && !unfused && L.stem_tc) {
-            int rc = ffcu_launch_stem_pack(c->d_in, c->in_u8 ? 1 : 0, c->layers[0].tab[4], n, c->d_col, s);
-            if (rc != 0) return rc;
-            return ffcu_stem_tc_launch(L.stem_tc, n, c->mode, L.epi, c->bufs[d.dst_buf], out2, c->d_err, s);
-        }
+        if (L.fused_stem && !unfused && L.stem_tc)
+            return ffcu_stem_fused_launch(L.stem_tc, c->d_in, c->in_u8 ? 1 : 0, c->layers[0].tab[4], n, c->mode, L.epi,
+                                          c->bufs[d.dst_buf], out2, c->d_err, s);
         if (L.fused_stem && !unfused)
             return ffcu_launch_stem(c->d_in, c->in_u8 ? 1 : 0, c->layers[0].tab[4], L.w, L.epi, n, c->mode, c->bufs[d.dst_buf], out2, nullptr, s);
         if (L.tc) return ffcu_tc_launch(tc_plan_for(c, L, n), n, c->mode, L.epi, res, acc_dbg, c->bufs[d.dst_buf], out2, c->d_err, s);
@@ -360,7 +356,6 @@ static int launch_forward(ffcu_ctx* c, int n)
         if (rc != 0) return rc;
         const DevLayer& L = c->layers[k];
         if (!L.skip) launches++;
-        if (L.stem_tc) launches++;                   // pack pass + GEMM
         if (L.d.kind == FFCU_FC && n <= FFCU_FC_SMALL_MAX_BATCH && L.d.Cout <= 512 && !c->no_fc_small) launches++;
     }
     c->launches = launches;

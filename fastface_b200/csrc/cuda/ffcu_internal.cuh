@@ -159,16 +159,16 @@ int ffcu_launch_fc_small(const int8_t* act, const int8_t* w, const float* w_scal
 // Tensor-core implicit GEMM (conv_tc.cu)
 // ---------------------------------------------------------------------------
 struct TcPlan;   // opaque: tile shape, TMA descriptors, launch geometry for one layer
-int ffcu_launch_stem_pack(const void* in_any, int in_u8, const float* inv3, int batch, int8_t* col, cudaStream_t s);
 int ffcu_stem_weight_k32(const int8_t* d_w, int8_t* d_wk, int Cout, cudaStream_t s);
-// Tensor-core stem: plan over the im2col buffer d_col [max_batch * 12544][32] and the repacked weights d_wk [64][32]
+// Tensor-core stem (one launch): plan over the repacked weights d_wk [64][32]
 struct StemTcPlan;
-StemTcPlan* ffcu_stem_tc_plan(int max_batch, const int8_t* d_col, const int8_t* d_wk, bool has_bn2, int device);
+StemTcPlan* ffcu_stem_tc_plan(int max_batch, const int8_t* d_wk, bool has_bn2, int device);
 void ffcu_stem_tc_free(StemTcPlan* p);
-int ffcu_stem_tc_launch(const StemTcPlan* p, int batch, int mode, const EpiTables& t, int8_t* out, int8_t* out_bn2,
-                        int* d_err, cudaStream_t s);
 // Column-tile width (64 / 128 / 256) for a call of `batch` faces, and the plan for one width.
 int     ffcu_tc_pick_bn(const ffcu_layer& L, int batch, int device);
+// NULL when the layer shape is not covered by the tensor-core kernels.
+int ffcu_stem_fused_launch(const StemTcPlan* p, const void* in_any, int in_u8, const float* inv3, int batch, int mode,
+                           const EpiTables& t, int8_t* out, int8_t* out_bn2, int* d_err, cudaStream_t s);
 // NULL when the layer shape is not covered by the tensor-core kernels.
 TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, const int8_t* d_w, int device, int bn);
 void    ffcu_tc_free(TcPlan* p);

@@ -363,67 +363,6 @@ __global__ void __launch_bounds__(STEM_THREADS) stem_kernel(const void* __restri
     }
 }
 
-// ---------------------------------------------------------------------------
-// Tensor-core form of the stem, CUDA-core half: quantise the input
-// (quantize_fp32_nhwc_to_int8, reference kernels/int8_epilogue.c:231-247) and write one 32-byte
-// im2col row per output pixel: bytes [kh][kw][c] (27 values, zero where the tap falls outside
-// the image) + 5 zero bytes.  The K = 32 GEMM + epilogue is conv_k32_kernel.
-// A block owns a 16x16 pixel tile (256 threads, one pixel each).
-// ---------------------------------------------------------------------------
-template <bool IN_U8>
-__global__ void __launch_bounds__(256) stem_pack_kernel(const void* __restrict__ in_any, const float* __restrict__ inv3,
-                                                        int8_t* __restrict__ col)
-{
-    constexpr int H = 112, W = 112, P = STEM_T + 2;
-    __shared__ int s_in[P * P];
-    const int b = blockIdx.z;
-    const int x0 = blockIdx.x * STEM_T, y0 = blockIdx.y * STEM_T;
-    const float i0 = __ldg(inv3), i1 = __ldg(inv3 + 1), i2 = __ldg(inv3 + 2);
-    for (int i = threadIdx.x; i < P * P; i += 256) {
-        int py = y0 - 1 + i / P, px = x0 - 1 + i % P;
-        int v = 0;
-        if (py >= 0 && py < H && px >= 0 && px < W) {
-            const size_t e = (((size_t)b * H + py) * W + px) * 3;
-            float f0, f1, f2;
-            if (IN_U8) {
-                const uint8_t* x = (const uint8_t*)in_any + e;
-                f0 = __fdiv_rn(__fsub_rn((float)__ldg(x), 127.5f), 127.5f);
-                f1 = __fdiv_rn(__fsub_rn((float)__ldg(x + 1), 127.5f), 127.5f);
-                f2 = __fdiv_rn(__fsub_rn((float)__ldg(x + 2), 127.5f), 127.5f);
-            } else {
-                const float* x = (const float*)in_any + e;
-                f0 = __ldg(x); f1 = __ldg(x + 1); f2 = __ldg(x + 2);
-            }
-            int q0 = max(-128, min(127, __float2int_rn(__fmul_rn(f0, i0))));
-            int q1 = max(-128, min(127, __float2int_rn(__fmul_rn(f1, i1))));
-            int q2 = max(-128, min(127, __float2int_rn(__fmul_rn(f2, i2))));
-            v = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16);
-        }
-        s_in[i] = v;
-    }
-    __syncthreads();
-    const int tx = threadIdx.x % STEM_T, ty = threadIdx.x / STEM_T;
-    unsigned a[9];
-#pragma unroll
-    for (int kh = 0; kh < 3; kh++)
-#pragma unroll
-        for (int kw = 0; kw < 3; kw++) a[kh * 3 + kw] = (unsigned)s_in[(ty + kh) * P + tx + kw];
-    // nine (c0, c1, c2, 0) words -> 27 consecutive bytes
-    int4 lo, hi;
-    lo.x = (int)__byte_perm(a[0], a[1], 0x4210);
-    lo.y = (int)__byte_perm(a[1], a[2], 0x5421);
-    lo.z = (int)__byte_perm(a[2], a[3], 0x6542);
-    lo.w = (int)__byte_perm(a[4], a[5], 0x4210);
-    hi.x = (int)__byte_perm(a[5], a[6], 0x5421);
-    hi.y = (int)__byte_perm(a[6], a[7], 0x6542);
-    hi.z = (int)(a[8] & 0x00ffffffu);
-    hi.w = 0;
-    const size_t pix = ((size_t)b * H + (y0 + ty)) * W + (x0 + tx);
-    int4* dst = (int4*)(col + pix * 32);
-    dst[0] = lo;
-    dst[1] = hi;
-}
-
 // Stem weights [co][tap][4] (the dp4a layout) -> [co][32] with k = 3 * tap + c, zero padded.
 __global__ void stem_weight_k32_kernel(const int8_t* __restrict__ w, int8_t* __restrict__ wk, int Cout)
 {
@@ -434,15 +373,6 @@ __global__ void stem_weight_k32_kernel(const int8_t* __restrict__ w, int8_t* __r
         if (k < 27) v = w[co * 36 + (k / 3) * 4 + (k % 3)];
         wk[co * 32 + k] = v;
     }
-}
-
-int ffcu_launch_stem_pack(const void* in_any, int in_u8, const float* inv3, int batch, int8_t* col, cudaStream_t s)
-{
-    dim3 grid(112 / STEM_T, 112 / STEM_T, batch);
-    if (in_u8) stem_pack_kernel<true><<<grid, 256, 0, s>>>(in_any, inv3, col);
-    else       stem_pack_kernel<false><<<grid, 256, 0, s>>>(in_any, inv3, col);
-    FFCU_CHECK(cudaGetLastError());
-    return 0;
 }
 
 int ffcu_stem_weight_k32(const int8_t* d_w, int8_t* d_wk, int Cout, cudaStream_t s)
