@@ -34,6 +34,8 @@ CASES = {
     "down28": (256, 256, 28, 3, 2),
     "shortcut112": (64, 64, 112, 1, 2),
     "shortcut56": (64, 128, 56, 1, 2),
+    "conv14_512": (256, 512, 14, 3, 1),
+    "down14": (512, 512, 14, 3, 2),
 }
 
 
