@@ -554,7 +554,7 @@ def run_own_arm(args, rank, local_rank, world):
                 "sustained": {"value": round(world * sus_steps * B / (sus_ms * 1e-3), 1), "unit": "faces/s", "steps": sus_steps,
                               "seconds": round(sus_ms * 1e-3, 3), "clocks": sclk.summary(),
                               "value_x_mhz": round(world * sus_steps * B / (sus_ms * 1e-3) * (sclk.summary()["sm_mhz"] or 0), 0),
-                              "frac_of_2x_bf16_sustained": round(GOP_PER_FACE * sus_steps * B / (sus_ms * 1e-3) / 1e3 / peak_sustained, 4),
+                              "frac_of_2x_bf16_sustained": round(GOP_PER_FACE * sus_steps * B / (sus_ms * 1e-3) / 1e3 / peak_sustained, 4),   # per GPU
                               "note": "device-resident forwards back to back for a few seconds on rank 0's clock sampling; "
                                       "value_x_mhz = faces/s x median SM MHz, for comparing boxes whose power-capped clocks differ"},
                 "self_check": "timed end-to-end embeddings equal the batch-8 run of the same faces (bit for bit)",
