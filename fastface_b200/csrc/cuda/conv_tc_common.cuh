@@ -555,14 +555,19 @@ __device__ __forceinline__ void tc_fc16(const TcParams& p, const float* tab, con
 }
 
 // Programmatic dependent launch.  Each tensor-core kernel is launched with
-// cudaLaunchAttributeProgrammaticStreamSerialization: its CTAs may become resident while the
-// previous kernel of the stream is still finishing, run their set-up (barriers, TMEM, the
-// per-channel tables, which no kernel writes) and then block here until that kernel has
-// completed and its stores are visible.  Nothing a previous kernel produced, and nothing it may
-// still read, is touched before this point.
-__device__ __forceinline__ void tc_pdl_sync()
+// cudaLaunchAttributeProgrammaticStreamSerialization.  tc_pdl_trigger, the kernel's first
+// statement, lets the NEXT kernel of the stream become resident at once (on SMs this one leaves
+// free: always the case at small batch, where a launch is 8-16 CTAs), so that its launch latency
+// and set-up (barriers, TMEM, the per-channel tables, which no kernel writes) are hidden several
+// kernels deep.  tc_pdl_wait blocks until the PREVIOUS kernel has completed and its stores are
+// visible; every warp that touches activations executes it first.  Nothing a previous kernel
+// produced, and nothing it may still read, is touched before that point.
+__device__ __forceinline__ void tc_pdl_trigger()
 {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void tc_pdl_wait()
+{
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 

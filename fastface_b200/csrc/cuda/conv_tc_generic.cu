@@ -8,6 +8,7 @@ template <int BN, int KC, bool CONTRACT, bool OUT_F32, int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
 {
+    tc_pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     // stage ring must start on a 1024-byte boundary (swizzle atoms)
     // round up to 1024 bytes by pointer arithmetic on the __shared__ array (an integer round-trip
@@ -30,7 +31,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     tc_load_tables(tab, p);
     tc_load_lut(lut, p, (int)(blockIdx.x % p.tiles_n) * BN, BN);
     tc_setup(sh, p.stages, TMEM_COLS, warp, p.epi_wps);
-    tc_pdl_sync();
     const uint32_t tmem_base = sh->tmem_base;
     volatile int* abort_flag = &sh->abort_flag;
 
@@ -55,6 +55,27 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             const int stage_bytes = G * SUB_BYTES;
             const int n_steps = kblocks / G;
             const int tn = blockIdx.x % p.tiles_n;
+            // this lane's first block of a tile: kb = g
+            int c0_first = g * KC, kw_first = 0, kh_first = 0;
+            while (c0_first >= p.Cp) { c0_first -= p.Cp; if (++kw_first == p.Kw) { kw_first = 0; kh_first++; } }
+            // The weights do not depend on the previous kernel: the weight boxes of the first tile's
+            // first steps (as many as the ring holds) are requested before the programmatic-dependency
+            // wait, the activation boxes after it.  Each slot's byte count is armed here for both.
+            int pre = 0;
+            if ((int)blockIdx.x < p.total_tiles && !TC_DBG(p, 1)) {
+                pre = n_steps < p.stages ? n_steps : p.stages;
+                int c0 = c0_first, kw = kw_first, kh = kh_first;
+#pragma unroll 1
+                for (int it = 0; it < pre; it++) {
+                    if (lane == 0) mbar_expect_tx(full0 + it * 8, G * SUB_BYTES);
+                    __syncwarp();
+                    if (issuer && !is_a)
+                        tma_load_4d(smem0 + it * stage_bytes, map, full0 + it * 8, (kh * p.Kw + kw) * p.Cp + c0, tn * BN, 0, 0);
+                    c0 += G * KC;
+                    while (c0 >= p.Cp) { c0 -= p.Cp; if (++kw == p.Kw) { kw = 0; kh++; } }
+                }
+            }
+            tc_pdl_wait();
             TileWalk wk;
             walk_init(wk, p, blockIdx.x / p.tiles_n, gridDim.x / p.tiles_n);
             for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, walk_next(wk, p)) {
@@ -62,27 +83,32 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 const int x0 = tw * p.TW * p.stride - p.pad;
                 const int y0 = th * p.TH * p.stride - p.pad;
                 const int c3 = is_a ? tb * p.TB : 0;
-                // this lane's first block: kb = g
-                int c0 = g * KC, kw = 0, kh = 0;
-                while (c0 >= p.Cp) { c0 -= p.Cp; if (++kw == p.Kw) { kw = 0; kh++; } }
+                int c0 = c0_first, kw = kw_first, kh = kh_first;
 #pragma unroll 1
                 for (int it = 0; it < n_steps; it++) {
-                    ok = mbar_wait(empty0 + stage * 8, phase ^ 1, abort_flag, p.err, FFCU_ERR_EMPTY_TIMEOUT);
-                    if (!ok) break;
+                    const bool first_fill = it < pre;          // slot is fresh and its weight box is on its way
+                    if (!first_fill) {
+                        ok = mbar_wait(empty0 + stage * 8, phase ^ 1, abort_flag, p.err, FFCU_ERR_EMPTY_TIMEOUT);
+                        if (!ok) break;
+                    }
                     if (TC_DBG(p, 1)) { if (lane == 0) mbar_arrive(full0 + stage * 8); }
                     else if (tile == (int)blockIdx.x && it == p.drop_stage) {
                         // armed by ffcu_test_arm_timeout for one launch: this step's data never arrives
                     } else {
-                        if (lane == 0) mbar_expect_tx(full0 + stage * 8, G * SUB_BYTES);
-                        __syncwarp();                           // the byte count is armed before any copy can land
+                        if (!first_fill) {
+                            if (lane == 0) mbar_expect_tx(full0 + stage * 8, G * SUB_BYTES);
+                            __syncwarp();                       // the byte count is armed before any copy can land
+                        }
                         const int tapk = (kh * p.Kw + kw) * p.Cp + c0;
-                        if (issuer) tma_load_4d(smem0 + stage * stage_bytes, map, full0 + stage * 8,
-                                    is_a ? c0 : tapk, is_a ? x0 + kw : tn * BN, is_a ? y0 + kh : 0, c3);
+                        if (issuer && (is_a || !first_fill))
+                            tma_load_4d(smem0 + stage * stage_bytes, map, full0 + stage * 8,
+                                        is_a ? c0 : tapk, is_a ? x0 + kw : tn * BN, is_a ? y0 + kh : 0, c3);
                     }
                     c0 += G * KC;
                     while (c0 >= p.Cp) { c0 -= p.Cp; if (++kw == p.Kw) { kw = 0; kh++; } }
                     if (++stage == p.stages) { stage = 0; phase ^= 1; }
                 }
+                pre = 0;
             }
         }
     } else if (warp == 1) {
@@ -134,6 +160,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             }
         }
     } else {
+        tc_pdl_wait();
         tc_epilogue_role<BN, CONTRACT, OUT_F32, EPI>(p, tab, lut, sh, tmem_base, abort_flag, warp, lane,
                                                 blockIdx.x, gridDim.x, p.total_tiles, 1, 0, 0u);
     }

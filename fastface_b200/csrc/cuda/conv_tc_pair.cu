@@ -19,6 +19,7 @@ template <int BN, bool CONTRACT, bool OUT_F32, int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
 {
+    tc_pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     // round up to 1024 bytes by pointer arithmetic on the __shared__ array (an integer round-trip
     // would hide the address space from the compiler and turn every table read into a generic load)
@@ -61,7 +62,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     __syncthreads();
     cluster_sync_all();                                  // peer's barriers are initialised
     tc_fence_after();
-    tc_pdl_sync();
+    tc_pdl_wait();
     const uint32_t tmem_base = sh->tmem_base;
     volatile int* abort_flag = &sh->abort_flag;
 

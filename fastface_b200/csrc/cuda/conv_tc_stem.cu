@@ -59,6 +59,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_stem_kernel(const __grid_constant__ CUtensorMap mapB, const TcParams p, const void* __restrict__ in_any,
                  const float* __restrict__ inv3)
 {
+    tc_pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     constexpr int BN = 64;
@@ -89,7 +90,7 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap mapB, const TcParams p, con
         }
     }
     tc_setup(sh, p.stages, TMEM_COLS, warp, p.epi_wps);
-    tc_pdl_sync();
+    tc_pdl_wait();
     const uint32_t tmem_base = sh->tmem_base;
     volatile int* abort_flag = &sh->abort_flag;
 

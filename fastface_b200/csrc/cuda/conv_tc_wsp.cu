@@ -27,6 +27,7 @@ template <bool CONTRACT, int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_wsp_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
 {
+    tc_pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     constexpr int BN = 128, KC = 128;
@@ -81,7 +82,7 @@ conv_wsp_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         if (rank == 0 && lane == 0) mbar_expect_tx(smem_u32(&sh->w_full), 2 * W_BYTES);
         __syncwarp();
         if (lane < 9) tma2_load_4d(smem_u32(s_w + lane * W_TAP_BYTES), &mapB, wbar_leader, lane * p.Cp, (int)rank * (BN / 2), 0, 0);
-        tc_pdl_sync();
+        tc_pdl_wait();
         const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
         const uint32_t full0_leader = map_to_cta(full0, 0);
         int stage = 0; uint32_t phase = 0;
@@ -104,7 +105,7 @@ conv_wsp_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
     } else if (warp == 1 || warp == TC_ISSUER2_WARP) {
-        tc_pdl_sync();
+        tc_pdl_wait();
         if (rank == 0) {
             // Two MMA issuers (leader CTA) take alternate tiles; each derives its ring positions from
             // the tile's index.  The warp loops and waits together, lane 0 issues.
@@ -158,7 +159,7 @@ conv_wsp_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             }
         }
     } else {
-        tc_pdl_sync();
+        tc_pdl_wait();
         const uint32_t leader_acc_empty = map_to_cta(smem_u32(&sh->acc_empty[0]), 0);
         tc_epilogue_role<BN, CONTRACT, false, EPI>(p, tab, lut, sh, tmem_base, abort_flag, warp, lane,
                                                    pair_id, n_pairs, total, 2, (int)rank, leader_acc_empty);

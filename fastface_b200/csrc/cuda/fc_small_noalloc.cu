@@ -9,8 +9,8 @@
 // image, so the call allocates nothing at all.
 //
 // Limits and sharing rules:
-//   * batch <= 16 and N <= 512 (the array is 16 x 512 int32 = 32 KiB; every GPU that loads
-//     the library carries it until the process exits);
+//   * batch <= 16 and N <= 512 (the array is 64 ticket counters + 16 x 512 int32 sums = 32.25 KiB;
+//     every GPU that loads the library carries it until the process exits);
 //   * all calls on one device share the one array.  It is cleared at the start of each call
 //     on the caller's stream, so calls issued back to back on one stream are fine, but two
 //     calls that can overlap on the GPU (different streams, different host threads) race on it;
@@ -29,7 +29,7 @@
 
 // The split-K accumulator.  In host code this name is only a handle for the symbol, not a
 // device address: the address each device gives it comes from cudaGetSymbolAddress below.
-static __device__ __align__(256) int g_fc_noalloc_scratch[FC_NOALLOC_MAX_BATCH * FC_NOALLOC_MAX_N];
+static __device__ __align__(256) int g_fc_noalloc_scratch[FFCU_FC_SMALL_TICKETS + FC_NOALLOC_MAX_BATCH * FC_NOALLOC_MAX_N];
 
 static int* g_scratch_addr[FC_NOALLOC_MAX_DEVICES];   // per device, filled on first use
 
@@ -85,7 +85,8 @@ extern "C" int ffcu_fc_small_noalloc(const int8_t* act, const int8_t* w, const f
     int* scratch = g_scratch_addr[dev];
     cudaStream_t s = (cudaStream_t)stream;
     // the array keeps whatever the last call (or an aborted one) left: start from zero
-    fc_noalloc_clear_kernel<<<(batch * N + 255) / 256, 256, 0, s>>>(batch * N);
+    const int used = FFCU_FC_SMALL_TICKETS + batch * N;    // ticket counters, then the sums this call adds into
+    fc_noalloc_clear_kernel<<<(used + 255) / 256, 256, 0, s>>>(used);
     FFCU_CHECK(cudaGetLastError());
     return ffcu_launch_fc_small(act, w, w_scale, bias, batch, N, K, mode, scratch, out, s);
 }

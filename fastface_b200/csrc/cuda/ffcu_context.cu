@@ -52,7 +52,7 @@ struct ffcu_ctx {
     float* d_out = nullptr;      // slot the next launch_forward writes
     cudaEvent_t ev_in_ready[2] = {}, ev_compute_done[2] = {}, ev_out_copied[2] = {};
     unsigned long long seq = 0;
-    int* d_fc_scratch = nullptr; // int32 [16][512] split-K accumulator of the small-batch FC (kept zero between calls)
+    int* d_fc_scratch = nullptr; // small-batch FC: 64 ticket counters + int32 [16][512] split-K accumulator (kept zero between calls)
     int* d_err = nullptr;        // device error word
     int* h_err = nullptr;        // pinned mirror
     cudaStream_t stream = nullptr;       // compute
@@ -115,8 +115,8 @@ extern "C" ffcu_ctx* ffcu_create(int device, int max_batch, int n_bufs, size_t b
     ok = ok && cudaStreamCreateWithFlags(&c->s_in, cudaStreamNonBlocking) == cudaSuccess;
     ok = ok && cudaStreamCreateWithFlags(&c->s_out, cudaStreamNonBlocking) == cudaSuccess;
     ok = ok && cudaMalloc(&c->d_err, sizeof(int)) == cudaSuccess;
-    ok = ok && cudaMalloc(&c->d_fc_scratch, FFCU_FC_SMALL_MAX_BATCH * 512 * sizeof(int)) == cudaSuccess;
-    if (ok) cudaMemset(c->d_fc_scratch, 0, FFCU_FC_SMALL_MAX_BATCH * 512 * sizeof(int));
+    ok = ok && cudaMalloc(&c->d_fc_scratch, (FFCU_FC_SMALL_TICKETS + FFCU_FC_SMALL_MAX_BATCH * 512) * sizeof(int)) == cudaSuccess;
+    if (ok) cudaMemset(c->d_fc_scratch, 0, (FFCU_FC_SMALL_TICKETS + FFCU_FC_SMALL_MAX_BATCH * 512) * sizeof(int));
     ok = ok && cudaHostAlloc(&c->h_err, sizeof(int), cudaHostAllocDefault) == cudaSuccess;
     ok = ok && cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess;
     if (ok) { cudaMemset(c->d_err, 0, sizeof(int)); *c->h_err = 0; }
@@ -356,7 +356,6 @@ static int launch_forward(ffcu_ctx* c, int n)
         if (rc != 0) return rc;
         const DevLayer& L = c->layers[k];
         if (!L.skip) launches++;
-        if (L.d.kind == FFCU_FC && n <= FFCU_FC_SMALL_MAX_BATCH && L.d.Cout <= 512 && !c->no_fc_small) launches++;
     }
     c->launches = launches;
     return 0;

@@ -152,6 +152,7 @@ int ffcu_launch_fc_simt(const int8_t* act, const int8_t* w, const float* w_scale
 
 // Small-batch (<= 16) split-K FC; scratch is an int32 [batch][N] accumulator, zero on entry and exit.
 #define FFCU_FC_SMALL_MAX_BATCH 16
+#define FFCU_FC_SMALL_TICKETS 64          // ticket counters at the head of the small-batch FC scratch (one per 8 outputs)
 int ffcu_launch_fc_small(const int8_t* act, const int8_t* w, const float* w_scale, const float* bias,
                          int batch, int N, int K, int mode, int* scratch, float* out, cudaStream_t s);
 

@@ -410,35 +410,55 @@ int ffcu_launch_stem(const void* in_any, int in_u8, const float* inv3, const int
 // ---------------------------------------------------------------------------
 // Small-batch FC (batch <= 16): the 12.85 MB weight matrix is the whole cost, so the
 // K axis is split across blocks to put every SM on it.  Block (n-group, k-split) computes
-// 8 outputs x up to 16 faces over its K slice with dp4a, reduces across its 256 threads and
+// 8 outputs x up to MAXB faces over its K slice with dp4a, reduces across its threads and
 // adds the int32 partial sums into a scratch accumulator [batch][N] (integer adds commute,
-// so the result is exact).  fc_finish_kernel then applies
-// out = bias + (float)dot * w_scale (reference kernels/gemm_int8_matvec.c:78-79) and
-// clears the scratch for the next call.
+// so the result is exact).  The block that arrives last at its n-group's ticket counter
+// applies out = bias + (float)dot * w_scale (reference kernels/gemm_int8_matvec.c:78-79)
+// and leaves sums and ticket at zero for the next call: one launch, no finishing kernel.
+//
+// The kernel is launched with programmatic stream serialisation: a block requests its weight
+// slice (which no kernel writes) BEFORE waiting for the previous kernel, so at batch 1 the
+// weight stream is hidden behind the last convolution; the activations are read after the wait.
+// MAXB (1, 2, 4, 8, 16 faces) sizes the accumulator registers: at MAXB = 1 all 1 024 blocks are
+// resident at once and every weight byte is in flight together.
+//
+// scratch layout: [FCS_TICKETS] ticket counters, then int32 sums [batch][N]; all zero on entry
+// (and again on exit).
 // ---------------------------------------------------------------------------
 #define FCS_TN 8
 #define FCS_MAXB 16
-__global__ void __launch_bounds__(256) fc_splitk_kernel(const int8_t* __restrict__ act, const int8_t* __restrict__ w,
-                                                        int B, int N, int K, int k_per_split,
-                                                        int* __restrict__ scratch)
+#define FCS_THREADS 128
+template <int MAXB, bool CONTRACT>
+__global__ void __launch_bounds__(FCS_THREADS) fc_small_kernel(const int8_t* __restrict__ act, const int8_t* __restrict__ w,
+                                                               const float* __restrict__ w_scale, const float* __restrict__ bias,
+                                                               int B, int N, int K, int k_per_split,
+                                                               int* __restrict__ scratch, float* __restrict__ out)
 {
-    __shared__ int red[8][FCS_MAXB * FCS_TN];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    __shared__ int red[FCS_THREADS / 32][MAXB * FCS_TN];
+    __shared__ int s_last;
+    int* tickets = scratch;
+    int* sums = scratch + FFCU_FC_SMALL_TICKETS;
     const int n0 = blockIdx.x * FCS_TN;
     const int k0 = blockIdx.y * k_per_split;
     const int kv = k_per_split >> 4;                       // 16-byte steps in this slice
-    int acc[FCS_MAXB][FCS_TN];
+    int acc[MAXB][FCS_TN];
 #pragma unroll
-    for (int i = 0; i < FCS_MAXB; i++)
+    for (int i = 0; i < MAXB; i++)
 #pragma unroll
         for (int j = 0; j < FCS_TN; j++) acc[i][j] = 0;
-    for (int k = threadIdx.x; k < kv; k += blockDim.x) {
-        int4 ww[FCS_TN];
+    int k = threadIdx.x;
+    int4 ww[FCS_TN];
+    if (k < kv) {
 #pragma unroll
         for (int j = 0; j < FCS_TN; j++) ww[j] = __ldg((const int4*)(w + (size_t)(n0 + j) * K + k0) + k);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");      // the activations come from the previous kernel
+    while (k < kv) {
 #pragma unroll
-        for (int i = 0; i < FCS_MAXB; i++) {
+        for (int i = 0; i < MAXB; i++) {
             if (i >= B) break;
-            const int4 a = __ldg((const int4*)(act + (size_t)i * K + k0) + k);
+            const int4 a = __ldcg((const int4*)(act + (size_t)i * K + k0) + k);
 #pragma unroll
             for (int j = 0; j < FCS_TN; j++) {
                 int s = acc[i][j];
@@ -447,10 +467,15 @@ __global__ void __launch_bounds__(256) fc_splitk_kernel(const int8_t* __restrict
                 acc[i][j] = s;
             }
         }
+        k += FCS_THREADS;
+        if (k < kv) {
+#pragma unroll
+            for (int j = 0; j < FCS_TN; j++) ww[j] = __ldg((const int4*)(w + (size_t)(n0 + j) * K + k0) + k);
+        }
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
-    for (int i = 0; i < FCS_MAXB; i++) {
+    for (int i = 0; i < MAXB; i++) {
         if (i >= B) break;
 #pragma unroll
         for (int j = 0; j < FCS_TN; j++) {
@@ -461,42 +486,60 @@ __global__ void __launch_bounds__(256) fc_splitk_kernel(const int8_t* __restrict
         }
     }
     __syncthreads();
+    const int i = threadIdx.x / FCS_TN, j = threadIdx.x % FCS_TN;     // FCS_THREADS = 16 faces x 8 outputs
     if (threadIdx.x < B * FCS_TN) {
         int s = 0;
 #pragma unroll
-        for (int wv = 0; wv < 8; wv++) s += red[wv][threadIdx.x];
-        const int i = threadIdx.x / FCS_TN, j = threadIdx.x % FCS_TN;
-        atomicAdd(scratch + (size_t)i * N + n0 + j, s);
+        for (int wv = 0; wv < FCS_THREADS / 32; wv++) s += red[wv][threadIdx.x];
+        atomicAdd(sums + (size_t)i * N + n0 + j, s);
+        __threadfence();                                   // the partial sum is visible before the ticket is taken
     }
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(tickets + blockIdx.x, 1) == (int)gridDim.y - 1) ? 1 : 0;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();                                       // every other block's sums are visible from here on
+    if (threadIdx.x < B * FCS_TN) {
+        const int n = n0 + j;
+        const int dot = atomicExch(sums + (size_t)i * N + n, 0);      // read and leave clean for the next call
+        out[(size_t)i * N + n] = ffcu_fc_fp<CONTRACT>(dot, __ldg(w_scale + n), __ldg(bias + n));
+    }
+    if (threadIdx.x == 0) tickets[blockIdx.x] = 0;
 }
 
-template <bool CONTRACT>
-__global__ void fc_finish_kernel(int* __restrict__ scratch, const float* __restrict__ w_scale,
-                                 const float* __restrict__ bias, int total, int N, float* __restrict__ out)
+template <int MAXB>
+static int fc_small_go(dim3 grid, cudaStream_t s, int mode, const int8_t* act, const int8_t* w, const float* w_scale,
+                       const float* bias, int B, int N, int K, int k_per_split, int* scratch, float* out)
 {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= total) return;
-    const int n = i % N;
-    const int dot = scratch[i];
-    scratch[i] = 0;                                        // leave the accumulator clean for the next call
-    out[i] = ffcu_fc_fp<CONTRACT>(dot, __ldg(w_scale + n), __ldg(bias + n));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(FCS_THREADS);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    if (mode) FFCU_CHECK(cudaLaunchKernelEx(&cfg, fc_small_kernel<MAXB, true>, act, w, w_scale, bias, B, N, K, k_per_split, scratch, out));
+    else      FFCU_CHECK(cudaLaunchKernelEx(&cfg, fc_small_kernel<MAXB, false>, act, w, w_scale, bias, B, N, K, k_per_split, scratch, out));
+    return 0;
 }
 
-// scratch: int32 [batch][N], all zero on entry (and again on exit).
+// scratch: FFCU_FC_SMALL_TICKETS + batch * N int32, all zero on entry (and again on exit).
 int ffcu_launch_fc_small(const int8_t* act, const int8_t* w, const float* w_scale, const float* bias,
                          int batch, int N, int K, int mode, int* scratch, float* out, cudaStream_t s)
 {
-    if (batch < 1 || batch > FCS_MAXB || N % FCS_TN != 0 || K % 16 != 0) {
-        ffcu_set_error("small-batch FC needs 1 <= batch <= %d, N %% 8 == 0, K %% 16 == 0", FCS_MAXB);
+    if (batch < 1 || batch > FCS_MAXB || N % FCS_TN != 0 || N / FCS_TN > FFCU_FC_SMALL_TICKETS || K % 16 != 0) {
+        ffcu_set_error("small-batch FC needs 1 <= batch <= %d, N %% 8 == 0, N <= %d, K %% 16 == 0", FCS_MAXB,
+                       FFCU_FC_SMALL_TICKETS * FCS_TN);
         return -1;
     }
     int splits = 16;
     while (splits > 1 && (K % (splits * 16) != 0)) splits >>= 1;
-    dim3 grid(N / FCS_TN, splits);
-    fc_splitk_kernel<<<grid, 256, 0, s>>>(act, w, batch, N, K, K / splits, scratch);
-    const int total = batch * N;
-    if (mode) fc_finish_kernel<true><<<(total + 255) / 256, 256, 0, s>>>(scratch, w_scale, bias, total, N, out);
-    else      fc_finish_kernel<false><<<(total + 255) / 256, 256, 0, s>>>(scratch, w_scale, bias, total, N, out);
-    FFCU_CHECK(cudaGetLastError());
-    return 0;
+    const dim3 grid(N / FCS_TN, splits);
+    const int kps = K / splits;
+    if (batch == 1) return fc_small_go<1>(grid, s, mode, act, w, w_scale, bias, batch, N, K, kps, scratch, out);
+    if (batch == 2) return fc_small_go<2>(grid, s, mode, act, w, w_scale, bias, batch, N, K, kps, scratch, out);
+    if (batch <= 4) return fc_small_go<4>(grid, s, mode, act, w, w_scale, bias, batch, N, K, kps, scratch, out);
+    if (batch <= 8) return fc_small_go<8>(grid, s, mode, act, w, w_scale, bias, batch, N, K, kps, scratch, out);
+    return fc_small_go<16>(grid, s, mode, act, w, w_scale, bias, batch, N, K, kps, scratch, out);
 }
