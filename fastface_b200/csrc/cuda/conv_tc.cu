@@ -1,6 +1,7 @@
 // conv_tc.cu -- host side of the tensor-core convolution: per-layer kernel choice, tile
 // geometry, TMA descriptors, launch.  The kernels live in conv_tc_{generic,ws,pair,k32}.cu.
 #include "conv_tc_common.cuh"
+#include <vector>
 
 // ---------------------------------------------------------------------------
 // host side: tile geometry, tensor maps, launch
@@ -378,6 +379,122 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
     return tc_launch_generic(p->BN, p->KC, mode, epi, p->out_f32, grid, p->smem_bytes, s, g->mapA, p->mapB, prm);
 }
 
+
+// ---------------------------------------------------------------------------
+// Layer chain (conv_tc_chain.cu): plan = the first input's tensor map, the per-layer records in
+// device memory (weights' tensor map, table / buffer pointers) and the shared-memory budget
+// ---------------------------------------------------------------------------
+struct ChainPlan {
+    CUtensorMap mapA;
+    ChainLayer* d_layers;
+    ChainParams prm;
+    int smem_bytes;
+};
+
+// layers[i]: device pointers of layer i (weights, tables, residual, outputs); all layers are 3x3 stride-1
+// pad-1 convolutions C -> C on an H x W map, layer i + 1 reading what layer i writes (its fused BN's
+// output where it has one).  d_in = the first layer's input (one face, NHWC).  NULL when the shape does
+// not fit the kernel (C / 64 column tiles x row tiles of 128 positions must be exactly eight CTAs).
+ChainPlan* ffcu_chain_plan(int H, int W, int C, const int8_t* d_in, const ChainLayerDesc* layers, int n_layers, int device)
+{
+    (void)device;
+    encode_tiled_fn enc = get_encode();
+    if (!enc || n_layers < 2 || C % 128 != 0 || C > TC_MAX_COUT) return nullptr;
+    // pitch: a power of two >= W + 1.  With P = W + 1 the right-hand padding of a row is the next row's
+    // left-hand slot, and the last tap of the last row reads one line past row H: one more (zero) row.
+    int P = 1;
+    while (P < W + 1) P <<= 1;
+    const int rows = H + 2 + (P == W + 1 ? 1 : 0);
+    const int tiles_n = C / CHAIN_BN;
+    const int tiles_m = (H * P + TC_TILE_M - 1) / TC_TILE_M;
+    if (tiles_n * tiles_m != CHAIN_CLUSTER || P > 256 || rows > 256) return nullptr;
+    const int planes = C / 128;
+    const int plane_bytes = P * rows * 128;
+    if (plane_bytes % 1024 != 0) return nullptr;
+    const int fixed = 2 * planes * plane_bytes + CHAIN_BN * 256 + 5 * CHAIN_BN * 4 + 512 /* barriers */ + 1024 /* alignment */;
+    const int stage_bytes = planes * CHAIN_BN * 128;
+    int stages = (232448 - fixed) / stage_bytes;
+    if (stages > CHAIN_MAX_STAGES) stages = CHAIN_MAX_STAGES;
+    if (stages < 2) return nullptr;
+    ChainPlan* p = new ChainPlan();
+    p->d_layers = nullptr;
+    {
+        cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, 1};
+        cuuint64_t strides[3] = {(cuuint64_t)C, (cuuint64_t)C * W, (cuuint64_t)C * W * H};
+        cuuint32_t box[4] = {128, (cuuint32_t)P, (cuuint32_t)rows, 1};
+        cuuint32_t es[4] = {1, 1, 1, 1};
+        CUresult r = enc(&p->mapA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d_in, dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { ffcu_set_error("cuTensorMapEncodeTiled(chain A) failed: %d", (int)r); delete p; return nullptr; }
+    }
+    std::vector<ChainLayer> h((size_t)n_layers);
+    memset(h.data(), 0, h.size() * sizeof(ChainLayer));
+    for (int i = 0; i < n_layers; i++) {
+        const ChainLayerDesc& d = layers[i];
+        cuuint64_t Ktot = (cuuint64_t)9 * C;
+        cuuint64_t dims[4] = {Ktot, (cuuint64_t)C, 1, 1};
+        cuuint64_t strides[3] = {Ktot, Ktot * C, Ktot * C};
+        cuuint32_t box[4] = {128, CHAIN_BN, 1, 1};
+        cuuint32_t es[4] = {1, 1, 1, 1};
+        CUresult r = enc(&h[i].mapB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d.w, dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { ffcu_set_error("cuTensorMapEncodeTiled(chain B) failed: %d", (int)r); delete p; return nullptr; }
+        h[i].w_scale = d.t.w_scale; h[i].bias = d.t.bias; h[i].slope = d.t.slope;
+        h[i].res_scale = d.res ? d.t.res_scale : nullptr; h[i].inv_out = d.t.inv_out;
+        h[i].lut = (d.out2 && d.t.bn_lut) ? d.t.bn_lut : nullptr;
+        h[i].res = (d.res && d.t.res_scale) ? d.res : nullptr;
+        h[i].out = d.out; h[i].out2 = (d.out2 && d.t.bn_lut) ? d.out2 : nullptr;
+    }
+    if (cudaMalloc(&p->d_layers, h.size() * sizeof(ChainLayer)) != cudaSuccess ||
+        cudaMemcpy(p->d_layers, h.data(), h.size() * sizeof(ChainLayer), cudaMemcpyHostToDevice) != cudaSuccess) {
+        ffcu_set_error("layer chain: device allocation or upload failed");
+        cudaFree(p->d_layers); cudaGetLastError(); delete p; return nullptr;
+    }
+    p->prm.layers = p->d_layers; p->prm.n_layers = n_layers;
+    p->prm.H = H; p->prm.W = W; p->prm.P = P; p->prm.C = C;
+    p->prm.planes = planes; p->prm.plane_bytes = plane_bytes; p->prm.tiles_n = tiles_n; p->prm.stages = stages;
+    p->prm.err = nullptr;
+    p->smem_bytes = fixed + stages * stage_bytes;
+    return p;
+}
+
+void ffcu_chain_free(ChainPlan* p)
+{
+    if (!p) return;
+    cudaFree(p->d_layers);
+    delete p;
+}
+
+int ffcu_chain_launch(const ChainPlan* p, int mode, int* d_err, cudaStream_t s)
+{
+    ChainParams prm = p->prm;
+    prm.err = d_err;
+    { static int l2a = -1; if (l2a < 0) { const char* e = getenv("FF_CHAIN_L2"); l2a = e ? atoi(e) : 0; } prm.l2_ahead = l2a; }
+#ifdef FF_TC_TIMING
+    // timing build, $FF_CHAIN_TS=1: the 30th launch of a chain prints CTA 0's per-layer time stamps
+    static unsigned long long* d_ts = nullptr;
+    static int calls = 0;
+    prm.ts = nullptr;
+    if (getenv("FF_CHAIN_TS")) {
+        if (!d_ts) cudaMalloc(&d_ts, 64 * 4 * sizeof(unsigned long long));
+        prm.ts = d_ts;
+        if (++calls == 29 || calls == 30) {
+            int rc = tc_launch_chain(mode, p->smem_bytes, s, p->mapA, prm);
+            cudaStreamSynchronize(s);
+            unsigned long long h[256];
+            cudaMemcpy(h, d_ts, sizeof h, cudaMemcpyDeviceToHost);
+            for (int L = 0; L < prm.n_layers; L++)
+                fprintf(stderr, "chain L%d: in->mma_issued %lld, mma_issued->acc %lld, acc->sent %lld, sent->next_in %lld ns\n", L,
+                        (long long)(h[4 * L + 1] - h[4 * L]), (long long)(h[4 * L + 2] - h[4 * L + 1]), (long long)(h[4 * L + 3] - h[4 * L + 2]),
+                        L + 1 < prm.n_layers ? (long long)(h[4 * L + 4] - h[4 * L + 3]) : 0ll);
+            return rc;
+        }
+    }
+#endif
+    return tc_launch_chain(mode, p->smem_bytes, s, p->mapA, prm);
+}
 
 // ---------------------------------------------------------------------------
 // Tensor-core stem (conv_tc_stem.cu): plan = the weights' tensor map and the launch geometry

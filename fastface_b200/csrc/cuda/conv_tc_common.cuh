@@ -571,10 +571,10 @@ __device__ __forceinline__ void tc_pdl_wait()
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
-// Launch with the programmatic-serialisation attribute (and the CTA-pair cluster shape when
-// pair is set).  $FF_PDL=0 launches the plain way.
+// Launch with the programmatic-serialisation attribute, as clusters of `cluster` CTAs when that is
+// 2 or more (the CTA-pair kernels, the eight-CTA layer chain).  $FF_PDL=0 launches the plain way.
 template <typename... KArgs, typename... Args>
-static int tc_launch_ex(void (*kern)(KArgs...), int grid, int smem, cudaStream_t s, bool pair, Args&&... args)
+static int tc_launch_ex(void (*kern)(KArgs...), int grid, int smem, cudaStream_t s, int cluster, Args&&... args)
 {
     static int pdl = -1;
     if (pdl < 0) { const char* e = getenv("FF_PDL"); pdl = (e && e[0] == '0') ? 0 : 1; }
@@ -585,9 +585,9 @@ static int tc_launch_ex(void (*kern)(KArgs...), int grid, int smem, cudaStream_t
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
     int n = 0;
-    if (pair) {
+    if (cluster >= 2) {
         attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = 2; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1;
+        attr[n].val.clusterDim.x = (unsigned)cluster; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1;
         n++;
     }
     if (pdl) {
@@ -812,6 +812,40 @@ int tc_launch_stem(int mode, int epi, int in_u8, int grid, int smem, cudaStream_
                    const TcParams& prm, const void* in_any, const float* inv3);
 int tc_launch_wsp(int mode, int epi, int grid, int smem, cudaStream_t s,
                   const CUtensorMap& mapA, const CUtensorMap& mapB_half, const TcParams& prm);
+
+// Layer chain (conv_tc_chain.cu)
+#define CHAIN_CLUSTER 8
+#define CHAIN_BN 64
+#define CHAIN_MAX_STAGES 8
+#define CHAIN_EPI_WARPS 16
+#define CHAIN_EPI_THREADS (32 * CHAIN_EPI_WARPS)
+
+struct ChainLayer {                       // one layer of the chain, in global memory (256 bytes, 128-byte aligned)
+    CUtensorMap mapB;                     // weights [Cout][9 * C] K-major, box {128, 64}
+    const float* w_scale; const float* bias; const float* slope; const float* res_scale; const float* inv_out;
+    const int8_t* lut;                    // fused BN byte table [Cout][256], or NULL
+    const int8_t* res;                    // residual (NHWC int8), or NULL
+    int8_t* out;                          // NHWC int8 output
+    int8_t* out2;                         // fused BN second output, or NULL
+    uint8_t pad_[256 - 128 - 9 * 8];
+};
+static_assert(sizeof(ChainLayer) == 256, "ChainLayer layout");
+
+struct ChainParams {
+    const ChainLayer* layers;
+    int n_layers;
+    int H, W, P, C;                       // feature map, pitch in lines, channels (in = out)
+    int planes, plane_bytes;              // C / 128 planes of P * rows lines of 128 bytes
+    int tiles_n;                          // C / 64 column tiles; CHAIN_CLUSTER / tiles_n row tiles
+    int stages;                           // weight ring: one filter tap (planes x 8 KB) per stage
+    int l2_ahead;                         // 1: prefetch each tap of the next layer's weights into L2 a layer ahead
+    int* err;
+#ifdef FF_TC_TIMING
+    unsigned long long* ts;               // timing build: per layer 4 time stamps of CTA 0 (ns)
+#endif
+};
+
+int tc_launch_chain(int mode, int smem, cudaStream_t s, const CUtensorMap& mapA, const ChainParams& prm);
 
 // Flat-pitch weight-stationary pair kernel: activation buffer = guard + box of WSP_BOX_ROWS image rows
 #define WSP_GUARD_BYTES 1024

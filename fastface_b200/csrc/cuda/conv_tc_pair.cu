@@ -196,7 +196,7 @@ static int launch_p(int grid, int smem, cudaStream_t s, const CUtensorMap& mapA,
         FFCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         smem_set[dev & 63] = smem;
     }
-    return tc_launch_ex(kern, grid, smem, s, true, mapA, mapB, prm);
+    return tc_launch_ex(kern, grid, smem, s, 2, mapA, mapB, prm);
 }
 
 template <int BN>

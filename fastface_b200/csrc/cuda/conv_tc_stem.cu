@@ -205,7 +205,7 @@ static int launch_stem(int grid, int smem, cudaStream_t s, const CUtensorMap& ma
         FFCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         smem_set[dev & 63] = smem;
     }
-    return tc_launch_ex(kern, grid, smem, s, false, mapB, prm, in_any, inv3);
+    return tc_launch_ex(kern, grid, smem, s, 1, mapB, prm, in_any, inv3);
 }
 
 int tc_launch_stem(int mode, int epi, int in_u8, int grid, int smem, cudaStream_t s, const CUtensorMap& mapB,

@@ -143,7 +143,7 @@ static int launch_w(int grid, int smem, cudaStream_t s, const CUtensorMap& mapA,
         FFCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         smem_set[dev & 63] = smem;
     }
-    return tc_launch_ex(kern, grid, smem, s, false, mapA, mapB, prm);
+    return tc_launch_ex(kern, grid, smem, s, 1, mapA, mapB, prm);
 }
 
 template <int BN>

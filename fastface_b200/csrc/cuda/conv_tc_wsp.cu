@@ -191,7 +191,7 @@ static int launch_wsp(int grid, int smem, cudaStream_t s, const CUtensorMap& map
         FFCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         smem_set[dev & 63] = smem;
     }
-    return tc_launch_ex(kern, grid, smem, s, true, mapA, mapB, prm);
+    return tc_launch_ex(kern, grid, smem, s, 2, mapA, mapB, prm);
 }
 
 int tc_launch_wsp(int mode, int epi, int grid, int smem, cudaStream_t s,

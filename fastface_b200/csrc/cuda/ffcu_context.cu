@@ -69,6 +69,12 @@ struct ffcu_ctx {
     int graph_max_batch = 1 << 30;
     std::map<long long, cudaGraphExec_t> graphs;
     std::map<long long, int> graph_launches;
+    // Batch 1: runs of same-shape 3x3 stride-1 convolutions (the 14x14 and 7x7 stages) go out as one
+    // launch each (conv_tc_chain.cu).  Found on the first one-face forward; FF_CHAIN=0 disables.
+    struct Chain { size_t first; int count; ChainPlan* plan; };
+    std::vector<Chain> chains;
+    bool chains_built = false;
+    int no_chain = 0;
 };
 
 extern "C" int ffcu_device_count(void)
@@ -125,6 +131,7 @@ extern "C" ffcu_ctx* ffcu_create(int device, int max_batch, int n_bufs, size_t b
     { const char* e = getenv("FF_FC_SMALL"); c->no_fc_small = (e && e[0] == '0') ? 1 : 0; }
     { const char* e = getenv("FF_GRAPH_MAX_BATCH"); if (e && atoi(e) > 0) c->graph_max_batch = atoi(e); }
     { const char* e = getenv("FF_GRAPH"); if (e && e[0] == '0') c->graph_max_batch = 0; }
+    { const char* e = getenv("FF_CHAIN"); c->no_chain = (e && e[0] == '0') ? 1 : 0; }
     if (!ok) {
         ffcu_set_error("device allocation failed on device %d: %s", device, cudaGetErrorString(cudaGetLastError()));
         ffcu_destroy(c);
@@ -143,6 +150,7 @@ extern "C" void ffcu_destroy(ffcu_ctx* c)
     if (c->s_in) cudaStreamSynchronize(c->s_in);
     if (c->s_out) cudaStreamSynchronize(c->s_out);
     for (auto& g : c->graphs) cudaGraphExecDestroy(g.second);
+    for (auto& ch : c->chains) ffcu_chain_free(ch.plan);
     for (auto& L : c->layers) {
         for (TcPlan* q : L.tc_bn) if (q) ffcu_tc_free(q);      // L.tc is one of them
         if (L.stem_tc) ffcu_stem_tc_free(L.stem_tc);
@@ -348,10 +356,66 @@ static int launch_layer(ffcu_ctx* c, size_t k, int n, int32_t* acc_dbg, bool unf
     return -1;
 }
 
+// A layer the chain kernel can take: tensor-core 3x3 stride-1 pad-1 convolution C -> C (C = 256 or 512)
+// with the no-overflow proof, its fused BN (if any) as a byte table.
+static bool chain_eligible(const ffcu_ctx* c, const DevLayer& L)
+{
+    const ffcu_layer& d = L.d;
+    return d.kind == FFCU_CONV && L.tc && !L.skip && !L.fused_stem && !c->force_simt && d.Kh == 3 && d.Kw == 3 &&
+           d.stride == 1 && d.pad == 1 && d.Cin_pad == d.Cout && d.Cin == d.Cout && d.Cout % 128 == 0 && d.H == d.W &&
+           d.Ho == d.H && d.Wo == d.W && L.epi.no_overflow && (d.bn2_dst_buf < 0 || L.bn_lut != nullptr);
+}
+
+static void build_chains(ffcu_ctx* c)
+{
+    c->chains_built = true;
+    if (c->no_chain) return;
+    size_t k = 0;
+    while (k < c->layers.size()) {
+        if (!chain_eligible(c, c->layers[k])) { k++; continue; }
+        size_t e = k + 1;
+        while (e < c->layers.size() && chain_eligible(c, c->layers[e]) && c->layers[e].d.H == c->layers[k].d.H &&
+               c->layers[e].d.Cout == c->layers[k].d.Cout) {
+            const ffcu_layer& prev = c->layers[e - 1].d;
+            const int feeds = prev.bn2_dst_buf >= 0 ? prev.bn2_dst_buf : prev.dst_buf;
+            if (c->layers[e].d.src_buf != feeds) break;
+            e++;
+        }
+        const int count = (int)(e - k);
+        if (count >= 2) {
+            std::vector<ChainLayerDesc> desc((size_t)count);
+            for (int i = 0; i < count; i++) {
+                const DevLayer& L = c->layers[k + i];
+                desc[i].w = L.w; desc[i].t = L.epi;
+                desc[i].res = L.d.res_buf >= 0 ? c->bufs[L.d.res_buf] : nullptr;
+                desc[i].out = c->bufs[L.d.dst_buf];
+                desc[i].out2 = L.d.bn2_dst_buf >= 0 ? c->bufs[L.d.bn2_dst_buf] : nullptr;
+            }
+            const ffcu_layer& d0 = c->layers[k].d;
+            ChainPlan* plan = ffcu_chain_plan(d0.H, d0.W, d0.Cout, c->bufs[d0.src_buf], desc.data(), count, c->device);
+            if (plan) c->chains.push_back({k, count, plan});
+        }
+        k = e;
+    }
+}
+
 static int launch_forward(ffcu_ctx* c, int n)
 {
     int launches = 0;
+    if (n == 1 && !c->chains_built) build_chains(c);
+    size_t next_chain = 0;
     for (size_t k = 0; k < c->layers.size(); k++) {
+        if (n == 1) {
+            while (next_chain < c->chains.size() && c->chains[next_chain].first < k) next_chain++;
+            if (next_chain < c->chains.size() && c->chains[next_chain].first == k) {
+                const ffcu_ctx::Chain& ch = c->chains[next_chain];
+                int rc = ffcu_chain_launch(ch.plan, c->mode, c->d_err, c->stream);
+                if (rc != 0) return rc;
+                launches++;
+                k += (size_t)ch.count - 1;
+                continue;
+            }
+        }
         int rc = launch_layer(c, k, n, nullptr);
         if (rc != 0) return rc;
         const DevLayer& L = c->layers[k];

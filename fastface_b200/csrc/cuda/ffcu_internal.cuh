@@ -159,6 +159,12 @@ int ffcu_launch_fc_small(const int8_t* act, const int8_t* w, const float* w_scal
 // ---------------------------------------------------------------------------
 // Tensor-core implicit GEMM (conv_tc.cu)
 // ---------------------------------------------------------------------------
+// Layer chain (batch 1): consecutive 3x3 stride-1 C -> C convolutions of one feature-map size in one launch.
+struct ChainPlan;
+struct ChainLayerDesc { const int8_t* w; EpiTables t; const int8_t* res; int8_t* out; int8_t* out2; };
+ChainPlan* ffcu_chain_plan(int H, int W, int C, const int8_t* d_in, const ChainLayerDesc* layers, int n_layers, int device);
+void       ffcu_chain_free(ChainPlan* p);
+int        ffcu_chain_launch(const ChainPlan* p, int mode, int* d_err, cudaStream_t s);
 struct TcPlan;   // opaque: tile shape, TMA descriptors, launch geometry for one layer
 int ffcu_stem_weight_k32(const int8_t* d_w, int8_t* d_wk, int Cout, cudaStream_t s);
 // Tensor-core stem (one launch): plan over the repacked weights d_wk [64][32]

@@ -553,6 +553,28 @@ def test_default_context_picks_the_tiling_from_the_call(built_lib, model_root, f
             assert np.array_equal(e.embed(faces[4]), want[4])
 
 
+@pytest.mark.parametrize("mode", [ffo.CONTRACT, ffo.STRICT], ids=["contract", "strict"])
+def test_single_face_layer_chains(built_lib, model_root, ffw4, oracle, monkeypatch, mode):
+    """One face: the 26 same-shape convolutions of the 14x14 stage and the 4 of the 7x7 stage go out as ONE
+    launch each (activations resident in the shared memory of a cluster of eight CTAs).  Same bytes as the
+    per-layer launches (FF_CHAIN=0) and as the oracle: eager call, graph capture and replays, both epilogue
+    orders, several faces through one context."""
+    faces = synth.faces(4, seed=77)
+    want = oracle.forward(faces, mode)
+    counts = {}
+    for flag in ("1", "0"):
+        monkeypatch.setenv("FF_CHAIN", flag)
+        with ff.FastFace(ffw4, cwd=model_root, max_batch=4) as e:
+            e.set_epilogue_mode(mode)
+            for rep in range(3):                 # eager, captured, replayed
+                for i in range(4):
+                    got = e.embed(faces[i])
+                    assert np.array_equal(got, want[i]), f"FF_CHAIN={flag} rep {rep} face {i}"
+            counts[flag] = e.launches_per_forward
+            assert np.array_equal(e.embed_batch(faces), want)      # batch 4: per-layer launches in the same context
+    assert counts["0"] == 54 and counts["1"] == 54 - 26 - 4 + 2, counts
+
+
 def test_bounded_wait_runs_out_and_the_device_stays_usable(built_lib):
     """The timeout path of the tensor-core kernels, exercised without faulting anything: the test hook
     makes the TMA producer of ONE one-CTA launch leave out a K step, and shortens the issuer's wait for
