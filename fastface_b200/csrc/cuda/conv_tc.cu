@@ -404,17 +404,30 @@ ChainPlan* ffcu_chain_plan(int H, int W, int C, const int8_t* d_in, const ChainL
     // left-hand slot, and the last tap of the last row reads one line past row H: one more (zero) row.
     int P = 1;
     while (P < W + 1) P <<= 1;
-    const int rows = H + 2 + (P == W + 1 ? 1 : 0);
     const int tiles_n = C / CHAIN_BN;
     const int tiles_m = (H * P + TC_TILE_M - 1) / TC_TILE_M;
-    if (tiles_n * tiles_m != CHAIN_CLUSTER || P > 256 || rows > 256) return nullptr;
+    // rows a CTA holds: the padded rows its row tile's outputs read (first output row .. last + 2)
+    int rows = 0;
+    for (int t = 0; t < tiles_m; t++) {
+        const int olo = (t * TC_TILE_M) / P;
+        int ohi = (t * TC_TILE_M + TC_TILE_M - 1) / P;
+        if (ohi > H - 1) ohi = H - 1;
+        if (ohi - olo + 3 > rows) rows = ohi - olo + 3;
+    }
+    rows += (P == W + 1 ? 1 : 0);
+    if (tiles_n * tiles_m != CHAIN_CLUSTER || P > 256 || P % 8 != 0 || rows > 256) return nullptr;
     const int planes = C / 128;
     const int plane_bytes = P * rows * 128;
     if (plane_bytes % 1024 != 0) return nullptr;
     const int fixed = 2 * planes * plane_bytes + CHAIN_BN * 256 + 5 * CHAIN_BN * 4 + 512 /* barriers */ + 1024 /* alignment */;
-    const int stage_bytes = planes * CHAIN_BN * 128;
+    // Filter taps per stage of the weight ring (1, or 3 where two such stages fit and $FF_CHAIN_TPS=3 asks for it).
+    int tps = 1;
+    { const char* e = getenv("FF_CHAIN_TPS"); if (e && (atoi(e) == 1 || atoi(e) == 3)) tps = atoi(e); }
+    while (tps > 1 && (232448 - fixed) / (tps * planes * CHAIN_BN * 128) < 2) tps /= 3;
+    const int stage_bytes = tps * planes * CHAIN_BN * 128;
     int stages = (232448 - fixed) / stage_bytes;
     if (stages > CHAIN_MAX_STAGES) stages = CHAIN_MAX_STAGES;
+    stages &= ~1;                                         // two issuers on alternate stages: the ring must be even
     if (stages < 2) return nullptr;
     ChainPlan* p = new ChainPlan();
     p->d_layers = nullptr;
@@ -454,7 +467,7 @@ ChainPlan* ffcu_chain_plan(int H, int W, int C, const int8_t* d_in, const ChainL
     }
     p->prm.layers = p->d_layers; p->prm.n_layers = n_layers;
     p->prm.H = H; p->prm.W = W; p->prm.P = P; p->prm.C = C;
-    p->prm.planes = planes; p->prm.plane_bytes = plane_bytes; p->prm.tiles_n = tiles_n; p->prm.stages = stages;
+    p->prm.planes = planes; p->prm.plane_bytes = plane_bytes; p->prm.win_rows = rows; p->prm.tiles_n = tiles_n; p->prm.stages = stages; p->prm.tps = tps;
     p->prm.err = nullptr;
     p->smem_bytes = fixed + stages * stage_bytes;
     return p;
@@ -471,9 +484,9 @@ int ffcu_chain_launch(const ChainPlan* p, int mode, int* d_err, cudaStream_t s)
 {
     ChainParams prm = p->prm;
     prm.err = d_err;
-    { static int l2a = -1; if (l2a < 0) { const char* e = getenv("FF_CHAIN_L2"); l2a = e ? atoi(e) : 0; } prm.l2_ahead = l2a; }
 #ifdef FF_TC_TIMING
     // timing build, $FF_CHAIN_TS=1: the 30th launch of a chain prints CTA 0's per-layer time stamps
+    { static int dbg = -1; if (dbg < 0) { const char* e = getenv("FF_TC_DBG"); dbg = e ? atoi(e) : 0; } prm.dbg = dbg; }
     static unsigned long long* d_ts = nullptr;
     static int calls = 0;
     prm.ts = nullptr;

@@ -7,7 +7,8 @@
 // activations before its first MMA.  Here the eight CTAs of a cluster take one tile each and keep
 // the WHOLE input tensor of the current layer in their own shared memory, laid out the way a TMA
 // load with 128-byte swizzle would have left it: line (row + 1) * P + (col + 1) of 128 channels per
-// plane, P = pitch in lines, zero lines for the padding.  Filter tap (kh, kw) is then the same buffer
+// plane, P = pitch in lines, zero lines for the padding (each CTA holds the window of rows its row
+// tile reads; the shared memory that saves goes to a deeper weight ring).  Filter tap (kh, kw) is then the same buffer
 // read (kh * P + kw) lines further on (the tensor core applies the swizzle to absolute shared-memory
 // addresses), so the activations need no loads at all.  A CTA's epilogue writes its 128 x 64 result,
 // already requantised to int8 (the fused BN's output where the layer has one), into the NEXT layer's
@@ -37,6 +38,101 @@ __device__ __forceinline__ void chain_bar_sync_epi()
     asm volatile("bar.sync 1, %0;" ::"n"(CHAIN_EPI_THREADS) : "memory");
 }
 
+// Two MMA issuers (warps 1 and 18; each warp loops and waits together, lane 0 issues).  One thread issues an
+// N = 64 MMA about every 70 cycles and pays a few hundred more per pipeline stage, which is slower than the
+// tensor core retires them (51 cycles): the issuers take alternate stages of the weight ring, each
+// accumulating into its own 64 TMEM columns; the epilogue adds the two (integer adds commute).  The ring is
+// even, so a slot is always the same issuer's (a parity wait cannot tell "this fill" from "two fills ago",
+// and with an odd ring the fill in between would be the other issuer's to consume).  PLANES (C / 128) and
+// TPS (filter taps per stage) are compile-time so that a stage's MMAs are one straight-line block, and the
+// ring / layer bookkeeping is carried forward by additions only.
+template <int PLANES, int TPS>
+__device__ __forceinline__ void chain_issuer_role(const ChainParams& p, ChainShared* sh, int me, int lane, uint32_t rank,
+                                                  uint32_t tmem_base, uint32_t s_a_addr, uint32_t s_b_addr,
+                                                  int tile_line0, uint32_t in_bytes)
+{
+    (void)rank;
+    constexpr uint32_t IDESC = idesc_i8(CHAIN_BN);
+    constexpr int B_BLOCK = CHAIN_BN * 128;
+    constexpr int S = 9 / TPS;                              // stages per layer (odd)
+    constexpr int STAGE_BYTES = TPS * PLANES * B_BLOCK;
+    volatile int* abort_flag = &sh->abort_flag;
+    const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
+    const int stages = p.stages, n_layers = p.n_layers;
+    const uint32_t leader = (lane == 0) ? 1u : 0u;
+    const uint32_t d_tmem = tmem_base + (uint32_t)(me * CHAIN_BN);
+    const uint64_t db_base = smem_desc<128>(s_b_addr);
+    const uint32_t a_buf_bytes = (uint32_t)(PLANES * p.plane_bytes);
+    const uint64_t dplane = (uint64_t)(p.plane_bytes >> 4);
+    const uint32_t P8 = (uint32_t)(p.P * 8);                // one padded row, in descriptor units (16 bytes)
+    uint64_t da_layer = 0;                                  // descriptor of the tile's first line in the layer's buffer
+    uint32_t ready = 0;                                     // answer of the early test for this issuer's next stage
+    uint32_t first = 0;                                     // non-zero after this issuer's first MMA of the layer
+    int stage = me; uint32_t phase = 0;                     // ring slot of this issuer's current stage
+    int L = 0, st = me;                                     // layer, stage within the layer
+    bool new_layer = true;
+    bool ok = true;
+#pragma unroll 1
+    while (L < n_layers) {
+        if (new_layer) {
+            new_layer = false;
+            const int buf = L & 1;
+            // arm the barrier of the buffer the peers fill during this layer (bytes that land before this
+            // only drive the count negative for a moment: the phase cannot complete before this arrival)
+            if (me == 0 && L + 1 < n_layers && lane == 0) mbar_expect_tx(smem_u32(&sh->act_full[buf ^ 1]), in_bytes);
+            if (L == 0) ok = mbar_wait(smem_u32(&sh->a0_full), 0, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
+            else {
+                ok = mbar_wait_cluster(smem_u32(&sh->act_full[buf]), (uint32_t)((L - 1) >> 1) & 1, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
+                if (ok) ok = mbar_wait(smem_u32(&sh->acc_empty), (uint32_t)(L - 1) & 1, abort_flag, p.err, FFCU_ERR_TMEM_TIMEOUT);
+            }
+            if (!ok) break;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_after();
+#ifdef FF_TC_TIMING
+            if (p.ts && rank == 0 && lane == 0 && me == 0) p.ts[4 * L + 0] = globaltimer_ns();      // input complete
+#endif
+            da_layer = smem_desc<128>(s_a_addr + (uint32_t)buf * a_buf_bytes + (uint32_t)(tile_line0 * 128));
+            first = 0;
+        }
+        if (!ready) {
+            ok = mbar_wait(full0 + stage * 8, phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
+            if (!ok) break;
+        }
+        // this issuer's next stage: test its barrier now, use the answer next round (a test takes a few hundred cycles)
+        int ns = stage + 2; uint32_t np = phase;
+        if (ns >= stages) { ns -= stages; np ^= 1; }
+        ready = mbar_test(full0 + ns * 8, np);
+        tc_fence_after();
+        {
+            // first tap of the stage: (kh, kw) = (st, 0) when a stage is a filter row, (st / 3, st % 3) otherwise
+            const int kh = (TPS == 3) ? st : st / 3;
+            const int kw0 = (TPS == 3) ? 0 : st - 3 * kh;
+            const uint64_t da0 = da_layer + (uint64_t)((uint32_t)kh * P8 + (uint32_t)kw0 * 8u);
+            const uint64_t db0 = db_base + (uint64_t)((uint32_t)(stage * STAGE_BYTES) >> 4);
+#pragma unroll
+            for (int g = 0; g < TPS; g++)
+#pragma unroll
+                for (int pl = 0; pl < PLANES; pl++)
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        umma_i8_w(leader, d_tmem, da0 + (uint64_t)(g * 8 + 2 * k) + (uint64_t)pl * dplane,
+                                  db0 + (uint64_t)(((g * PLANES + pl) * B_BLOCK >> 4) + 2 * k), IDESC,
+                                  (g | pl | k) ? 1u : first);
+            first = 1;
+        }
+        umma_commit_w(leader, empty0 + stage * 8);
+        stage = ns; phase = np;
+        st += 2;
+        if (st >= S) {                                      // that was this issuer's last stage of the layer
+            umma_commit_w(leader, smem_u32(&sh->acc_full));
+#ifdef FF_TC_TIMING
+            if (p.ts && rank == 0 && lane == 0 && st - 2 == S - 1) p.ts[4 * L + 1] = globaltimer_ns();   // last MMA issued
+#endif
+            st -= S; L++; new_layer = true;
+        }
+    }
+}
+
 template <bool CONTRACT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_chain_kernel(const __grid_constant__ CUtensorMap mapA, const ChainParams p)
@@ -44,7 +140,7 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap mapA, const ChainParams p)
     tc_pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    constexpr uint32_t TMEM_COLS = 64;
+    constexpr uint32_t TMEM_COLS = 2 * CHAIN_BN;          // one accumulator per MMA issuer
     constexpr uint32_t IDESC = idesc_i8(CHAIN_BN);
     constexpr int B_BLOCK = CHAIN_BN * 128;               // one plane of one tap: 64 output channels x 128 input channels
 
@@ -54,9 +150,13 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap mapA, const ChainParams p)
     const int tile_m = (int)rank / p.tiles_n;
     const int tile_n = (int)rank % p.tiles_n;
     const int a_buf_bytes = p.planes * p.plane_bytes;
-    const int stage_bytes = p.planes * B_BLOCK;
+    const int stage_bytes = p.tps * p.planes * B_BLOCK;
     // Row tile t produces output rows [t * 128 / P, (t * 128 + 127) / P] (clipped to the map) and reads the
     // input rows one above and one below: a CTA receives only those rows of every layer's result.
+    // A CTA keeps only the lines its row tile reads: a window of p.win_rows padded rows starting at the
+    // first output row of its tile (padded row index = output row + kh).  base_line(t) is a multiple of 8
+    // lines, so a line's swizzle phase is the same in every window.
+    auto base_line = [&](int t) { return ((t * TC_TILE_M) / p.P) * p.P; };
     auto rows_lo = [&](int t) { return (t * TC_TILE_M) / p.P - 1; };
     auto rows_hi = [&](int t) { const int h = (t * TC_TILE_M + TC_TILE_M - 1) / p.P; return (h < p.H - 1 ? h : p.H - 1) + 1; };
     uint8_t* s_a = smem;                                  // [2][planes][plane_bytes]
@@ -70,7 +170,7 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap mapA, const ChainParams p)
         mbar_init(smem_u32(&sh->act_full[0]), 1);          // one arming arrival; the rest is byte counting
         mbar_init(smem_u32(&sh->act_full[1]), 1);
         mbar_init(smem_u32(&sh->a0_full), 1);
-        mbar_init(smem_u32(&sh->acc_full), 1);
+        mbar_init(smem_u32(&sh->acc_full), 2);              // both issuers' MMAs of the layer are complete
         mbar_init(smem_u32(&sh->acc_empty), CHAIN_EPI_WARPS);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -90,14 +190,17 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap mapA, const ChainParams p)
     const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
 
     if (warp == 0) {
-        // Weight producer.  One stage = one filter tap of this CTA's 64 output channels (planes boxes of
-        // 8 KB); the ring runs ahead across layers.  The first layer's activations are requested once the
+        // Weight producer.  One stage = p.tps filter taps of this CTA's 64 output channels (planes boxes of
+        // 8 KB each); the ring runs ahead across layers.  The first layer's activations are requested once the
         // ring is full of weights: they are the only thing that depends on the previous kernel.
-        const int total_steps = p.n_layers * 9;
+        const int G = p.tps;                                  // filter taps per stage
+        const int total_steps = p.n_layers * (9 / G);
         const int pre = p.stages < total_steps ? p.stages : total_steps;
         int stage = 0; uint32_t phase = 0;
         bool ok = true;
         int L = 0, tap = 0;
+        const int my_g = lane / p.planes, my_pl = lane - my_g * p.planes;   // this lane's box within a stage
+        const bool loader = lane < G * p.planes;
 #pragma unroll 1
         for (int gs = 0; gs < total_steps && ok; gs++) {
             if (gs == pre) {
@@ -107,92 +210,44 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap mapA, const ChainParams p)
                 // both buffers: the copy into the second one only puts the zero lines of the padding in place
                 if (lane < 2 * p.planes)
                     tma_load_4d(smem_u32(s_a) + lane * p.plane_bytes, &mapA, smem_u32(&sh->a0_full),
-                                (lane % p.planes) * 128, -1, -1, 0);
+                                (lane % p.planes) * 128, -1, (tile_m * TC_TILE_M) / p.P - 1, 0);
             }
             ok = mbar_wait(empty0 + stage * 8, phase ^ 1, abort_flag, p.err, FFCU_ERR_EMPTY_TIMEOUT);
             if (!ok) break;
+#ifdef FF_TC_TIMING
+            if (p.dbg & 1) {
+                if (lane == 0) mbar_arrive(full0 + stage * 8);
+                if (++stage == p.stages) { stage = 0; phase ^= 1; }
+                tap += G;
+                if (tap == 9) { tap = 0; L++; }
+                continue;
+            }
+#endif
             if (lane == 0) mbar_expect_tx(full0 + stage * 8, stage_bytes);
             __syncwarp();
-            if (tap == 0 && lane < p.planes) {
+            if (tap == 0 && loader) {
                 // the layer's tensor map sits in global memory, put there by a host copy: order this thread's
                 // use of it (through the tensor-map proxy) after that write
                 asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(&p.layers[L].mapB) : "memory");
             }
-            if (lane < p.planes)
+            if (loader)
                 tma_load_4d(smem_u32(s_b) + stage * stage_bytes + lane * B_BLOCK, &p.layers[L].mapB, full0 + stage * 8,
-                            tap * p.C + lane * 128, tile_n * CHAIN_BN, 0, 0);
-            if (p.l2_ahead && L + 1 < p.n_layers && lane < p.planes) {
-                // the same tap of the NEXT layer's weights: into L2 now, so that its TMA load a layer later is a hit
-                asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
-                             ::"l"(&p.layers[L + 1].mapB), "r"(tap * p.C + lane * 128), "r"(tile_n * CHAIN_BN), "r"(0), "r"(0) : "memory");
-            }
+                            (tap + my_g) * p.C + my_pl * 128, tile_n * CHAIN_BN, 0, 0);
             if (++stage == p.stages) { stage = 0; phase ^= 1; }
-            if (++tap == 9) { tap = 0; L++; }
+            tap += G;
+            if (tap == 9) { tap = 0; L++; }
         }
-    } else if (warp == 1) {
-        // MMA issuer: the warp loops and waits together, lane 0 issues
-        int stage = 0; uint32_t phase = 0;
-        bool ok = true;
-        const uint32_t leader = (lane == 0) ? 1u : 0u;
-        const uint64_t da_base = smem_desc<128>(smem_u32(s_a));
-        const uint64_t db_base = smem_desc<128>(smem_u32(s_b));
-        uint32_t ready = 0;                                 // answer of the early test for the upcoming stage
-        // bytes of one layer's result this CTA receives: its rows x W positions x C channels
+    } else if (warp == 1 || warp == TC_ISSUER2_WARP) {
+        const int me = (warp == 1) ? 0 : 1;
+        const int tile_line0 = tile_m * TC_TILE_M - base_line(tile_m);
         const int my_lo = rows_lo(tile_m) < 0 ? 0 : rows_lo(tile_m);
         const int my_hi = rows_hi(tile_m) > p.H - 1 ? p.H - 1 : rows_hi(tile_m);
         const uint32_t in_bytes = (uint32_t)((my_hi - my_lo + 1) * p.W * p.C);
-#pragma unroll 1
-        for (int L = 0; L < p.n_layers && ok; L++) {
-            const int buf = L & 1;
-            // arm the barrier of the buffer the peers fill during this layer (bytes that land before this
-            // only drive the count negative for a moment: the phase cannot complete before this arrival)
-            if (L + 1 < p.n_layers && lane == 0) mbar_expect_tx(smem_u32(&sh->act_full[buf ^ 1]), in_bytes);
-            if (L == 0) ok = mbar_wait(smem_u32(&sh->a0_full), 0, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
-            else {
-                ok = mbar_wait_cluster(smem_u32(&sh->act_full[buf]), (uint32_t)((L - 1) >> 1) & 1, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
-                if (ok) ok = mbar_wait(smem_u32(&sh->acc_empty), (uint32_t)(L - 1) & 1, abort_flag, p.err, FFCU_ERR_TMEM_TIMEOUT);
-            }
-            if (!ok) break;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            tc_fence_after();
-#ifdef FF_TC_TIMING
-            if (p.ts && rank == 0 && lane == 0) p.ts[4 * L + 0] = globaltimer_ns();      // input complete
-#endif
-            const uint32_t a_off0 = (uint32_t)(buf * a_buf_bytes + tile_m * TC_TILE_M * 128);
-            uint64_t da_row = da_base + (uint64_t)(a_off0 >> 4);   // descriptor of tap (kh, 0), plane 0
-            int kw = 0;
-#pragma unroll 1
-            for (int tap = 0; tap < 9; tap++) {
-                if (!ready) {
-                    ok = mbar_wait(full0 + stage * 8, phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT);
-                    if (!ok) break;
-                }
-                // test the next stage now, use the answer next round (a barrier test takes a few hundred cycles)
-                int ns = stage + 1; uint32_t np = phase;
-                if (ns == p.stages) { ns = 0; np ^= 1; }
-                ready = mbar_test(full0 + ns * 8, np);
-                tc_fence_after();
-                uint64_t da = da_row + (uint64_t)(kw * 8);          // one line = 128 bytes = 8 descriptor units
-#ifdef FF_TC_TIMING
-                if (p.l2_ahead & 2) da = da_row;                    // timing experiment: every tap from an atom-aligned start (wrong results)
-#endif
-                uint64_t db = db_base + (uint64_t)((uint32_t)(stage * stage_bytes) >> 4);
-#pragma unroll 1
-                for (int pl = 0; pl < p.planes; pl++, da += (uint64_t)(p.plane_bytes >> 4), db += (uint64_t)(B_BLOCK >> 4)) {
-#pragma unroll
-                    for (int k = 0; k < 4; k++)
-                        umma_i8_w(leader, tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, (tap | pl | k) ? 1u : 0u);
-                }
-                umma_commit_w(leader, empty0 + stage * 8);
-                stage = ns; phase = np;
-                if (++kw == 3) { kw = 0; da_row += (uint64_t)(p.P * 8); }
-            }
-            if (ok) umma_commit_w(leader, smem_u32(&sh->acc_full));
-#ifdef FF_TC_TIMING
-            if (p.ts && rank == 0 && lane == 0) p.ts[4 * L + 1] = globaltimer_ns();      // last MMA issued
-#endif
-        }
-    } else if (warp < TC_ISSUER2_WARP) {
+        if (p.planes == 2 && p.tps == 3)      chain_issuer_role<2, 3>(p, sh, me, lane, rank, tmem_base, smem_u32(s_a), smem_u32(s_b), tile_line0, in_bytes);
+        else if (p.planes == 2)               chain_issuer_role<2, 1>(p, sh, me, lane, rank, tmem_base, smem_u32(s_a), smem_u32(s_b), tile_line0, in_bytes);
+        else if (p.tps == 3)                  chain_issuer_role<4, 3>(p, sh, me, lane, rank, tmem_base, smem_u32(s_a), smem_u32(s_b), tile_line0, in_bytes);
+        else                                  chain_issuer_role<4, 1>(p, sh, me, lane, rank, tmem_base, smem_u32(s_a), smem_u32(s_b), tile_line0, in_bytes);
+    } else {
         // Epilogue: sixteen warps on the CTA's one tile, warp = (TMEM lane quarter, 16-channel group).
         const int q = warp & 3;
         const int cg = (warp - 2) >> 2;
@@ -262,8 +317,13 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap mapA, const ChainParams p)
 #ifdef FF_TC_TIMING
             if (p.ts && rank == 0 && warp == 2 && lane == 0) p.ts[4 * L + 2] = globaltimer_ns();   // accumulator complete
 #endif
-            int v[16];
-            tmem_ld16(taddr, v);
+            int v[16], v2[16];
+            tmem_ld16_issue(taddr, v);
+            tmem_ld16_issue(taddr + CHAIN_BN, v2);                 // the second issuer's partial sums
+            tmem_ld_wait(v);
+            tmem_ld_wait(v2);
+#pragma unroll
+            for (int i = 0; i < 16; i++) v[i] += v2[i];
             int ow[4], ow2[4];
 #pragma unroll
             for (int g = 0; g < 4; g++) {
@@ -300,7 +360,8 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap mapA, const ChainParams p)
                 for (uint32_t rk = 0; rk < CHAIN_CLUSTER; rk++)
                     if (dest_mask & (1u << rk))
                         asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
-                                     ::"r"(map_to_cta(dst, rk)), "r"(n0), "r"(n1), "r"(n2), "r"(n3), "r"(map_to_cta(bar, rk)) : "memory");
+                                     ::"r"(map_to_cta(dst - (uint32_t)(base_line((int)rk / p.tiles_n) * 128), rk)),
+                                       "r"(n0), "r"(n1), "r"(n2), "r"(n3), "r"(map_to_cta(bar, rk)) : "memory");
             }
             tc_fence_before();                                     // this warp's TMEM reads are complete
             __syncwarp();

@@ -835,13 +835,15 @@ struct ChainParams {
     const ChainLayer* layers;
     int n_layers;
     int H, W, P, C;                       // feature map, pitch in lines, channels (in = out)
-    int planes, plane_bytes;              // C / 128 planes of P * rows lines of 128 bytes
+    int planes, plane_bytes;              // C / 128 planes of P * win_rows lines of 128 bytes
+    int win_rows;                         // padded rows a CTA holds (the rows its row tile reads)
     int tiles_n;                          // C / 64 column tiles; CHAIN_CLUSTER / tiles_n row tiles
-    int stages;                           // weight ring: one filter tap (planes x 8 KB) per stage
-    int l2_ahead;                         // 1: prefetch each tap of the next layer's weights into L2 a layer ahead
+    int stages;                           // weight ring
+    int tps;                              // filter taps per stage (1, 3 or 9), planes x 8 KB each
     int* err;
 #ifdef FF_TC_TIMING
     unsigned long long* ts;               // timing build: per layer 4 time stamps of CTA 0 (ns)
+    int dbg;                              // timing build: bit 0 = skip the weight loads (wrong results)
 #endif
 };
 
