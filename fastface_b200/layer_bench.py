@@ -10,6 +10,14 @@ weights int8 ~ round(N(0, 40)) clipped to +-127, per-channel fp32 scales and bia
 per launch of the tensor-core implicit GEMM, its int8 output's checksum and, with --winograd,
 the exact-integer Winograd F(2,3) kernel on the same tensors (checked equal to 4 x the direct
 int32 accumulators) with its time beside it.
+
+    python -m fastface_b200.layer_bench --forward [--batch 1] [--iters 10]
+
+runs the whole network instead (seeded synthetic model, seeded faces) through the public
+embed / embed_batch call --iters times and prints the launch count, the device time per forward and
+the wall-clock latency per call; at batch 1 the launch list is the small-batch one (layer chains,
+one-launch FC), so this is also the command the profiler captures those kernels under.  With
+--cos-sim N it ends with one N x N similarity matrix of the last embeddings.
 """
 from __future__ import annotations
 
@@ -87,6 +95,33 @@ def run(name: str, batch: int, iters: int, residual: bool, winograd: bool, impl:
     return line
 
 
+def run_forward(batch: int, iters: int, cos_sim: int) -> dict:
+    import tempfile
+    import time
+
+    from fastface_b200 import synth
+
+    root = tempfile.mkdtemp(prefix="ff_layer_bench_")
+    ffw4 = synth.materialize(root, 0)
+    faces = synth.faces(batch, seed=1)
+    with ff.FastFace(ffw4, cwd=root, max_batch=batch) as e:
+        out = None
+        wall = []
+        for _ in range(max(iters, 1)):
+            t0 = time.perf_counter()
+            out = e.embed(faces[0])[None, :] if batch == 1 else e.embed_batch(faces)
+            wall.append((time.perf_counter() - t0) * 1e3)
+        dev_ms = e.bench_resident(faces, max(iters, 1)) / max(iters, 1)
+        line = {"forward": True, "batch": batch, "launches_per_forward": e.launches_per_forward,
+                "device_ms_per_forward": round(dev_ms, 5), "call_ms_p50": round(sorted(wall)[len(wall) // 2], 5),
+                "emb_crc32": f"{zlib.crc32(np.ascontiguousarray(out).tobytes()):08x}", "iters": iters}
+        if cos_sim > 0:
+            q = np.ascontiguousarray(np.resize(out, (cos_sim, out.shape[1])).astype(np.float32))
+            m = e.cos_sim_matrix(q, q)
+            line["cos_sim_matrix"] = {"n": cos_sim, "diag_min": float(np.min(np.diag(m)))}
+    return line
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default="conv56", choices=sorted(CASES))
@@ -95,7 +130,12 @@ def main():
     ap.add_argument("--residual", action="store_true", help="residual add + fused BN second output instead of PReLU")
     ap.add_argument("--winograd", action="store_true", help="also run the integer Winograd F(2,3) kernel on the same tensors")
     ap.add_argument("--impl", default="tc", choices=["tc", "simt"])
+    ap.add_argument("--forward", action="store_true", help="time the whole network through embed / embed_batch instead of one layer")
+    ap.add_argument("--cos-sim", type=int, default=0, help="with --forward: finish with an N x N similarity matrix")
     a = ap.parse_args()
+    if a.forward:
+        print(json.dumps(run_forward(a.batch, a.iters, a.cos_sim)), flush=True)
+        return
     print(json.dumps(run(a.case, a.batch, a.iters, a.residual, a.winograd, a.impl)), flush=True)
 
 

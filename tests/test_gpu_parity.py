@@ -342,6 +342,15 @@ def test_layer_microbench_reports_both_kernels(built_lib):
     assert line["ms_per_launch"] > 0 and line["winograd_f23"]["ms_per_launch"] > 0
 
 
+def test_network_microbench_single_face(built_lib):
+    """`layer_bench --forward` at batch 1: the small-batch launch list (stem, layer chains, one-launch FC) through
+    the public call; the similarity matrix of an embedding with itself has a unit diagonal."""
+    from fastface_b200 import layer_bench
+    line = layer_bench.run_forward(1, 3, 4)
+    assert line["launches_per_forward"] == 26 and line["device_ms_per_forward"] > 0
+    assert abs(line["cos_sim_matrix"]["diag_min"] - 1.0) < 1e-6
+
+
 @pytest.mark.parametrize("case", [c for c in BIG_LAYER_CASES if (c[2], c[3], c[4], c[6]) == (28, 128, 128, 1)] + [LAYER_CASES[4]],
                          ids=lambda c: c[0])
 def test_128_channel_layers_on_the_per_tap_pair_kernel(built_lib, case, monkeypatch):
