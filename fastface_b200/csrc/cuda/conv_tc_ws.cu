@@ -84,11 +84,11 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             const uint64_t dw = smem_desc<KC>(smem_u32(s_w));
             const uint32_t leader = (lane == 0) ? 1u : 0u;
             uint32_t ready_a = 0, ready_f = 0;           // answers of the early tests for this issuer's next tile
-            for (int tile = blockIdx.x + me * gridDim.x, local = me; tile < p.total_tiles && ok; tile += 2 * gridDim.x, local += 2) {
-                const int stage = local % p.stages;
-                const uint32_t phase = (uint32_t)(local / p.stages) & 1;
-                const int a = local % TC_NACC(BN);
-                const uint32_t aphase = (uint32_t)(local / TC_NACC(BN)) & 1;
+            // ring positions carried forward by additions (both rings are even: +2 keeps this issuer on its own slots)
+            const int stages = p.stages;
+            int stage = me; uint32_t phase = 0;
+            int a = me; uint32_t aphase = 0;
+            for (int tile = blockIdx.x + me * gridDim.x; tile < p.total_tiles && ok; tile += 2 * gridDim.x) {
                 if (!ready_a) {
                     ok = mbar_wait(smem_u32(&sh->acc_empty[a]), aphase ^ 1, abort_flag, p.err, FFCU_ERR_TMEM_TIMEOUT);
                     if (!ok) break;
@@ -97,11 +97,13 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     ok = mbar_wait(smem_u32(&sh->full[stage]), phase, abort_flag, p.err, FFCU_ERR_TMA_TIMEOUT, p.full_wait);
                     if (!ok) break;
                 }
-                {   // test the barriers of this issuer's next tile now, use the answers next round
-                    const int nl = local + 2;
-                    ready_a = mbar_test(smem_u32(&sh->acc_empty[nl % TC_NACC(BN)]), ((uint32_t)(nl / TC_NACC(BN)) & 1) ^ 1);
-                    ready_f = mbar_test(smem_u32(&sh->full[nl % p.stages]), (uint32_t)(nl / p.stages) & 1);
-                }
+                int ns = stage + 2; uint32_t np = phase;
+                if (ns >= stages) { ns -= stages; np ^= 1; }
+                int na = a + 2; uint32_t nap = aphase;
+                if (na >= TC_NACC(BN)) { na -= TC_NACC(BN); nap ^= 1; }
+                // test the barriers of this issuer's next tile now, use the answers next round
+                ready_a = mbar_test(smem_u32(&sh->acc_empty[na]), nap ^ 1);
+                ready_f = mbar_test(smem_u32(&sh->full[ns]), np);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
                 const uint64_t da0 = smem_desc_sbo<KC>(smem_u32(s_a + (size_t)stage * WS_A_BYTES), WS_PITCH * 64);
@@ -121,6 +123,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 umma_commit_w(leader, smem_u32(&sh->empty[stage]));
                 umma_commit_w(leader, smem_u32(&sh->acc_full[a]));
                 }
+                stage = ns; phase = np; a = na; aphase = nap;
             }
         }
     } else {

@@ -117,11 +117,13 @@ conv_wsp_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             uint32_t ready_a = 0, ready_f = 0;
             TileWalk wk;
             walk_init(wk, p, (pair_id + me * n_pairs) * 2, n_pairs * 4);
-            for (int tile = pair_id + me * n_pairs, local = me; tile < total && ok; tile += 2 * n_pairs, local += 2, walk_next(wk, p)) {
-                const int stage = local % p.stages;
-                const uint32_t phase = (uint32_t)(local / p.stages) & 1;
-                const int a = local % TC_NACC(BN);
-                const uint32_t aphase = (uint32_t)(local / TC_NACC(BN)) & 1;
+            // ring positions carried forward by additions (both rings are even: +2 keeps this issuer on its own slots)
+            const int stages = p.stages;
+            int stage = me; uint32_t phase = 0;
+            int a = me; uint32_t aphase = 0;
+            int ns = 0, na = 0; uint32_t np = 0, nap = 0;
+            for (int tile = pair_id + me * n_pairs; tile < total && ok;
+                 tile += 2 * n_pairs, walk_next(wk, p), stage = ns, phase = np, a = na, aphase = nap) {
                 if (!ready_a) {
                     ok = mbar_wait_cluster(smem_u32(&sh->acc_empty[a]), aphase ^ 1, abort_flag, p.err, FFCU_ERR_TMEM_TIMEOUT);
                     if (!ok) break;
@@ -131,9 +133,12 @@ conv_wsp_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                     if (!ok) break;
                 }
                 {   // test the barriers of this issuer's next tile now, use the answers next round
-                    const int nl = local + 2;
-                    ready_a = mbar_test_cluster(smem_u32(&sh->acc_empty[nl % TC_NACC(BN)]), ((uint32_t)(nl / TC_NACC(BN)) & 1) ^ 1);
-                    ready_f = mbar_test_cluster(smem_u32(&sh->full[nl % p.stages]), (uint32_t)(nl / p.stages) & 1);
+                    ns = stage + 2; np = phase;
+                    if (ns >= stages) { ns -= stages; np ^= 1; }
+                    na = a + 2; nap = aphase;
+                    if (na >= TC_NACC(BN)) { na -= TC_NACC(BN); nap ^= 1; }
+                    ready_a = mbar_test_cluster(smem_u32(&sh->acc_empty[na]), nap ^ 1);
+                    ready_f = mbar_test_cluster(smem_u32(&sh->full[ns]), np);
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
