@@ -290,6 +290,9 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
     // the specialised variants carry no accumulator dump, no out-of-range conversion check and no
     // arithmetic fused BN: a launch that needs one of those takes the general variant
     if (!p->out_f32 && (acc_out || !t.no_overflow || (has_bn2 && !p->lut_bytes))) epi = EPI_RUNTIME;
+    // the specialised variants of the 64-input-channel kernels convert the accumulator without the conversion
+    // unit, which is exact below 2^22: a layer without that bound takes the general variant too
+    if (!p->out_f32 && p->KC == 64 && !t.acc22) epi = EPI_RUNTIME;
     if (p->ws) {
         TcParams prm = {};
         prm.t = t; prm.res = res; prm.acc_out = acc_out; prm.out = out; prm.err = d_err;
@@ -549,7 +552,7 @@ int ffcu_stem_fused_launch(const StemTcPlan* p, const void* in_any, int in_u8, c
     int epi = EPI_RUNTIME;
     if (has_slope && has_bn2) epi = EPI_SLOPE_BN;
     else if (has_slope && !out_bn2) epi = EPI_SLOPE;
-    if (!t.no_overflow) epi = EPI_RUNTIME;
+    if (!t.no_overflow || !t.acc22) epi = EPI_RUNTIME;
     TcParams prm = {};
     prm.t = t; prm.res = nullptr; prm.acc_out = nullptr; prm.out = out; prm.err = d_err;
     prm.out2 = has_bn2 ? out_bn2 : nullptr;

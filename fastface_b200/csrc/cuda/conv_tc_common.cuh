@@ -489,7 +489,7 @@ __device__ __forceinline__ uint32_t tc_lut_byte(uint32_t w, uint32_t lut_base)
 // Sixteen columns of one accumulator row: v[16] int32 at channels cb .. cb + 15 -> four packed
 // int8 words (and four more for the fused BN's output).  CI = 0 / 1: first or second chunk of the
 // pair whose 32 table rows start at shared-memory address lut_pr.
-template <bool CONTRACT, int EPI, bool CHECK, int CI>
+template <bool CONTRACT, int EPI, bool CHECK, int CI, bool ACC22 = false>
 __device__ __forceinline__ void tc_epilogue16(const TcParams& p, const float* tab, uint32_t lut_pr,
                                               const int (&v)[16], const int* rw, int cb,
                                               bool rt_res, bool rt_slope, bool rt_bn2, int (&ow)[4], int (&ow2)[4])
@@ -504,11 +504,17 @@ __device__ __forceinline__ void tc_epilogue16(const TcParams& p, const float* ta
         const float4 sl = *(const float4*)&tab[2 * TC_MAX_COUT + cb + 4 * g];
         const float4 rs = *(const float4*)&tab[3 * TC_MAX_COUT + cb + 4 * g];
         const float4 iv = *(const float4*)&tab[4 * TC_MAX_COUT + cb + 4 * g];
-        const int r = has_res ? rw[g] : 0;
-        const float f0 = ffcu_conv_fp<CONTRACT>(v[4 * g + 0], ws.x, bi.x, has_res, (int)(int8_t)(r & 0xff), rs.x, has_slope, sl.x);
-        const float f1 = ffcu_conv_fp<CONTRACT>(v[4 * g + 1], ws.y, bi.y, has_res, (int)(int8_t)((r >> 8) & 0xff), rs.y, has_slope, sl.y);
-        const float f2 = ffcu_conv_fp<CONTRACT>(v[4 * g + 2], ws.z, bi.z, has_res, (int)(int8_t)((r >> 16) & 0xff), rs.z, has_slope, sl.z);
-        const float f3 = ffcu_conv_fp<CONTRACT>(v[4 * g + 3], ws.w, bi.w, has_res, r >> 24, rs.w, has_slope, sl.w);
+        // int -> float: the residual's bytes never need the conversion unit (ffcu_byte2f is exact for every byte);
+        // the accumulator does not either where the launcher has the layer's 22-bit bound (ACC22)
+        const uint32_t rx = has_res ? ((uint32_t)rw[g] ^ 0x80808080u) : 0x80808080u;
+        const float a0 = ACC22 ? ffcu_i2f_22(v[4 * g + 0]) : __int2float_rn(v[4 * g + 0]);
+        const float a1 = ACC22 ? ffcu_i2f_22(v[4 * g + 1]) : __int2float_rn(v[4 * g + 1]);
+        const float a2 = ACC22 ? ffcu_i2f_22(v[4 * g + 2]) : __int2float_rn(v[4 * g + 2]);
+        const float a3 = ACC22 ? ffcu_i2f_22(v[4 * g + 3]) : __int2float_rn(v[4 * g + 3]);
+        const float f0 = ffcu_conv_fp_f<CONTRACT>(a0, ws.x, bi.x, has_res, ffcu_byte2f<0>(rx), rs.x, has_slope, sl.x);
+        const float f1 = ffcu_conv_fp_f<CONTRACT>(a1, ws.y, bi.y, has_res, ffcu_byte2f<1>(rx), rs.y, has_slope, sl.y);
+        const float f2 = ffcu_conv_fp_f<CONTRACT>(a2, ws.z, bi.z, has_res, ffcu_byte2f<2>(rx), rs.z, has_slope, sl.z);
+        const float f3 = ffcu_conv_fp_f<CONTRACT>(a3, ws.w, bi.w, has_res, ffcu_byte2f<3>(rx), rs.w, has_slope, sl.w);
         const int w = ffcu_pack4(ffcu_requant_nosat<CHECK>(f0, iv.x), ffcu_requant_nosat<CHECK>(f1, iv.y),
                                  ffcu_requant_nosat<CHECK>(f2, iv.z), ffcu_requant_nosat<CHECK>(f3, iv.w));
         ow[g] = w;
@@ -638,7 +644,7 @@ __device__ __forceinline__ void walk_next(TileWalk& w, const TcParams& p)
 // (EPI != EPI_RUNTIME) assume what their launcher guarantees: the layer has the no-overflow proof, a
 // fused BN comes with its byte table, no accumulator dump is asked for; everything else runs the
 // EPI_RUNTIME variant.
-template <int BN, bool CONTRACT, bool OUT_F32, int EPI>
+template <int BN, bool CONTRACT, bool OUT_F32, int EPI, bool ACC22 = false>
 __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float* tab, const uint8_t* lut, TcShared* sh,
                                                  uint32_t tmem_base, volatile int* abort_flag, int warp, int lane,
                                                  int first, int step, int total, int m_mul, int m_off,
@@ -722,7 +728,7 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
                 }
                 if (OUT_F32) tc_fc16<CONTRACT>(p, tab, v0, cb, o);
                 else if (check) tc_epilogue16<CONTRACT, EPI, true, 0>(p, tab, lut_pr, v0, rw, cb, has_res, has_slope, has_bn2, w0, w0b);
-                else            tc_epilogue16<CONTRACT, EPI, false, 0>(p, tab, lut_pr, v0, rw, cb, has_res, has_slope, has_bn2, w0, w0b);
+                else            tc_epilogue16<CONTRACT, EPI, false, 0, ACC22>(p, tab, lut_pr, v0, rw, cb, has_res, has_slope, has_bn2, w0, w0b);
             }
             tmem_ld_wait(v1);
             if (more) tmem_ld16_issue(taddr + (uint32_t)(pr * 32 + 32), v0);  // lands while v1 is computed
@@ -736,7 +742,7 @@ __device__ __forceinline__ void tc_epilogue_role(const TcParams& p, const float*
                 if (OUT_F32) tc_fc16<CONTRACT>(p, tab, v1, cb + 16, o + 16);
                 else {
                     if (check) tc_epilogue16<CONTRACT, EPI, true, 1>(p, tab, lut_pr, v1, rw + 4, cb + 16, has_res, has_slope, has_bn2, w1, w1b);
-                    else       tc_epilogue16<CONTRACT, EPI, false, 1>(p, tab, lut_pr, v1, rw + 4, cb + 16, has_res, has_slope, has_bn2, w1, w1b);
+                    else       tc_epilogue16<CONTRACT, EPI, false, 1, ACC22>(p, tab, lut_pr, v1, rw + 4, cb + 16, has_res, has_slope, has_bn2, w1, w1b);
                     if (!TC_DBG(p, 4)) {
                         const int w8[8] = {w0[0], w0[1], w0[2], w0[3], w1[0], w1[1], w1[2], w1[3]};
                         st_global_32B((int8_t*)p.out + o, w8);

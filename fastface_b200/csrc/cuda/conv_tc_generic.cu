@@ -161,7 +161,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         }
     } else {
         tc_pdl_wait();
-        tc_epilogue_role<BN, CONTRACT, OUT_F32, EPI>(p, tab, lut, sh, tmem_base, abort_flag, warp, lane,
+        tc_epilogue_role<BN, CONTRACT, OUT_F32, EPI, (KC == 64 && EPI != EPI_RUNTIME && !OUT_F32)>(p, tab, lut, sh, tmem_base, abort_flag, warp, lane,
                                                 blockIdx.x, gridDim.x, p.total_tiles, 1, 0, 0u);
     }
     tc_teardown(abort_flag, tmem_base, TMEM_COLS, warp);

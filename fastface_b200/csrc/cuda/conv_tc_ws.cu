@@ -127,7 +127,7 @@ conv_ws_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             }
         }
     } else {
-        tc_epilogue_role<BN, CONTRACT, false, EPI>(p, tab, lut, sh, tmem_base, abort_flag, warp, lane,
+        tc_epilogue_role<BN, CONTRACT, false, EPI, (EPI != EPI_RUNTIME)>(p, tab, lut, sh, tmem_base, abort_flag, warp, lane,
                                              blockIdx.x, gridDim.x, p.total_tiles, 1, 0, 0u);
     }
     tc_teardown(abort_flag, tmem_base, TMEM_COLS, warp);

@@ -199,6 +199,20 @@ static bool epilogue_cannot_overflow(const ffcu_layer* l)
     return true;
 }
 
+// True when |accumulator| <= 128 * sum|w| stays below 2^22 for every output channel of this conv layer.
+static bool accumulator_fits_22_bits(const ffcu_layer* l)
+{
+    if (l->kind != FFCU_CONV || !l->w || l->Cout < 1) return false;
+    const size_t K = l->w_bytes / (size_t)l->Cout;
+    for (int c = 0; c < l->Cout; c++) {
+        long long s = 0;
+        const int8_t* wr = l->w + (size_t)c * K;
+        for (size_t k = 0; k < K; k++) s += wr[k] < 0 ? -(long long)wr[k] : (long long)wr[k];
+        if (128 * s >= (1ll << 22)) return false;
+    }
+    return true;
+}
+
 static void free_layer_memory(DevLayer& L)
 {
     cudaFree(L.w); L.w = nullptr;
@@ -244,6 +258,7 @@ extern "C" int ffcu_add_layer(ffcu_ctx* c, const ffcu_layer* l)
     }
     L.epi.bn_lut = L.bn_lut;
     L.epi.no_overflow = epilogue_cannot_overflow(l) ? 1 : 0;
+    L.epi.acc22 = accumulator_fits_22_bits(l) ? 1 : 0;
     L.d.bn2_lut = nullptr;
     L.d.bn2_in_scale = L.d.bn2_scale = L.d.bn2_offset = L.d.bn2_inv_out = nullptr;
     L.d.w = nullptr;
@@ -688,6 +703,7 @@ static int conv_once_impl(int device, const ffcu_layer* l, int batch, int mode, 
     if (rc == 0) {
         EpiTables t{tab[0], tab[1], tab[2], tab[3], tab[4], tab[5], tab[6], tab[7], tab[8], d_lut};
         t.no_overflow = epilogue_cannot_overflow(l) ? 1 : 0;
+        t.acc22 = accumulator_fits_22_bits(l) ? 1 : 0;
         if (impl == 0) {
             plan = ffcu_tc_plan(*l, batch, d_in, d_w, device, ffcu_tc_pick_bn(*l, batch, device));
             if (!plan) { ffcu_set_error("layer shape is not covered by the tensor-core kernel"); rc = -2; }
@@ -707,6 +723,7 @@ static int conv_once_impl(int device, const ffcu_layer* l, int batch, int mode, 
         ONCE_TRY(cudaEventCreate(&e1));
         EpiTables t{tab[0], tab[1], tab[2], tab[3], tab[4], tab[5], tab[6], tab[7], tab[8], d_lut};
         t.no_overflow = epilogue_cannot_overflow(l) ? 1 : 0;
+        t.acc22 = accumulator_fits_22_bits(l) ? 1 : 0;
         if (rc == 0) ONCE_TRY(cudaEventRecord(e0, s));
         for (int it = 0; it < iters && rc == 0; it++)
             rc = impl == 0 ? ffcu_tc_launch(plan, batch, mode, t, d_res, d_acc, d_out, d_out2, d_err, s)

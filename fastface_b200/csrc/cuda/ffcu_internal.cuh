@@ -48,6 +48,10 @@ struct EpiTables {
     // below 2^31 for every int8 input: the kernels then skip the per-element emulation of
     // x86's out-of-range conversion result (it cannot trigger).
     int no_overflow;
+    // 1 when the host has proved |accumulator| < 2^22 for every int8 input (128 * sum|w| per output channel):
+    // the kernels may then convert the accumulator to float with one integer add and one float add instead
+    // of the conversion unit (the 64-input-channel layers and the stem are bound by that unit).
+    int acc22;
 };
 
 // ---------------------------------------------------------------------------
@@ -97,6 +101,38 @@ __device__ __forceinline__ int ffcu_bn_q_nosat(int a, float in_scale, float bn_s
     float t = __fmul_rn(__int2float_rn(a), in_scale);
     t = __fmaf_rn(t, bn_scale, bn_offset);
     return ffcu_requant_nosat<CHECK>(t, inv);
+}
+
+// (float)acc without the conversion unit, exact for -2^22 <= acc < 2^22: the bit pattern of 1.5 * 2^23 plus acc
+// is the float 12582912 + acc (one unit in the last place is 1 in that binade); subtracting the constant is exact.
+__device__ __forceinline__ float ffcu_i2f_22(int acc)
+{
+    return __fadd_rn(__int_as_float(acc + 0x4B400000), -12582912.0f);
+}
+// (float)(int8_t) of byte K of a packed word, given wx = word ^ 0x80808080 (each byte + 128 as unsigned): the
+// byte dropped into the low byte of 2^23's bit pattern is the float 8388608 + byte + 128.  Always exact.
+template <int K>
+__device__ __forceinline__ float ffcu_byte2f(uint32_t wx)
+{
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(wx), "r"(0x4B000000u), "n"(0x7650 | K));
+    return __fadd_rn(__uint_as_float(d), -8388736.0f);
+}
+
+// Conv epilogue value before requantisation, from operands already converted to float.
+template <bool CONTRACT>
+__device__ __forceinline__ float ffcu_conv_fp_f(float t, float ws, float bias, bool has_res, float resf,
+                                                float rs, bool has_slope, float slope)
+{
+    if (CONTRACT) {
+        t = __fmaf_rn(t, ws, bias);
+        if (has_res) t = __fmaf_rn(resf, rs, t);
+    } else {
+        t = __fadd_rn(__fmul_rn(t, ws), bias);
+        if (has_res) t = __fadd_rn(t, __fmul_rn(resf, rs));
+    }
+    if (has_slope && t < 0.0f) t = __fmul_rn(t, slope);
+    return t;
 }
 
 // Conv epilogue value before requantisation (reference kernels/int8_epilogue.c:53-76).

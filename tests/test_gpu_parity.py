@@ -186,6 +186,71 @@ def test_single_layer_large_batch_vs_oracle(built_lib, case):
         assert not msg, msg
 
 
+@pytest.mark.parametrize("case", LAYER_CASES, ids=[c[0] for c in LAYER_CASES])
+@pytest.mark.parametrize("wide", [False, True], ids=["narrow", "wide"])
+def test_single_layer_specialised_epilogues(built_lib, case, wide, monkeypatch):
+    """Without an accumulator dump a layer takes the specialised epilogue variant of its kernel (the ones the
+    forward runs; a dump forces the general variant).  int8 output and fused BN output against the oracle,
+    both evaluation orders."""
+    name, B, H, Cin, Cout, k, stride, sl, rs = case
+    if wide:
+        force_wide_tiles(monkeypatch, Cout)
+    rng = np.random.default_rng(zlib.crc32(name.encode()) + 7)
+    L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
+    in_scale = (np.float32(1) / L["inv"]).astype(np.float32)
+    bn_s = rng.uniform(0.5, 1.5, Cout).astype(np.float32)
+    bn_o = (rng.standard_normal(Cout) * 0.1).astype(np.float32)
+    bn_inv = (np.float32(1) / (rng.uniform(0.005, 0.05, Cout).astype(np.float32) + np.float32(1e-9))).astype(np.float32)
+    lib = _libffo()
+    lib.ffo_bn_requant.argtypes = [C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                   C.c_float, C.c_void_p, C.c_int, C.c_int]
+    for mode in (ffo.CONTRACT, ffo.STRICT):
+        _, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"], L["res"], L["rs"], mode)
+        _, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"], slope=L["slope"],
+                              res=L["res"], res_scale=L["rs"], mode=mode, impl="tc", want_acc=False)
+        msg = describe_mismatch(f"int8 output (mode {mode})", out, out_o)
+        assert not msg, msg
+        if rs or sl:                       # the forward's fused-BN layers: residual + BN, and PReLU + BN in the stem
+            want2 = np.zeros_like(out_o)
+            lib.ffo_bn_requant(out_o.ctypes.data, 1.0, in_scale.ctypes.data, bn_s.ctypes.data, bn_o.ctypes.data, None,
+                               bn_inv.ctypes.data, 1.0, want2.ctypes.data, out_o.size // Cout, Cout)
+            _, out, out2 = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"], slope=L["slope"],
+                                        res=L["res"], res_scale=L["rs"], mode=mode, impl="tc", want_acc=False,
+                                        bn2=(in_scale, bn_s, bn_o, bn_inv))
+            assert np.array_equal(out, out_o)
+            msg = describe_mismatch(f"fused BN output (mode {mode})", out2, want2)
+            assert not msg, msg
+
+
+@pytest.mark.parametrize("wval,xval,proved", [(56, -128, True), (56, 127, True), (127, 127, False), (-127, -128, False)])
+def test_accumulator_to_float_near_and_beyond_22_bits(built_lib, wval, xval, proved):
+    """The 64-input-channel kernels convert the accumulator to float with an integer add and a float add where the
+    host has proved |accumulator| < 2^22 from the weights (128 * sum|w|), and take the general variant otherwise.
+    All-equal weights and activations drive the accumulator to the largest magnitude the weights allow: 576 * 56 *
+    128 = 4 128 768 is just inside the bound (proved: the add-based conversion runs at its edge), 576 * 127 * 127 is
+    twice beyond it (not proved: the layer must fall back).  Random tensors with the same weights ride along."""
+    rng = np.random.default_rng(1000 + wval + xval)
+    B, H, Cin, Cout = 2, 16, 64, 64
+    w = np.full((Cout, Cin, 3, 3), wval, np.int8)
+    assert (128 * np.abs(w.astype(np.int64)).reshape(Cout, -1).sum(1).max() < (1 << 22)) == proved
+    ws = np.exp(rng.uniform(np.log(5e-6), np.log(1.2e-5), Cout)).astype(np.float32)
+    bias = (rng.standard_normal(Cout) * 0.1).astype(np.float32)
+    inv = np.full(Cout, 1.0, np.float32)
+    slope = rng.uniform(0, 0.25, Cout).astype(np.float32)
+    res = rng.integers(-128, 128, size=(B, H, H, Cout), dtype=np.int8)
+    rs = rng.uniform(0.2, 2.0, Cout).astype(np.float32)
+    for x in (np.full((B, H, H, Cin), xval, np.int8), rng.integers(-128, 128, size=(B, H, H, Cin), dtype=np.int8)):
+        for mode in (ffo.CONTRACT, ffo.STRICT):
+            for sl, r, rsc in ((slope, None, None), (None, res, rs)):
+                acc_o, out_o = oracle_conv(x, w, ws, bias, inv, 1, 1, sl, r, rsc, mode)
+                _, out = ff.conv_once(x, w, ws, bias, inv, stride=1, pad=1, slope=sl, res=r, res_scale=rsc, mode=mode,
+                                      impl="tc", want_acc=False)
+                msg = describe_mismatch(f"w={wval} x={xval} mode {mode} {'PReLU' if sl is not None else 'residual'}", out, out_o)
+                assert not msg, msg
+        if x.min() == x.max():
+            assert (np.abs(acc_o).max() >= (1 << 22)) == (not proved)
+
+
 @pytest.mark.parametrize("impl", ["tc", "simt"])
 def test_requant_out_of_range_matches_x86_conversion(built_lib, impl):
     """With a requant scale so large that t * inv leaves the int32 range, the reference's
