@@ -483,10 +483,26 @@ void ffcu_chain_free(ChainPlan* p)
     delete p;
 }
 
+// One-shot fault injection for the layer chain's timeout-path test: consumed by the next chain launch.
+static int g_test_chain_drop_step = -1;
+static long long g_test_chain_wait = 0;
+
+extern "C" void ffcu_test_arm_chain_timeout(int drop_step, long long wait_cycles)
+{
+    g_test_chain_drop_step = drop_step;
+    g_test_chain_wait = wait_cycles;
+}
+
 int ffcu_chain_launch(const ChainPlan* p, int mode, int* d_err, cudaStream_t s)
 {
     ChainParams prm = p->prm;
     prm.err = d_err;
+    prm.wait_cycles = TC_WAIT_CYCLES; prm.drop_step = -1;
+    if (g_test_chain_drop_step >= 0) {                    // armed for this one launch
+        prm.drop_step = g_test_chain_drop_step;
+        if (g_test_chain_wait > 0) prm.wait_cycles = g_test_chain_wait;
+        g_test_chain_drop_step = -1; g_test_chain_wait = 0;
+    }
 #ifdef FF_TC_TIMING
     // timing build, $FF_CHAIN_TS=1: the 30th launch of a chain prints CTA 0's per-layer time stamps
     { static int dbg = -1; if (dbg < 0) { const char* e = getenv("FF_TC_DBG"); dbg = e ? atoi(e) : 0; } prm.dbg = dbg; }

@@ -845,7 +845,9 @@ struct ChainParams {
     int win_rows;                         // padded rows a CTA holds (the rows its row tile reads)
     int tiles_n;                          // C / 64 column tiles; CHAIN_CLUSTER / tiles_n row tiles
     int stages;                           // weight ring
-    int tps;                              // filter taps per stage (1, 3 or 9), planes x 8 KB each
+    int tps;                              // filter taps per stage (1 or 3), planes x 8 KB each
+    long long wait_cycles;                // limit of every barrier wait (TC_WAIT_CYCLES unless a test shortened it)
+    int drop_step;                        // >= 0: CTA 0's producer leaves out this ring step (ffcu_test_arm_chain_timeout; -1 otherwise)
     int* err;
 #ifdef FF_TC_TIMING
     unsigned long long* ts;               // timing build: per layer 4 time stamps of CTA 0 (ns)

@@ -147,6 +147,12 @@ int ffcu_winograd_f23_once(int device, const int8_t* in, const int8_t* w_oihw, i
  * the launch returns; ffcu_conv_once / ffcu_wait report 1000 + the error word.  Nothing faults,
  * traps or spins without a limit, and the hook disarms itself after that one launch. */
 void ffcu_test_arm_timeout(int drop_stage, long long full_wait_cycles);
+/* The same for the batch-1 layer-chain kernel (a cluster of eight CTAs): CTA 0's weight producer leaves out
+ * ring step drop_step of the next chain launch and every barrier wait of that launch is limited to
+ * wait_cycles.  CTA 0's MMA issuer gives up first; the other seven, waiting for results CTA 0 never
+ * sends, give up one limit later; all eight meet at the final cluster barrier, free their tensor memory
+ * and return; the call reports 1000 + the error word.  Disarms itself after that one launch. */
+void ffcu_test_arm_chain_timeout(int drop_step, long long wait_cycles);
 
 /* Small-batch FC (batch <= 16, N <= 512) that allocates nothing: no counterpart in the
  * reference.  For callers that hold device buffers but cannot call cudaMalloc -- a serving loop

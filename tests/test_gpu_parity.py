@@ -670,6 +670,30 @@ def test_bounded_wait_runs_out_and_the_device_stays_usable(built_lib):
         assert np.array_equal(acc, acc_o) and np.array_equal(out, out_o)
 
 
+def test_layer_chain_bounded_waits_run_out_and_the_device_stays_usable(built_lib, model_root, ffw4, oracle):
+    """The timeout path of the cluster-resident layer chain, exercised without faulting anything: the test hook makes
+    CTA 0's weight producer leave out one ring step of the next chain launch and limits every barrier wait of that
+    launch to two million cycles (about a millisecond).  CTA 0's issuer must give up, then the seven peers that wait
+    for CTA 0's results, all eight must meet at the final cluster barrier and return; the call reports 1000 + the
+    error word.  The same context must then serve the same face bit-exactly (eager, captured, replayed)."""
+    lib = ff.load_library()
+    lib.ffcu_test_arm_chain_timeout.restype = None
+    lib.ffcu_test_arm_chain_timeout.argtypes = [C.c_int, C.c_longlong]
+    faces = synth.faces(2, seed=5)
+    want = oracle.forward(faces, ffo.CONTRACT)
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=2) as e:
+        lib.ffcu_test_arm_chain_timeout(12, 2_000_000)          # layer 1, fourth tap
+        with pytest.raises(RuntimeError) as ei:
+            e.embed(faces[0])
+        # 1000 + the code of whichever wait ran out first: the issuer's for the missing stage (TMA, 1) or the epilogue
+        # warps' for the accumulator that stage belongs to (4): both started about together, with the same limit
+        assert "rc=1001" in str(ei.value) or "rc=1004" in str(ei.value), str(ei.value)
+        for _ in range(3):
+            assert np.array_equal(e.embed(faces[0]), want[0])
+            assert np.array_equal(e.embed(faces[1]), want[1])
+        assert e.launches_per_forward == 26
+
+
 def test_embed_and_embed_batch_agree_with_oracle(engine, oracle):
     faces = synth.faces(8, seed=99)
     want = oracle.forward(faces, ffo.CONTRACT)
