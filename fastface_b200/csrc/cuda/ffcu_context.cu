@@ -71,6 +71,12 @@ struct ffcu_ctx {
     std::map<long long, int> graph_launches;
     // Batch 1: runs of same-shape 3x3 stride-1 convolutions (the 14x14 and 7x7 stages) go out as one
     // launch each (conv_tc_chain.cu).  Found on the first one-face forward; FF_CHAIN=0 disables.
+    // Calls of at most lean_max_batch faces run copy-in, forward and copy-out on the compute stream alone
+    // (FF_LEAN_MAX_BATCH, default 1: the single-face call; 0 = always the three-stream pipeline, whose overlap of
+    // the next call's copy-in with this call's kernels is worth more than the hops it costs from a few faces up).
+    int lean_max_batch = 1;
+    bool lean_last = false;      // the previous submit took that path
+    bool err_copied = false;     // ... and queued the error word's copy already
     struct Chain { size_t first; int count; ChainPlan* plan; };
     std::vector<Chain> chains;
     bool chains_built = false;
@@ -132,6 +138,7 @@ extern "C" ffcu_ctx* ffcu_create(int device, int max_batch, int n_bufs, size_t b
     { const char* e = getenv("FF_GRAPH_MAX_BATCH"); if (e && atoi(e) > 0) c->graph_max_batch = atoi(e); }
     { const char* e = getenv("FF_GRAPH"); if (e && e[0] == '0') c->graph_max_batch = 0; }
     { const char* e = getenv("FF_CHAIN"); c->no_chain = (e && e[0] == '0') ? 1 : 0; }
+    { const char* e = getenv("FF_LEAN_MAX_BATCH"); if (e && atoi(e) >= 0) c->lean_max_batch = atoi(e); }
     if (!ok) {
         ffcu_set_error("device allocation failed on device %d: %s", device, cudaGetErrorString(cudaGetLastError()));
         ffcu_destroy(c);
@@ -487,6 +494,31 @@ static int submit_impl(ffcu_ctx* c, const void* host_in, size_t bytes_per_face, 
     FFCU_CHECK(cudaSetDevice(c->device));
     const int slot = (int)(c->seq & 1);
     const bool reused = c->seq >= 2;
+    if (n <= c->lean_max_batch) {
+        // Latency path (a handful of faces): copy-in, forward and copy-out in order on the compute stream.  The three-
+        // stream pipeline below buys overlap a small batch has no use for and costs it two cross-stream hops and a
+        // dozen driver calls per face.
+        if (!c->lean_last) {                          // the pipeline's copy streams may still hold the slots
+            FFCU_CHECK(cudaStreamSynchronize(c->s_in));
+            FFCU_CHECK(cudaStreamSynchronize(c->s_out));
+            c->lean_last = true;
+        }
+        FFCU_CHECK(cudaMemcpyAsync(c->in_slot[slot], host_in, (size_t)n * bytes_per_face, cudaMemcpyHostToDevice, c->stream));
+        c->d_in = c->in_slot[slot]; c->d_out = c->out_slot[slot];
+        c->in_u8 = u8;
+        int rc = run_forward(c, n, slot);
+        c->in_u8 = false;
+        if (rc != 0) return rc;
+        FFCU_CHECK(cudaMemcpyAsync(host_out, c->out_slot[slot], (size_t)n * 512 * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+        FFCU_CHECK(cudaMemcpyAsync(c->h_err, c->d_err, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+        c->err_copied = true;
+        c->seq++;
+        return 0;
+    }
+    if (c->lean_last) {                               // back to the pipeline: the compute stream owns the slots until it drains
+        FFCU_CHECK(cudaStreamSynchronize(c->stream));
+        c->lean_last = false;
+    }
     // copy-in stream: the slot is free once the forward that last read it has finished
     if (reused) FFCU_CHECK(cudaStreamWaitEvent(c->s_in, c->ev_compute_done[slot], 0));
     FFCU_CHECK(cudaMemcpyAsync(c->in_slot[slot], host_in, (size_t)n * bytes_per_face, cudaMemcpyHostToDevice, c->s_in));
@@ -522,10 +554,15 @@ extern "C" int ffcu_wait(ffcu_ctx* c)
 {
     if (!c) return -1;
     FFCU_CHECK(cudaSetDevice(c->device));
-    FFCU_CHECK(cudaStreamSynchronize(c->s_in));
-    FFCU_CHECK(cudaMemcpyAsync(c->h_err, c->d_err, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
-    FFCU_CHECK(cudaStreamSynchronize(c->stream));
-    FFCU_CHECK(cudaStreamSynchronize(c->s_out));
+    if (c->lean_last && c->err_copied) {
+        FFCU_CHECK(cudaStreamSynchronize(c->stream));    // the error word's copy was queued behind the forward
+    } else {
+        FFCU_CHECK(cudaStreamSynchronize(c->s_in));
+        FFCU_CHECK(cudaMemcpyAsync(c->h_err, c->d_err, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+        FFCU_CHECK(cudaStreamSynchronize(c->stream));
+        FFCU_CHECK(cudaStreamSynchronize(c->s_out));
+    }
+    c->err_copied = false;
     if (*c->h_err != 0) {
         ffcu_set_error("device reported error word %d (a bounded wait inside a kernel ran out)", *c->h_err);
         int e = *c->h_err;
