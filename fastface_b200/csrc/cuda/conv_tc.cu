@@ -384,6 +384,145 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
 
 
 // ---------------------------------------------------------------------------
+// Stride-2 convolution + the block's 1x1 stride-2 shortcut in one launch (conv_tc_sc.cu)
+// ---------------------------------------------------------------------------
+struct ScPlan {
+    TcPlan* main;            // the main path's plan for 64-column tiles (tensor maps of its input and weights)
+    ffcu_layer d2;           // the shortcut layer
+    const int8_t* d_in2;
+    CUtensorMap mapB2;       // shortcut weights [Cout][Cin2], box {KC, 64}
+    TcGeom geoms2[8];        // shortcut input boxes per tile geometry
+    int n_geoms2;
+    int kb_sc, stages, group, smem_bytes, lut_bytes;
+};
+
+static bool encode_A2(ScPlan* sp, TcGeom* g)
+{
+    encode_tiled_fn enc = get_encode();
+    const ffcu_layer& d = sp->d2;
+    const int KC = sp->main->KC;
+    const cuuint64_t Cp = (cuuint64_t)d.Cin_pad;
+    cuuint64_t dims[4] = {Cp, (cuuint64_t)d.W, (cuuint64_t)d.H, (cuuint64_t)sp->main->max_batch};
+    cuuint64_t strides[3] = {Cp, Cp * d.W, Cp * d.W * d.H};
+    // box of KC bytes per pixel even where the shortcut's input has fewer channels: the rest is out-of-range fill (zeros)
+    cuuint32_t box[4] = {(cuuint32_t)KC, (cuuint32_t)(g->TW * 2), (cuuint32_t)(g->TH * 2), (cuuint32_t)g->TB};
+    cuuint32_t estr[4] = {1, 2, 2, 1};
+    if (g->TW == 1) { box[1] = 1; estr[1] = 1; }
+    if (g->TH == 1) { box[2] = 1; estr[2] = 1; }
+    CUresult r = enc(&g->mapA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)sp->d_in2, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, KC == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { ffcu_set_error("cuTensorMapEncodeTiled(shortcut A) failed: %d", (int)r); return false; }
+    return true;
+}
+
+// main: 3x3 stride-2 pad-1 convolution without residual or fused BN; sc: 1x1 stride-2 pad-0 convolution with the same
+// output shape whose residual is main's output.  NULL when the pair does not fit the kernel.
+ScPlan* ffcu_sc_plan(const ffcu_layer& main, const ffcu_layer& sc, int max_batch, const int8_t* d_in_main, const int8_t* d_w_main,
+                     const int8_t* d_in_sc, const int8_t* d_w_sc, int device)
+{
+    encode_tiled_fn enc = get_encode();
+    if (!enc) return nullptr;
+    if (main.kind != FFCU_CONV || sc.kind != FFCU_CONV || main.Kh != 3 || main.Kw != 3 || main.stride != 2 || main.pad != 1 ||
+        sc.Kh != 1 || sc.Kw != 1 || sc.stride != 2 || sc.pad != 0 || main.Cout != sc.Cout || main.Ho != sc.Ho || main.Wo != sc.Wo ||
+        main.H != sc.H || main.W != sc.W || main.Cout % 64 != 0 || main.Cout > TC_MAX_COUT || sc.Cin_pad % 64 != 0)
+        return nullptr;
+    TcPlan* mp = ffcu_tc_plan(main, max_batch, d_in_main, d_w_main, device, 64);
+    if (!mp) return nullptr;
+    ScPlan* sp = new ScPlan();
+    sp->main = mp; sp->d2 = sc; sp->d_in2 = d_in_sc; sp->n_geoms2 = 0;
+    const int KC = mp->KC;
+    sp->kb_sc = (sc.Cin_pad + KC - 1) / KC;
+    sp->lut_bytes = sc.bn2_dst_buf >= 0 ? 64 * 256 : 0;
+    const int sub_bytes = (TC_TILE_M + 64) * KC;
+    const int fixed = 10 * TC_MAX_COUT * 4 + sp->lut_bytes + (int)sizeof(TcShared) + 1024;
+    // K blocks per stage: the main plan's, or the next smaller divisor of the K loop that leaves two stages beside the
+    // second table set and the byte table this kernel holds
+    const int kblocks = 9 * (main.Cin_pad / KC);
+    int group = mp->group, st = 0;
+    for (; group >= 1; group--) {
+        if (kblocks % group) continue;
+        st = (232448 - fixed) / (group * sub_bytes);
+        if (st >= 2) break;
+    }
+    if (st > TC_MAX_STAGES) st = TC_MAX_STAGES;
+    if (group < 1 || st < 2 || sp->kb_sc > group || 2 * group > 32) { ffcu_tc_free(mp); delete sp; return nullptr; }
+    sp->stages = st; sp->group = group;
+    sp->smem_bytes = st * group * sub_bytes + fixed;
+    cuuint64_t K2 = (cuuint64_t)sc.Cin_pad;
+    cuuint64_t dims[4] = {K2, (cuuint64_t)sc.Cout, 1, 1};
+    cuuint64_t strides[3] = {K2, K2 * sc.Cout, K2 * sc.Cout};
+    cuuint32_t box[4] = {(cuuint32_t)KC, 64, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(&sp->mapB2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d_w_sc, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, KC == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { ffcu_tc_free(mp); delete sp; cudaGetLastError(); return nullptr; }
+    return sp;
+}
+
+void ffcu_sc_free(ScPlan* sp)
+{
+    if (!sp) return;
+    ffcu_tc_free(sp->main);
+    delete sp;
+}
+
+// t1 / t2: the main path's and the shortcut's tables; out_main: where the main path's int8 output goes when another
+// layer reads it (write_main), out_sc / out2_sc: the block's output and its fused BN output (or NULL).
+int ffcu_sc_launch(const ScPlan* csp, int batch, int mode, const EpiTables& t1, const EpiTables& t2, int8_t* out_main,
+                   int write_main, int8_t* out_sc, int8_t* out2_sc, int* d_err, cudaStream_t s)
+{
+    ScPlan* sp = const_cast<ScPlan*>(csp);
+    TcPlan* p = sp->main;
+    if (batch < 1 || batch > p->max_batch) { ffcu_set_error("shortcut-fused launch: batch out of range"); return -1; }
+    const ffcu_layer& d = p->d;
+    int TW, TH, TB;
+    pick_geometry(d.Wo, d.Ho, batch, &TW, &TH, &TB);
+    TcGeom* g = nullptr;
+    for (int i = 0; i < p->n_geoms; i++)
+        if (p->geoms[i].TW == TW && p->geoms[i].TH == TH && p->geoms[i].TB == TB) g = &p->geoms[i];
+    if (!g) {
+        if (p->n_geoms == 8) p->n_geoms = 0;
+        g = &p->geoms[p->n_geoms];
+        g->TW = TW; g->TH = TH; g->TB = TB;
+        if (!encode_A(p, g)) return -1;
+        p->n_geoms++;
+    }
+    TcGeom* g2 = nullptr;
+    for (int i = 0; i < sp->n_geoms2; i++)
+        if (sp->geoms2[i].TW == TW && sp->geoms2[i].TH == TH && sp->geoms2[i].TB == TB) g2 = &sp->geoms2[i];
+    if (!g2) {
+        if (sp->n_geoms2 == 8) sp->n_geoms2 = 0;
+        g2 = &sp->geoms2[sp->n_geoms2];
+        g2->TW = TW; g2->TH = TH; g2->TB = TB;
+        if (!encode_A2(sp, g2)) return -1;
+        sp->n_geoms2++;
+    }
+    TcParams prm = {};
+    prm.t = t1; prm.res = nullptr; prm.acc_out = nullptr; prm.out = out_main; prm.out2 = nullptr; prm.err = d_err;
+    prm.batch = batch; prm.Ho = d.Ho; prm.Wo = d.Wo; prm.Cout = d.Cout;
+    prm.taps = 9; prm.Kw = 3; prm.Cp = d.Cin_pad; prm.cin_blocks = d.Cin_pad / p->KC;
+    prm.stride = 2; prm.pad = 1;
+    prm.TW = TW; prm.TH = TH; prm.TB = TB;
+    prm.tiles_w = (d.Wo + TW - 1) / TW; prm.tiles_h = (d.Ho + TH - 1) / TH; prm.tiles_b = (batch + TB - 1) / TB;
+    prm.tiles_n = d.Cout / 64;
+    prm.total_tiles = prm.tiles_w * prm.tiles_h * prm.tiles_b * prm.tiles_n;
+    prm.stages = sp->stages; prm.group = sp->group; prm.lut_bytes = 0; prm.ntab = 5;
+    prm.full_wait = TC_WAIT_CYCLES; prm.drop_stage = -1;
+#ifdef FF_TC_TIMING
+    prm.dbg = 0;
+#endif
+    int grid = prm.total_tiles < p->n_sm ? prm.total_tiles : p->n_sm;
+    if (grid > prm.tiles_n) grid -= grid % prm.tiles_n;
+    prm.epi_wps = tc_epi_wps(64, prm.total_tiles / grid);
+    ScParams q = {};
+    q.t2 = t2; q.out_sc = out_sc; q.out2_sc = (out2_sc && t2.bn_lut && sp->lut_bytes) ? out2_sc : nullptr;
+    q.kb_sc = sp->kb_sc; q.write_main = (write_main && out_main) ? 1 : 0; q.lut_bytes = q.out2_sc ? sp->lut_bytes : 0;
+    return tc_launch_sc(p->KC, mode, grid, sp->smem_bytes, s, g->mapA, p->mapB, g2->mapA, sp->mapB2, prm, q);
+}
+
+// ---------------------------------------------------------------------------
 // Layer chain (conv_tc_chain.cu): plan = the first input's tensor map, the per-layer records in
 // device memory (weights' tensor map, table / buffer pointers) and the shared-memory budget
 // ---------------------------------------------------------------------------
@@ -432,6 +571,7 @@ ChainPlan* ffcu_chain_plan(int H, int W, int C, const int8_t* d_in, const ChainL
     if (stages > CHAIN_MAX_STAGES) stages = CHAIN_MAX_STAGES;
     stages &= ~1;                                         // two issuers on alternate stages: the ring must be even
     if (stages < 2) return nullptr;
+    if (!tc_chain_fits(fixed + stages * stage_bytes)) return nullptr;      // no room for a cluster of eight on this device
     ChainPlan* p = new ChainPlan();
     p->d_layers = nullptr;
     {

@@ -411,3 +411,25 @@ int tc_launch_chain(int mode, int smem, cudaStream_t s, const CUtensorMap& mapA,
     if (mode) return tc_launch_ex(conv_chain_kernel<true>, CHAIN_CLUSTER, smem, s, CHAIN_CLUSTER, mapA, prm);
     return tc_launch_ex(conv_chain_kernel<false>, CHAIN_CLUSTER, smem, s, CHAIN_CLUSTER, mapA, prm);
 }
+
+// Can this device co-schedule one cluster of the chain kernel (eight CTAs with `smem` bytes each in one GPC)?
+// Asked once per plan; a device that cannot keeps the per-layer launches.
+bool tc_chain_fits(int smem)
+{
+    if (cudaFuncSetAttribute(conv_chain_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(conv_chain_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(CHAIN_CLUSTER);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CHAIN_CLUSTER; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, conv_chain_kernel<true>, &cfg) != cudaSuccess) { cudaGetLastError(); return false; }
+    return n >= 1;
+}

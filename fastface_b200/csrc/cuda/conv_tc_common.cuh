@@ -819,6 +819,18 @@ int tc_launch_stem(int mode, int epi, int in_u8, int grid, int smem, cudaStream_
 int tc_launch_wsp(int mode, int epi, int grid, int smem, cudaStream_t s,
                   const CUtensorMap& mapA, const CUtensorMap& mapB_half, const TcParams& prm);
 
+// Stride-2 convolution + 1x1 shortcut in one launch (conv_tc_sc.cu)
+struct ScParams {
+    EpiTables t2;            // the shortcut layer's tables; res_scale scales the main path's int8 output
+    int8_t* out_sc;          // the block's output (NHWC int8)
+    int8_t* out2_sc;         // its fused BN output, or NULL
+    int kb_sc;               // K blocks of the shortcut: its input channels / KC, rounded up (<= the main path's group)
+    int write_main;          // 1: the main path's int8 output is stored too (TcParams::out): another layer reads it
+    int lut_bytes;           // 64 * 256 when out2_sc comes through the byte table, else 0
+};
+int tc_launch_sc(int kc, int mode, int grid, int smem, cudaStream_t s, const CUtensorMap& mapA, const CUtensorMap& mapB,
+                 const CUtensorMap& mapA2, const CUtensorMap& mapB2, const TcParams& prm, const ScParams& q);
+
 // Layer chain (conv_tc_chain.cu)
 #define CHAIN_CLUSTER 8
 #define CHAIN_BN 64
@@ -856,6 +868,7 @@ struct ChainParams {
 };
 
 int tc_launch_chain(int mode, int smem, cudaStream_t s, const CUtensorMap& mapA, const ChainParams& prm);
+bool tc_chain_fits(int smem);
 
 // Flat-pitch weight-stationary pair kernel: activation buffer = guard + box of WSP_BOX_ROWS image rows
 #define WSP_GUARD_BYTES 1024

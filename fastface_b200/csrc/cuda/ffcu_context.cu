@@ -34,6 +34,8 @@ struct DevLayer {
     bool fused_stem = false;   // conv that also does the input quantisation (reads the fp32 input)
     bool skip = false;         // quantise layer absorbed by the fused stem
     StemTcPlan* stem_tc = nullptr; // fused stem on tensor cores, one launch (else the dp4a stem kernel)
+    ScPlan* sc = nullptr;          // this stride-2 conv and the next layer (the block's 1x1 shortcut) as one launch
+    int sc_write_main = 0;         // ... which must still store this layer's output: a later layer reads it
     int8_t* wk32 = nullptr;        // its weights repacked [64][32]
 };
 
@@ -161,6 +163,7 @@ extern "C" void ffcu_destroy(ffcu_ctx* c)
     for (auto& L : c->layers) {
         for (TcPlan* q : L.tc_bn) if (q) ffcu_tc_free(q);      // L.tc is one of them
         if (L.stem_tc) ffcu_stem_tc_free(L.stem_tc);
+        if (L.sc) ffcu_sc_free(L.sc);
         free_layer_memory(L);
     }
     for (int i = 0; i < FFCU_MAX_BUFS; i++) cudaFree(c->bufs[i]);
@@ -306,6 +309,30 @@ extern "C" int ffcu_finalize(ffcu_ctx* c)
             }
         }
     }
+    // [conv 3x3 stride 2] -> [conv 1x1 stride 2 on the block's input, ADD of the former's output fused]: one launch
+    // where the call's column tile is 64 channels wide (conv_tc_sc.cu).  FF_FUSE_SC=0 keeps the two launches.
+    const char* fsc = getenv("FF_FUSE_SC");
+    if (!c->force_simt && !(fsc && fsc[0] == '0')) {
+        for (size_t k = 0; k + 1 < c->layers.size(); k++) {
+            DevLayer& M = c->layers[k]; DevLayer& S = c->layers[k + 1];
+            const ffcu_layer& m = M.d; const ffcu_layer& sd = S.d;
+            if (m.kind != FFCU_CONV || sd.kind != FFCU_CONV || !M.tc || !S.tc || M.fused_stem) continue;
+            if (m.stride != 2 || m.Kh != 3 || m.res_buf >= 0 || m.bn2_dst_buf >= 0 || sd.Kh != 1 || sd.stride != 2) continue;
+            if (sd.res_buf != m.dst_buf || sd.res_buf < 0 || !S.epi.res_scale) continue;
+            if (!M.epi.no_overflow || !S.epi.no_overflow) continue;
+            if (sd.bn2_dst_buf >= 0 && !S.bn_lut) continue;
+            if (sd.src_buf < 0 || sd.src_buf >= c->n_bufs) continue;
+            // does anything after the shortcut still read the main path's tensor before it is overwritten?
+            int write_main = 0;
+            for (size_t j = k + 2; j < c->layers.size(); j++) {
+                const ffcu_layer& o = c->layers[j].d;
+                if (o.src_buf == m.dst_buf || o.res_buf == m.dst_buf) { write_main = 1; break; }
+                if (o.dst_buf == m.dst_buf || o.bn2_dst_buf == m.dst_buf) break;
+            }
+            M.sc = ffcu_sc_plan(m, sd, c->max_batch, c->bufs[m.src_buf], M.w, c->bufs[sd.src_buf], S.w, c->device);
+            M.sc_write_main = write_main;
+        }
+    }
     c->launches = 0;
     for (auto& L : c->layers) if (!L.skip) c->launches++;
     c->finalized = true;
@@ -431,10 +458,30 @@ static int launch_forward(ffcu_ctx* c, int n)
             while (next_chain < c->chains.size() && c->chains[next_chain].first < k) next_chain++;
             if (next_chain < c->chains.size() && c->chains[next_chain].first == k) {
                 const ffcu_ctx::Chain& ch = c->chains[next_chain];
-                int rc = ffcu_chain_launch(ch.plan, c->mode, c->d_err, c->stream);
+                if (ffcu_chain_launch(ch.plan, c->mode, c->d_err, c->stream) == 0) {
+                    launches++;
+                    k += (size_t)ch.count - 1;
+                    continue;
+                }
+                // the cluster launch was refused (no eight free SMs in one GPC right now, a partitioned device ...):
+                // drop the chains for this context and go on with this layer as a launch of its own
+                cudaGetLastError();
+                for (auto& gone : c->chains) ffcu_chain_free(gone.plan);
+                c->chains.clear();
+                c->no_chain = 1;
+            }
+        }
+        {
+            DevLayer& M = c->layers[k];
+            if (M.sc && ffcu_tc_pick_bn(M.d, n, c->device) == 64) {
+                // stride-2 conv + the block's shortcut, one launch
+                DevLayer& S = c->layers[k + 1];
+                int8_t* out2 = S.d.bn2_dst_buf >= 0 ? c->bufs[S.d.bn2_dst_buf] : nullptr;
+                int rc = ffcu_sc_launch(M.sc, n, c->mode, M.epi, S.epi, c->bufs[M.d.dst_buf], M.sc_write_main,
+                                        c->bufs[S.d.dst_buf], out2, c->d_err, c->stream);
                 if (rc != 0) return rc;
                 launches++;
-                k += (size_t)ch.count - 1;
+                k++;
                 continue;
             }
         }

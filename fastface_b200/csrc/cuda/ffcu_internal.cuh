@@ -195,6 +195,13 @@ int ffcu_launch_fc_small(const int8_t* act, const int8_t* w, const float* w_scal
 // ---------------------------------------------------------------------------
 // Tensor-core implicit GEMM (conv_tc.cu)
 // ---------------------------------------------------------------------------
+// A down-sampling block's stride-2 3x3 convolution and its 1x1 stride-2 shortcut (+ ADD + fused BN) in one launch.
+struct ScPlan;
+ScPlan* ffcu_sc_plan(const ffcu_layer& main, const ffcu_layer& sc, int max_batch, const int8_t* d_in_main, const int8_t* d_w_main,
+                     const int8_t* d_in_sc, const int8_t* d_w_sc, int device);
+void    ffcu_sc_free(ScPlan* sp);
+int     ffcu_sc_launch(const ScPlan* sp, int batch, int mode, const EpiTables& t1, const EpiTables& t2, int8_t* out_main,
+                       int write_main, int8_t* out_sc, int8_t* out2_sc, int* d_err, cudaStream_t s);
 // Layer chain (batch 1): consecutive 3x3 stride-1 C -> C convolutions of one feature-map size in one launch.
 struct ChainPlan;
 struct ChainLayerDesc { const int8_t* w; EpiTables t; const int8_t* res; int8_t* out; int8_t* out2; };

@@ -312,8 +312,9 @@ def test_unfused_plan_agrees(built_lib, model_root, ffw4, oracle, monkeypatch):
     monkeypatch.setenv("FF_FUSE_STEM", "0")
     with ff.FastFace(ffw4, cwd=model_root, max_batch=3) as e:
         assert np.array_equal(e.embed_batch(faces), want)
-        # fused: 1 stem launch, 52 convs, 1 FC; unfused: 1 quantise, 53 convs, 25 BN passes, 1 FC
-        assert e.launches_per_forward == 80 and n_fused == 54
+        # fused: 1 stem launch, 52 convs (the four stride-2 conv + shortcut pairs one launch each at this batch), 1 FC;
+        # unfused: 1 quantise, 53 convs (same four pairs fused), 25 BN passes, 1 FC
+        assert e.launches_per_forward == 80 - 4 and n_fused == 54 - 4
 
 
 @pytest.mark.parametrize("case", LAYER_CASES[:4], ids=lambda c: c[0])
@@ -412,7 +413,7 @@ def test_network_microbench_single_face(built_lib):
     the public call; the similarity matrix of an embedding with itself has a unit diagonal."""
     from fastface_b200 import layer_bench
     line = layer_bench.run_forward(1, 3, 4)
-    assert line["launches_per_forward"] == 26 and line["device_ms_per_forward"] > 0
+    assert line["launches_per_forward"] == 22 and line["device_ms_per_forward"] > 0
     assert abs(line["cos_sim_matrix"]["diag_min"] - 1.0) < 1e-6
 
 
@@ -646,7 +647,29 @@ def test_single_face_layer_chains(built_lib, model_root, ffw4, oracle, monkeypat
                     assert np.array_equal(got, want[i]), f"FF_CHAIN={flag} rep {rep} face {i}"
             counts[flag] = e.launches_per_forward
             assert np.array_equal(e.embed_batch(faces), want)      # batch 4: per-layer launches in the same context
-    assert counts["0"] == 54 and counts["1"] == 54 - 26 - 4 + 2, counts
+    assert counts["0"] == 54 - 4 and counts["1"] == 54 - 4 - 26 - 4 + 2, counts
+
+
+@pytest.mark.parametrize("B", [1, 5, 40, 300])
+def test_stride2_conv_and_shortcut_in_one_launch(built_lib, model_root, ffw4, oracle, monkeypatch, B):
+    """A down-sampling block's 3x3 stride-2 convolution and its 1x1 stride-2 shortcut (ADD and the next block's BN
+    fused) run as ONE launch where the call's column tile is 64 channels wide: all four blocks at small batch, the
+    112x112 one at any batch.  Same bytes as the two launches (FF_FUSE_SC=0) and as the oracle, both epilogue orders."""
+    faces = synth.faces(B, seed=300 + B)
+    sample = sorted(set([0, B // 2, B - 1]))
+    want = {m: oracle.forward(faces[sample], m) for m in (ffo.CONTRACT, ffo.STRICT)}
+    counts = {}
+    for flag in ("1", "0"):
+        monkeypatch.setenv("FF_FUSE_SC", flag)
+        with ff.FastFace(ffw4, cwd=model_root, max_batch=B) as e:
+            for mode in (ffo.CONTRACT, ffo.STRICT):
+                e.set_epilogue_mode(mode)
+                for rep in range(2):
+                    got = e.embed_batch(faces) if B > 1 else e.embed(faces[0])[None, :]
+                    assert np.array_equal(got[sample], want[mode]), f"FF_FUSE_SC={flag} mode {mode} rep {rep}"
+            counts[flag] = e.launches_per_forward
+    fused_pairs = counts["0"] - counts["1"]                 # the wider the batch, the fewer blocks keep 64-column tiles
+    assert fused_pairs == 4 if B <= 5 else 1 <= fused_pairs <= 4, counts
 
 
 def test_bounded_wait_runs_out_and_the_device_stays_usable(built_lib):
@@ -691,7 +714,7 @@ def test_layer_chain_bounded_waits_run_out_and_the_device_stays_usable(built_lib
         for _ in range(3):
             assert np.array_equal(e.embed(faces[0]), want[0])
             assert np.array_equal(e.embed(faces[1]), want[1])
-        assert e.launches_per_forward == 26
+        assert e.launches_per_forward == 22
 
 
 def test_embed_and_embed_batch_agree_with_oracle(engine, oracle):
@@ -753,7 +776,7 @@ def test_stem_on_cuda_cores_agrees(built_lib, model_root, ffw4, oracle, monkeypa
         with ff.FastFace(ffw4, cwd=model_root, max_batch=3) as e:
             assert np.array_equal(e.embed_batch(faces), want), f"FF_STEM_TC={flag}"
             assert np.array_equal(e.embed_batch_u8(pix), want_u8), f"FF_STEM_TC={flag}, uint8 input"
-            assert e.launches_per_forward == 54
+            assert e.launches_per_forward == 54 - 4
 
 
 def test_network_with_the_large_batch_tiling(built_lib, model_root, ffw4, oracle, monkeypatch):
