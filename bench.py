@@ -472,7 +472,7 @@ def run_own_arm(args, rank, local_rank, world):
                                  f"written) / CUDA-event time, against the {peaks['source']} copy bandwidth"}
         all_tc = tc_ops / (tc_ms * 1e-3) / 1e12 if tc_ms > 0 else 0.0
         roof_all = {"achieved": round(all_tc, 1), "frac": round(all_tc / peak, 4), "peak": round(peak, 1), "unit": "TOP/s",
-                    "note": f"all {len(tc)} tensor-core launches of a forward: {tc_ops / 1e9:.1f} GOP in {tc_ms:.3f} ms "
+                    "note": f"all {len(tc)} tensor-core layers of a forward (a stride-2 conv that shares its launch with the shortcut is timed as that one launch): {tc_ops / 1e9:.1f} GOP in {tc_ms:.3f} ms "
                             f"({100.0 * tc_ms / all_ms:.1f}% of the per-layer total)"}
         # per resolution stage: time, algorithmic ops, achieved rate and its share of the
         # kind::i8 rate the probe reaches in this run (a tensor-pipe utilisation figure from CUDA events)

@@ -4,22 +4,24 @@
 //
 // At batch 1 a 14x14 layer is 8 tiles (2 row tiles x 4 column tiles of 64 channels); as separate
 // launches each layer pays kernel completion + dependency release + a TMA round trip for 50 KB of
-// activations before its first MMA.  Here the eight CTAs of a cluster take one tile each and keep
-// the WHOLE input tensor of the current layer in their own shared memory, laid out the way a TMA
-// load with 128-byte swizzle would have left it: line (row + 1) * P + (col + 1) of 128 channels per
-// plane, P = pitch in lines, zero lines for the padding (each CTA holds the window of rows its row
-// tile reads; the shared memory that saves goes to a deeper weight ring).  Filter tap (kh, kw) is then the same buffer
-// read (kh * P + kw) lines further on (the tensor core applies the swizzle to absolute shared-memory
-// addresses), so the activations need no loads at all.  A CTA's epilogue writes its 128 x 64 result,
-// already requantised to int8 (the fused BN's output where the layer has one), into the NEXT layer's
-// buffer of all eight CTAs (st.shared::cluster) and arrives on their barriers; the weights stream
-// through a TMA ring that runs ahead across layer boundaries, since they depend on nothing.
-// Global memory still receives every output (the residual two layers on reads it from there, and the
-// kernel after the chain).  Replaces, per layer, what conv_tc_kernel does (reference
-// kernels/conv2d_nhwc.c:179-220, kernels/int8_epilogue.c:25-112, :253-318); same arithmetic, same bytes.
+// activations before its first MMA.  Here the eight CTAs of a cluster take one tile each and keep the
+// rows of the current layer's input their row tile reads in their own shared memory (double-buffered),
+// laid out the way a TMA load with 128-byte swizzle would have left them: line (row + 1) * P + (col + 1)
+// of 128 channels per plane, P = pitch in lines, zero lines for the padding.  Filter tap (kh, kw) is then
+// the same buffer read (kh * P + kw) lines further on (the tensor core applies the swizzle to absolute
+// shared-memory addresses), so the activations need no loads at all.  A CTA's epilogue requantises its
+// 128 x 64 result to int8 (the fused BN's output where the layer has one) and writes each 16-byte piece
+// straight into the NEXT layer's buffer of every CTA whose row tile reads that row, with st.async stores
+// that count their bytes on the receiving CTA's barrier: "input complete" is a byte count, no fence or
+// barrier round.  The weights stream through a TMA ring that runs ahead across layer boundaries, since
+// they depend on nothing.  Global memory still receives every output (the residual two layers on is
+// read from there, and the kernel after the chain).  Replaces, per layer, what conv_tc_kernel does
+// (reference kernels/conv2d_nhwc.c:179-220, kernels/int8_epilogue.c:25-112, :253-318); same
+// arithmetic, same bytes.
 //
-// Every wait is bounded as in the other kernels; nobody leaves before the whole cluster has
-// arrived at the final barrier, so no CTA's shared memory is written after it has exited.
+// Every wait is bounded as in the other kernels (the limit is a launch parameter); nobody leaves before
+// the whole cluster has arrived at the final barrier, so no CTA's shared memory is written after it has
+// exited.
 #include "conv_tc_common.cuh"
 
 struct ChainShared {
