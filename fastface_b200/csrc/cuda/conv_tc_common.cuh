@@ -531,6 +531,9 @@ __device__ __forceinline__ void tc_epilogue16(const TcParams& p, const float* ta
                                 ffcu_bn_q_nosat<CHECK>(a2, b_in.z, b_sc.z, b_of.z, b_iv.z),
                                 ffcu_bn_q_nosat<CHECK>(a3, b_in.w, b_sc.w, b_of.w, b_iv.w));
         } else if (has_bn2) {
+#ifdef FF_TC_TIMING
+            if (TC_DBG(p, 32)) { ow2[g] = w ^ 0x01010101; return; }     // timing experiment: no table look-ups (wrong results)
+#endif
             // BN of the four int8 results just packed: one table row per channel, indexed by the byte
             constexpr int R = CI * 16 + 4 * g;
             const uint32_t b0 = tc_lut_byte<0, R + 0>((uint32_t)w, lut_pr), b1 = tc_lut_byte<1, R + 1>((uint32_t)w, lut_pr);
