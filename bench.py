@@ -459,7 +459,7 @@ def run_own_arm(args, rank, local_rank, world):
                         f"{'burst' if peak == peak_burst else 'sustained'} of {peaks['source']} MEASURED_PEAKS (int8 runs at twice "
                         f"the bf16 rate; the driver measures no int8 figure); i8_mma_probe_tops = kind::i8 MMAs on "
                         f"shared-memory operands with no loads, measured in this run"}
-        # the stem (fp32 faces -> int8, 3->64 conv, PReLU, fused BN): HBM-bound, bytes per face stated in DESIGN.md
+        # the stem (fp32 faces -> int8, 3->64 conv, PReLU, fused BN): HBM-bound; bytes per face = one fp32 face read + two int8 112x112x64 tensors written
         stem = [(l, t / 3.0) for l, t in zip(layers, per_layer) if l["kind"] == 1 and l["Cin"] == 3]
         roof_stem = None
         if stem and peaks["hbm_gbs"]:

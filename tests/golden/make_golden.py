@@ -33,7 +33,7 @@ from oracle import ffo            # noqa: E402
 
 
 def conv56_case(seed=0):
-    """BASELINE single-layer case: conv3x3 s1 p1 64->64, 56x56 NHWC, batch 8."""
+    """The reference's single-layer benchmark case: conv3x3 s1 p1 64->64, 56x56 NHWC, batch 8."""
     rng = np.random.Generator(np.random.PCG64(4242 + seed))
     x = rng.integers(-127, 128, size=(8, 56, 56, 64), dtype=np.int8)
     w = np.clip(np.rint(rng.standard_normal((64, 64, 3, 3)) * 40.0), -127, 127).astype(np.int8)

@@ -446,7 +446,7 @@ def test_stem_conv_simt_vs_oracle(built_lib):
 @pytest.mark.parametrize("mode,tag", [(ff.EPILOGUE_CONTRACT, "contract"), (ff.EPILOGUE_STRICT, "strict")])
 @pytest.mark.parametrize("impl", ["tc", "simt"])
 def test_conv56_microbench_vs_reference_golden(built_lib, mode, tag, impl):
-    """BASELINE single-layer case: int32 and int8 CRCs of the reference's own kernels."""
+    """The reference's single-layer benchmark case: int32 and int8 CRCs of the reference's own kernels."""
     c = make_golden.conv56_case()
     gold = {}
     for line in open(os.path.join(GOLDEN, f"ref_conv56_{tag}.txt")):

@@ -48,7 +48,7 @@ def test_oracle_batch_independence(oracle):
 
 @pytest.mark.parametrize("mode,tag", [(ffo.CONTRACT, "contract"), (ffo.STRICT, "strict")])
 def test_oracle_single_layer_conv56(mode, tag):
-    """BASELINE single-layer case (conv3x3 64->64, 56x56, batch 8) against the reference's
+    """The reference's single-layer benchmark case (conv3x3 64->64, 56x56, batch 8) against the reference's
     conv2d_i8_nhwc_batched + fused_epilogue_int8 CRCs."""
     import ctypes as C
     ffo.build()
