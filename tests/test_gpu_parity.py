@@ -574,7 +574,8 @@ def test_network_trace_at_batch_64(built_lib, model_root, ffw4, oracle, mode, st
 @pytest.mark.parametrize("seed", [1, 2])
 def test_network_other_model_seeds(built_lib, tmp_path_factory, seed):
     """Synthetic models of seeds 1 and 2 (other weights, scales and calibration tables): every dump
-    point at batch 3 against the C port, embeddings at batch 8 and 40 against port and live reference."""
+    point at batch 3 against the C port, embeddings at batch 8 and 40 against port and live reference, single faces
+    (the layer-chain launch list) against the batch."""
     root = str(tmp_path_factory.mktemp(f"ffmodel_seed{seed}"))
     path = synth.materialize(root, seed)
     orc = ffo.Oracle(path, os.path.join(root, "models", "op_scales.bin"), os.path.join(root, "models", "op_scales_v2.bin"))
@@ -592,7 +593,9 @@ def test_network_other_model_seeds(built_lib, tmp_path_factory, seed):
         assert not first, "; ".join(first)
         got8 = e.embed_batch(faces[:8])
         got40 = e.embed_batch(faces)
+        got1 = [e.embed(faces[i]) for i in (0, 5, 0, 5)]        # single faces: layer chains, eager then captured
     assert np.array_equal(got8, orc.forward(faces[:8], ffo.CONTRACT))
+    assert all(np.array_equal(g, got8[i]) for g, i in zip(got1, (0, 5, 0, 5)))
     assert np.array_equal(got40[:8], got8)
     if ffo.ref_available():
         assert np.array_equal(got40, ffo.ref_embed_many(root, path, faces, batch=8))
@@ -611,7 +614,10 @@ def test_model_from_the_weight_producer(built_lib, tmp_path_factory):
     faces = synth.faces(6, seed=911)
     with ff.FastFace(path, cwd=root, max_batch=6) as e:
         got = e.embed_batch(faces)
-    assert np.array_equal(got, orc.forward(faces, ffo.CONTRACT))
+        one = [e.embed(faces[2]) for _ in range(3)]              # the single-face launch list on real calibrated scales
+    want = orc.forward(faces, ffo.CONTRACT)
+    assert np.array_equal(got, want)
+    assert all(np.array_equal(o, want[2]) for o in one)
 
 
 def test_default_context_picks_the_tiling_from_the_call(built_lib, model_root, ffw4, oracle):
