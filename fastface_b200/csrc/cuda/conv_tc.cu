@@ -197,6 +197,13 @@ TcPlan* ffcu_tc_plan(const ffcu_layer& L, int max_batch, const int8_t* d_in, con
             const int sb = (TC_TILE_M + p->BN / 2) * 128;
             int st = 0;
             p->pair_group = pick_group(sb, &st);
+            if (st == 2 && p->pair_group > 1 && lut_bytes && !genv) {
+                // the fused BN's byte table has taken the third stage: four (or more) stages of one K block keep more
+                // bytes in flight than two of several (measured on the 14x14 / 7x7 residual + BN layers: -1.6 % / -3 %)
+                int st1 = (232448 - fixed) / sb;
+                if (st1 > TC_MAX_STAGES) st1 = TC_MAX_STAGES;
+                if (st1 >= 4) { p->pair_group = 1; st = st1; }
+            }
             if (st >= 2) { p->pair = true; p->pair_stages = st; p->pair_smem_bytes = st * p->pair_group * sb + fixed; }
         }
     }
@@ -365,6 +372,7 @@ int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, co
         const int pairs = prm.tiles_n * ((m_tiles + 1) / 2);
         const int max_pairs = p->n_sm / 2;
         prm.stages = p->pair_stages; prm.group = p->pair_group;
+        { const char* e = getenv("FF_TC_STAGES"); if (e && atoi(e) >= 2 && atoi(e) < prm.stages) prm.stages = atoi(e); }
         int npairs = pairs < max_pairs ? pairs : max_pairs;
         if (npairs > prm.tiles_n) npairs -= npairs % prm.tiles_n;      // a pair keeps one column tile (its BN table)
         const int pgrid = 2 * npairs;
