@@ -567,12 +567,13 @@ ChainPlan* ffcu_chain_plan(int H, int W, int C, const int8_t* d_in, const ChainL
     rows += (P == W + 1 ? 1 : 0);
     if (tiles_n * tiles_m != CHAIN_CLUSTER || P > 256 || P % 8 != 0 || rows > 256) return nullptr;
     const int planes = C / 128;
+    if (planes != 2 && planes != 4) return nullptr;       // the issue loops are built for 256 and 512 channels
     const int plane_bytes = P * rows * 128;
     if (plane_bytes % 1024 != 0) return nullptr;
     const int fixed = 2 * planes * plane_bytes + CHAIN_BN * 256 + 5 * CHAIN_BN * 4 + 512 /* barriers */ + 1024 /* alignment */;
     // Filter taps per stage of the weight ring (1, or 3 where two such stages fit and $FF_CHAIN_TPS=3 asks for it).
     int tps = 1;
-    { const char* e = getenv("FF_CHAIN_TPS"); if (e && (atoi(e) == 1 || atoi(e) == 3)) tps = atoi(e); }
+    { const char* e = getenv("FF_CHAIN_TPS"); if (e && (atoi(e) == 1 || atoi(e) == 3) && planes == 2) tps = atoi(e); }
     while (tps > 1 && (232448 - fixed) / (tps * planes * CHAIN_BN * 128) < 2) tps /= 3;
     const int stage_bytes = tps * planes * CHAIN_BN * 128;
     int stages = (232448 - fixed) / stage_bytes;

@@ -255,7 +255,6 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap mapA, const ChainParams p)
         const uint32_t in_bytes = (uint32_t)((my_hi - my_lo + 1) * p.W * p.C);
         if (p.planes == 2 && p.tps == 3)      chain_issuer_role<2, 3>(p, sh, me, lane, rank, tmem_base, smem_u32(s_a), smem_u32(s_b), tile_line0, in_bytes);
         else if (p.planes == 2)               chain_issuer_role<2, 1>(p, sh, me, lane, rank, tmem_base, smem_u32(s_a), smem_u32(s_b), tile_line0, in_bytes);
-        else if (p.tps == 3)                  chain_issuer_role<4, 3>(p, sh, me, lane, rank, tmem_base, smem_u32(s_a), smem_u32(s_b), tile_line0, in_bytes);
         else                                  chain_issuer_role<4, 1>(p, sh, me, lane, rank, tmem_base, smem_u32(s_a), smem_u32(s_b), tile_line0, in_bytes);
     } else {
         // Epilogue: sixteen warps on the CTA's one tile, warp = (TMEM lane quarter, 16-channel group).
