@@ -45,7 +45,7 @@ METRIC = "faces/sec (IR-ResNet50 INT8, 112x112)"
 # dram__bytes_read + dram__bytes_write of ONE launch of the dominant kernel at batch 1024 (residual + fused-BN
 # variant: input, residual, two outputs, weights) from the ncu capture summarised in the file named here; a
 # constant, valid while that kernel's memory behaviour is unchanged (algorithmic bytes: 206.1 MB)
-DOMINANT_TRAFFIC_BYTES = 167.2e6
+DOMINANT_TRAFFIC_BYTES = 166.3e6
 DOMINANT_TRAFFIC_SOURCE = "constant from profiles/tensor_core_conv_kernels_single_layer_ncu_full.md, case 1 (ncu capture, not measured in this run)"
 # stem (one launch): 150 528 B fp32 face in + 2 x 802 816 B int8 out (conv output and its fused BN)
 STEM_BYTES_PER_FACE = 150528 + 2 * 802816
