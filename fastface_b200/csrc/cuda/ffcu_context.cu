@@ -322,6 +322,11 @@ extern "C" int ffcu_finalize(ffcu_ctx* c)
             if (!M.epi.no_overflow || !S.epi.no_overflow) continue;
             if (sd.bn2_dst_buf >= 0 && !S.bn_lut) continue;
             if (sd.src_buf < 0 || sd.src_buf >= c->n_bufs) continue;
+            // One launch reads both layers' inputs while it writes the shortcut's outputs (and, tile by tile, long after
+            // other tiles' outputs are out): an output that shares a buffer with an input would overwrite pixels other
+            // CTAs have yet to read.  As two launches that sharing is legal (the 3x3 conv's input is dead by then).
+            if (sd.dst_buf == m.src_buf || sd.dst_buf == sd.src_buf || m.dst_buf == m.src_buf || m.dst_buf == sd.src_buf ||
+                (sd.bn2_dst_buf >= 0 && (sd.bn2_dst_buf == m.src_buf || sd.bn2_dst_buf == sd.src_buf))) continue;
             // does anything after the shortcut still read the main path's tensor before it is overwritten?
             int write_main = 0;
             for (size_t j = k + 2; j < c->layers.size(); j++) {

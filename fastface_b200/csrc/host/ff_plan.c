@@ -86,12 +86,23 @@ static int buf_get(bufset* b)
         if (b->ref[i] == 0) { b->ref[i] = 1; if (i + 1 > b->used) b->used = i + 1; return i; }
     return -1;
 }
-/* a free buffer other than x and y (the operands of the launch that will also write it) */
-static int buf_get_not(bufset* b, int x, int y)
+/* a free buffer other than x, y and z (the operands of the launch that will also write it) */
+static int buf_get_not(bufset* b, int x, int y, int z)
 {
     for (int i = 0; i < FF_MAX_BUFS; i++)
-        if (b->ref[i] == 0 && i != x && i != y) { b->ref[i] = 1; if (i + 1 > b->used) b->used = i + 1; return i; }
+        if (b->ref[i] == 0 && i != x && i != y && i != z) { b->ref[i] = 1; if (i + 1 > b->used) b->used = i + 1; return i; }
     return -1;
+}
+
+/* [conv 3x3 stride 2][conv 1x1 stride 2 on the block's input, ADD of the former's output fused] may go out as ONE
+ * launch (conv_tc_sc.cu) that reads the first conv's input while it writes the second conv's outputs: when `sc` is such
+ * a second conv (the layer before it produced its residual), the buffer the first conv reads, else -1.  That buffer is
+ * free by the time the second conv is planned, and must not be handed to either of its outputs. */
+static int pair_input_buf(const ff_plan* p, const ffcu_layer* sc)
+{
+    if (sc < p->layers + 1 || sc->kind != FFCU_CONV || sc->res_buf < 0) return -1;
+    const ffcu_layer* m = sc - 1;
+    return (m->kind == FFCU_CONV && m->dst_buf == sc->res_buf) ? m->src_buf : -1;
 }
 static void buf_hold(bufset* b, int i) { if (i >= 0) b->ref[i]++; }
 static void buf_drop(bufset* b, int i) { if (i >= 0 && b->ref[i] > 0) b->ref[i]--; }
@@ -213,7 +224,7 @@ int ff_plan_build(ff_plan* p, const ff_model* m)
                 return -2;
             }
             l->inv_out = per_channel(p, inv_pc, 1.0f / (eff_next + 1e-9f), Cout);
-            int dst = buf_get(&bs);
+            int dst = buf_get_not(&bs, pair_input_buf(p, l), -1, -1);
             if (dst < 0) { ff_set_error("activation buffer pool exhausted"); return -2; }
             l->dst_buf = dst;
             if (add_fused) { int s = add_idx % FF_ID_SLOTS; buf_drop(&bs, id_buf[s]); id_buf[s] = -1; add_idx++; }
@@ -235,7 +246,7 @@ int ff_plan_build(ff_plan* p, const ff_model* m)
             const int can_fuse = fuse_bn && prev && prev->kind == FFCU_CONV && prev->dst_buf == cur_buf
                                  && prev->bn2_dst_buf < 0 && prev->Cout == C;
             /* a fused second output must not land in a buffer the same launch still reads */
-            int dst = can_fuse ? buf_get_not(&bs, prev->src_buf, prev->res_buf) : buf_get(&bs);
+            int dst = can_fuse ? buf_get_not(&bs, prev->src_buf, prev->res_buf, pair_input_buf(p, prev)) : buf_get(&bs);
             if (dst < 0) { ff_set_error("activation buffer pool exhausted"); return -2; }
             /* The BN input is always the tensor the previous launch wrote; BN is a pure
              * per-element function of that int8 value, so it rides along as a second output of

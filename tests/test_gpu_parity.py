@@ -656,15 +656,21 @@ def test_single_face_layer_chains(built_lib, model_root, ffw4, oracle, monkeypat
     assert counts["0"] == 54 - 4 and counts["1"] == 54 - 4 - 26 - 4 + 2, counts
 
 
-@pytest.mark.parametrize("B", [1, 5, 40, 300])
+@pytest.mark.parametrize("B", [1, 5, 32, 40, 64, 300])
 def test_stride2_conv_and_shortcut_in_one_launch(built_lib, model_root, ffw4, oracle, monkeypatch, B):
     """A down-sampling block's 3x3 stride-2 convolution and its 1x1 stride-2 shortcut (ADD and the next block's BN
     fused) run as ONE launch where the call's column tile is 64 channels wide: all four blocks at small batch, the
-    112x112 one at any batch.  Same bytes as the two launches (FF_FUSE_SC=0) and as the oracle, both epilogue orders."""
+    112x112 one at any batch.  Same bytes as the two launches (FF_FUSE_SC=0) for every face, and as the oracle on a
+    sample, both epilogue orders.  Batches 32 and 64 give the 14x14 block tiles of 2 x 2 pixels x 32 faces and more
+    tiles than CTAs: there a shortcut output sharing a buffer with the 3x3 conv's input (legal as two launches) is
+    overwritten before later tiles have read it; batch 64 with the column tile pinned to 64 fuses all four blocks
+    at several tiles per CTA."""
+    if B == 64:
+        monkeypatch.setenv("FF_TC_BN", "64")
     faces = synth.faces(B, seed=300 + B)
     sample = sorted(set([0, B // 2, B - 1]))
     want = {m: oracle.forward(faces[sample], m) for m in (ffo.CONTRACT, ffo.STRICT)}
-    counts = {}
+    counts, full = {}, {}
     for flag in ("1", "0"):
         monkeypatch.setenv("FF_FUSE_SC", flag)
         with ff.FastFace(ffw4, cwd=model_root, max_batch=B) as e:
@@ -673,9 +679,14 @@ def test_stride2_conv_and_shortcut_in_one_launch(built_lib, model_root, ffw4, or
                 for rep in range(2):
                     got = e.embed_batch(faces) if B > 1 else e.embed(faces[0])[None, :]
                     assert np.array_equal(got[sample], want[mode]), f"FF_FUSE_SC={flag} mode {mode} rep {rep}"
+                    if flag == "1":
+                        full[(mode, rep)] = got
+                    else:
+                        bad = np.nonzero((got != full[(mode, rep)]).any(axis=1))[0]
+                        assert bad.size == 0, f"mode {mode} rep {rep}: faces {bad[:16].tolist()} differ between one and two launches"
             counts[flag] = e.launches_per_forward
     fused_pairs = counts["0"] - counts["1"]                 # the wider the batch, the fewer blocks keep 64-column tiles
-    assert fused_pairs == 4 if B <= 5 else 1 <= fused_pairs <= 4, counts
+    assert fused_pairs == 4 if (B <= 5 or B == 64) else 1 <= fused_pairs <= 4, counts
 
 
 def test_bounded_wait_runs_out_and_the_device_stays_usable(built_lib):

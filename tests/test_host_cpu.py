@@ -122,6 +122,42 @@ def test_synth_model_is_the_177_op_sequence():
     assert abs(macs / 1e9 - 6.3093) < 1e-3
 
 
+def test_launch_list_never_writes_a_buffer_the_same_launch_reads(model_root, ffw4, tmp_path):
+    """Activation buffers are reused by reference count.  No launch may write (output or fused-BN second output) a
+    buffer it reads (input, residual).  A down-sampling block's [conv 3x3 stride 2][conv 1x1 stride 2 + ADD] pair can
+    go out as ONE launch that reads both layers' inputs while it writes the second layer's outputs, tile by tile: for
+    that pair the union counts, although as two launches the first conv's input is dead when the second one writes.
+    (With the shortcut's output in the 3x3 conv's input buffer, a 32-face batch came back with faces 0-7 wrong.)"""
+    import subprocess
+    exe = str(tmp_path / "plan_buffers")
+    host = os.path.join(ROOT, "fastface_b200", "csrc", "host")
+    subprocess.run(["gcc", "-std=c11", "-O1", "-I" + os.path.join(ROOT, "include"), "-I" + host,
+                    os.path.join(ROOT, "tests", "plan_buffers.c"), os.path.join(host, "ff_model.c"),
+                    os.path.join(host, "ff_plan.c"), "-lm", "-o", exe], check=True)
+    mdir = os.path.join(model_root, "models")
+    out = subprocess.run([exe, ffw4, os.path.join(mdir, "op_scales.bin"), os.path.join(mdir, "op_scales_v2.bin")],
+                         check=True, capture_output=True, text=True).stdout
+    layers = []
+    for line in out.splitlines():
+        if line.startswith("L "):
+            f = line.split()
+            layers.append({f[k]: int(f[k + 1]) for k in range(2, len(f), 2)})
+    assert len(layers) == 55                                   # input quantise + 53 convs + FC
+    pairs = 0
+    for i, l in enumerate(layers):
+        reads = {l["src"], l["res"]} - {-1}
+        writes = {l["dst"], l["bn2"]} - {-1}
+        assert not (reads & writes), (i, l)
+        if i and l["kind"] == 1 and l["k"] == 1 and l["stride"] == 2:
+            m = layers[i - 1]
+            assert m["k"] == 3 and m["stride"] == 2 and l["res"] == m["dst"], (i, m, l)
+            pairs += 1
+            assert not (({m["src"], l["src"]}) & (writes | {m["dst"]})), (i, m, l)
+    assert pairs == 4
+    n_bufs = int(out.split("N_BUFS")[1])
+    assert n_bufs == 5
+
+
 def _rss_kb():
     try:
         C.CDLL("libc.so.6").malloc_trim(0)      # hand free heap pages back first: what stays is what is still allocated
