@@ -554,6 +554,42 @@ def test_network_at_the_benchmark_batches(built_lib, model_root, ffw4, oracle, B
         assert not bad, f"faces {bad[:8]} differ from the oracle"
 
 
+SWEEP_BATCHES = [3, 6, 12, 16, 17, 24, 31, 32, 33, 47, 48, 63, 65, 96, 127, 128, 129, 160, 192, 255, 257, 320, 384, 511, 512, 640]
+
+
+@pytest.mark.parametrize("bn", ["auto", "64", "128", "wide"])
+def test_network_batch_sweep_against_the_small_batch_launch_list(built_lib, model_root, ffw4, oracle, monkeypatch, bn):
+    """Tile shape, column-tile width, kernel family, fused launches and graph replay all depend on the batch of
+    the call; the reference treats the faces of a batch independently (arcface_forward_int8_batched.c:402-410).
+    So every batch size must give, face for face, the bytes of the batch-8 launch list (which the tests above
+    pin against the reference): 26 sizes around the tile-batch multiples (16 / 32 / 128), each in a context
+    created for exactly that batch and again as a call of that size inside one batch-640 context.  Then the same with
+    the column tile pinned (FF_TC_BN): 64 puts every down-sampling block on the fused stride-2 + shortcut launch and
+    every layer on the one-CTA kernels at many tiles per CTA, 128 / wide put small batches on the CTA-pair kernels."""
+    nmax = max(SWEEP_BATCHES)
+    faces = synth.faces(nmax, seed=77)
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=8) as small:
+        want = small.embed_batch(faces)
+    if bn != "auto":
+        monkeypatch.setenv("FF_TC_BN", bn)
+    idx = [0, 7, 8, nmax - 1]
+    assert np.array_equal(want[idx], oracle.forward(faces[idx], ffo.CONTRACT))
+    failures = []
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=nmax) as big:
+        for B in SWEEP_BATCHES:
+            with ff.FastFace(ffw4, cwd=model_root, max_batch=B) as e:
+                for rep in range(2):
+                    got = e.embed_batch(faces[:B])
+                    bad = np.flatnonzero((got != want[:B]).any(axis=1))
+                    if bad.size:
+                        failures.append(f"context of batch {B}, call {rep}: {bad.size} faces differ, first {bad[:8].tolist()}")
+            got = big.embed_batch(faces[nmax - B:])          # the last B faces: another offset into the same buffers
+            bad = np.flatnonzero((got != want[nmax - B:]).any(axis=1))
+            if bad.size:
+                failures.append(f"batch-{nmax} context, call of {B}: {bad.size} faces differ, first {bad[:8].tolist()}")
+    assert not failures, "\n".join(failures)
+
+
 @pytest.mark.parametrize("mode,strict", [(ff.EPILOGUE_CONTRACT, False), (ff.EPILOGUE_STRICT, True)])
 def test_network_trace_at_batch_64(built_lib, model_root, ffw4, oracle, mode, strict):
     """Every dump point (int32 accumulators, int8 activations, embeddings) at batch 64, in both epilogue
