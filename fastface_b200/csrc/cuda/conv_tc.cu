@@ -89,8 +89,11 @@ static bool encode_A(const TcPlan* p, TcGeom* g)
 // machine.  A batch that yields fewer tiles than SMs (latency use: one face is 2 row tiles on the
 // 14x14 maps) takes narrower column tiles, so that Cout / BN times as many SMs share the layer's
 // weight stream instead of one SM reading all of it.  $FF_TC_BN: 64 / 128 / 256 pins the tile
-// where it divides Cout; "wide" keeps the widest tile at any batch.
-int ffcu_tc_pick_bn(const ffcu_layer& L, int batch, int device)
+// where it divides Cout; "wide" keeps the widest tile at any batch.  The tile is halved while the launch would
+// fill less than 1 / fill_div of the SMs: half (the default, $FF_TC_BN_FILL) measured best at batch 16-128, where
+// a wider tile on half the SMs beats twice the CTAs each streaming the same activations again; the fused
+// stride-2 + shortcut launch (64 columns only) asks with fill_div = 1, the rule it was measured with.
+int ffcu_tc_pick_bn(const ffcu_layer& L, int batch, int device, int fill_div)
 {
     int bn = L.Cout >= 256 ? 256 : L.Cout;
     const char* bn_env = getenv("FF_TC_BN");
@@ -102,9 +105,12 @@ int ffcu_tc_pick_bn(const ffcu_layer& L, int batch, int device)
     static int n_sm_dev[64] = {};
     int& n_sm = n_sm_dev[device & 63];
     if (!n_sm && cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) n_sm = 148;
+    static int fill_env = -1;
+    if (fill_env < 0) { const char* e = getenv("FF_TC_BN_FILL"); fill_env = (e && atoi(e) >= 1 && atoi(e) <= 4) ? atoi(e) : 2; }
+    if (fill_div < 1) fill_div = fill_env;
     const long long rows = (L.kind == FFCU_FC) ? (long long)batch : (long long)batch * L.Ho * L.Wo;
     const long long m_tiles = (rows + TC_TILE_M - 1) / TC_TILE_M;
-    while (bn > 64 && L.Cout % (bn / 2) == 0 && m_tiles * (L.Cout / bn) < n_sm) bn /= 2;
+    while (bn > 64 && L.Cout % (bn / 2) == 0 && m_tiles * (L.Cout / bn) * fill_div < n_sm) bn /= 2;
     return bn;
 }
 

@@ -478,7 +478,7 @@ static int launch_forward(ffcu_ctx* c, int n)
         }
         {
             DevLayer& M = c->layers[k];
-            if (M.sc && ffcu_tc_pick_bn(M.d, n, c->device) == 64) {
+            if (M.sc && ffcu_tc_pick_bn(M.d, n, c->device, 1) == 64) {
                 // stride-2 conv + the block's shortcut, one launch
                 DevLayer& S = c->layers[k + 1];
                 int8_t* out2 = S.d.bn2_dst_buf >= 0 ? c->bufs[S.d.bn2_dst_buf] : nullptr;
@@ -724,7 +724,7 @@ extern "C" int ffcu_bench_layers(ffcu_ctx* c, const float* host_in, int n, int i
         DevLayer& M = c->layers[k];
         // a stride-2 conv that shares its launch with the block's shortcut at this batch is timed as the forward runs
         // it: the pair's one launch under the conv, nothing under the shortcut
-        const bool pair = M.sc && k + 1 < nl && ffcu_tc_pick_bn(M.d, n, c->device) == 64;
+        const bool pair = M.sc && k + 1 < nl && ffcu_tc_pick_bn(M.d, n, c->device, 1) == 64;
         FFCU_CHECK(cudaEventRecord(ev[2 * k], c->stream));
         for (int it = 0; it < iters && rc == 0; it++) {
             if (pair) {
