@@ -590,6 +590,85 @@ def test_network_batch_sweep_against_the_small_batch_launch_list(built_lib, mode
     assert not failures, "\n".join(failures)
 
 
+def test_single_layer_random_cases(built_lib, monkeypatch):
+    """Sixty seeded random single-layer cases over the network's layer shapes: 3x3 / 1x1, stride 1 / 2, PReLU or
+    residual or neither, batch 1..400 (bounded by 1.5 GMAC per case, a third at powers of two), a third with the
+    widest column tile pinned; int32 accumulators and int8 outputs against the oracle in both epilogue orders."""
+    rng = np.random.default_rng(2024)
+    shapes = [(112, 64, 64), (56, 64, 64), (56, 64, 128), (56, 128, 128), (28, 128, 128), (28, 128, 256), (28, 256, 256),
+              (14, 256, 256), (14, 256, 512), (14, 512, 512), (7, 512, 512)]
+    done = 0
+    while done < 60:
+        H, Cin, Cout = shapes[int(rng.integers(len(shapes)))]
+        k, stride = [(3, 1), (3, 2), (1, 2), (1, 1)][int(rng.integers(4))]
+        if k == 1 and Cin == Cout and stride == 1:
+            continue
+        bmax = max(1, int(1.5e9 / ((H // stride) ** 2 * Cin * Cout * k * k)))
+        B = int(rng.integers(1, min(bmax, 400) + 1))
+        if rng.random() < 0.3:
+            B = int(rng.choice([b for b in (1, 2, 8, 16, 32, 64, 128) if b <= bmax] or [1]))
+        sl = rng.random() < 0.5
+        rs = (not sl) and rng.random() < 0.7
+        L = random_layer(rng, B, H, Cin, Cout, k, stride, sl, rs)
+        if rng.random() < 0.3:
+            monkeypatch.setenv("FF_TC_BN", "wide")
+        else:
+            monkeypatch.delenv("FF_TC_BN", raising=False)
+        for mode in (ff.EPILOGUE_CONTRACT, ff.EPILOGUE_STRICT):
+            acc, out = ff.conv_once(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride=stride, pad=L["pad"],
+                                    slope=L["slope"], res=L["res"], res_scale=L["rs"], mode=mode, impl="tc")
+            acc_o, out_o = oracle_conv(L["x"], L["w"], L["ws"], L["bias"], L["inv"], stride, L["pad"], L["slope"],
+                                       L["res"], L["rs"], mode)
+            tag = f"B={B} H={H} {Cin}->{Cout} k{k} s{stride} slope={sl} res={rs} mode={mode}"
+            msg = describe_mismatch("int32 accumulators, " + tag, acc, acc_o) or describe_mismatch("int8 output, " + tag, out, out_o)
+            assert not msg, msg
+        done += 1
+
+
+def test_random_call_sequence_in_one_context(built_lib, model_root, ffw4):
+    """300 calls of random size (1..300 faces, weighted towards 1-8 and the tile-batch multiples), random offset
+    into the face set, random entry point (fastface_embed, fastface_embed_batch, fastface_embed_batch_u8) and an
+    epilogue-order switch now and then, all through ONE context: the latency path and the three-stream pipeline
+    alternate, graphs are captured and replayed per (size, order, slot), plans and tile geometries are made on
+    first use.  Every result must equal the batch-8 launch list's for the same faces (8-bit pixels and their
+    normalised floats give the same bits)."""
+    N = 300
+    rng = np.random.default_rng(11)
+    pix = rng.integers(0, 256, size=(N, 112, 112, 3), dtype=np.uint8)
+    faces = ((pix.astype(np.float32) - np.float32(127.5)) / np.float32(127.5)).astype(np.float32)
+    want = {}
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=8) as small:
+        for mode in (ff.EPILOGUE_CONTRACT, ff.EPILOGUE_STRICT):
+            small.set_epilogue_mode(mode)
+            want[mode] = small.embed_batch(faces)
+    fails = []
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=N) as e:
+        mode = ff.EPILOGUE_CONTRACT
+        for it in range(300):
+            r = rng.random()
+            if r < 0.3:
+                n = int(rng.integers(1, 9))
+            elif r < 0.5:
+                n = int(rng.choice([16, 17, 31, 32, 33, 64, 128, 129, 256, 300]))
+            else:
+                n = int(rng.integers(1, N + 1))
+            off = int(rng.integers(0, N - n + 1))
+            if rng.random() < 0.15:
+                mode = ff.EPILOGUE_STRICT if mode == ff.EPILOGUE_CONTRACT else ff.EPILOGUE_CONTRACT
+                e.set_epilogue_mode(mode)
+            u8 = rng.random() < 0.4
+            if n == 1 and not u8 and rng.random() < 0.5:
+                got = e.embed(faces[off])[None]
+            elif u8:
+                got = e.embed_batch_u8(pix[off:off + n])
+            else:
+                got = e.embed_batch(faces[off:off + n])
+            bad = np.flatnonzero((got != want[mode][off:off + n]).any(axis=1))
+            if bad.size:
+                fails.append((it, n, off, mode, u8, bad[:6].tolist()))
+    assert not fails, fails[:10]
+
+
 @pytest.mark.parametrize("mode,strict", [(ff.EPILOGUE_CONTRACT, False), (ff.EPILOGUE_STRICT, True)])
 def test_network_trace_at_batch_64(built_lib, model_root, ffw4, oracle, mode, strict):
     """Every dump point (int32 accumulators, int8 activations, embeddings) at batch 64, in both epilogue
