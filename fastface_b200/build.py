@@ -22,7 +22,7 @@ CLI = os.path.join(PKG, "fastface_int8_b200")     # reference-compatible command
 
 HOST_SRCS = ["csrc/host/ff_model.c", "csrc/host/ff_plan.c", "csrc/host/fastface_api.c"]
 CUDA_SRCS = ["csrc/cuda/ffcu_context.cu", "csrc/cuda/kernels_simt.cu", "csrc/cuda/conv_tc.cu",
-             "csrc/cuda/conv_tc_generic.cu", "csrc/cuda/conv_tc_ws.cu", "csrc/cuda/conv_tc_pair.cu", "csrc/cuda/conv_tc_wsp.cu", "csrc/cuda/conv_tc_chain.cu", "csrc/cuda/conv_tc_sc.cu", "csrc/cuda/conv_tc_stem.cu", "csrc/cuda/peak_probe.cu", "csrc/cuda/cos_sim.cu", "csrc/cuda/fc_small_noalloc.cu", "csrc/cuda/winograd_f23.cu"]
+             "csrc/cuda/conv_tc_generic.cu", "csrc/cuda/conv_tc_ws.cu", "csrc/cuda/conv_tc_pair.cu", "csrc/cuda/conv_tc_wsp.cu", "csrc/cuda/conv_tc_chain.cu", "csrc/cuda/conv_tc_sc.cu", "csrc/cuda/conv_tc_fc.cu", "csrc/cuda/conv_tc_stem.cu", "csrc/cuda/peak_probe.cu", "csrc/cuda/cos_sim.cu", "csrc/cuda/fc_small_noalloc.cu", "csrc/cuda/winograd_f23.cu"]
 
 # -fmad=false: the epilogues state every fp32 rounding explicitly; the compiler must not fuse.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

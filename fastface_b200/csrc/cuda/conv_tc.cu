@@ -284,6 +284,69 @@ static int tc_epi_wps(int bn, int tiles_per_cta)
     return 8;
 }
 
+static int g_test_fc_drop_step = -1;
+static long long g_test_fc_wait = 0;
+
+extern "C" void ffcu_test_arm_fc_timeout(int drop_step, long long wait_cycles)
+{
+    g_test_fc_drop_step = drop_step;
+    g_test_fc_wait = wait_cycles;
+}
+
+// The FC as a split-K GEMM (conv_tc_fc.cu): `scratch` = tiles' tickets (FFCU_FC_TC_TICKETS ints) followed by
+// [rows][N] int32 sums, all zero between calls.  Returns 1 when this plan / batch does not take that kernel
+// (the caller then launches the one-CTA-per-tile form), 0 on success, < 0 on error.
+int ffcu_fc_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, float* out, int* scratch, int scratch_rows,
+                      int* d_err, cudaStream_t s)
+{
+    TcPlan* p = const_cast<TcPlan*>(cp);
+    static int on = -1;
+    if (on < 0) { const char* e = getenv("FF_FC_SPLITK"); on = (e && e[0] == '0') ? 0 : 1; }
+    if (!on || !scratch || !p->out_f32 || p->BN != 64 || p->KC != 128 || p->pair || p->ws || p->wsp) return 1;
+    const ffcu_layer& d = p->d;
+    const int kblocks = d.Cin_pad / 128;
+    const int tiles_n = d.Cout / 64, tiles_m = (batch + TC_TILE_M - 1) / TC_TILE_M;
+    if (batch < 1 || batch > p->max_batch || d.Cin_pad % 128 != 0 || tiles_m * TC_TILE_M > scratch_rows ||
+        tiles_m * tiles_n > FFCU_FC_TC_TICKETS) return 1;
+    // K ranges: the most that divide the K loop, leave two K blocks per CTA and keep the grid within the SMs
+    int splits = 1;
+    for (int sp = 2; sp <= kblocks / 2; sp++)
+        if (kblocks % sp == 0 && tiles_n * tiles_m * sp <= p->n_sm) splits = sp;
+    const int bps = kblocks / splits;
+    if (d.Wo != 1 || d.Ho != 1 || d.W != 1 || d.H != 1) return 1;
+    const int TW = 1, TH = 1, TB = TC_TILE_M;              // a row tile = 128 consecutive faces
+    TcGeom* g = nullptr;
+    for (int i = 0; i < p->n_geoms; i++)
+        if (p->geoms[i].TW == TW && p->geoms[i].TH == TH && p->geoms[i].TB == TB) g = &p->geoms[i];
+    if (!g) {
+        if (p->n_geoms == 8) p->n_geoms = 0;
+        g = &p->geoms[p->n_geoms];
+        g->TW = TW; g->TH = TH; g->TB = TB;
+        if (!encode_A(p, g)) return -1;
+        p->n_geoms++;
+    }
+    FcTcParams prm = {};
+    prm.w_scale = t.w_scale; prm.bias = t.bias; prm.out = out;
+    prm.tickets = scratch; prm.sums = scratch + FFCU_FC_TC_TICKETS; prm.err = d_err;
+    prm.batch = batch; prm.N = d.Cout;
+    prm.tiles_n = tiles_n; prm.tiles_m = tiles_m; prm.splits = splits; prm.blocks_per_split = bps;
+    prm.group = (bps % 2 == 0) ? 2 : 1;
+    const int sub = (TC_TILE_M + 64) * 128;
+    int st = (232448 - (int)sizeof(TcShared) - 2048) / (prm.group * sub);
+    if (st > TC_MAX_STAGES) st = TC_MAX_STAGES;
+    if (st > bps / prm.group) st = bps / prm.group;
+    if (st < 1) return 1;
+    prm.stages = st;
+    prm.drop_step = -1; prm.wait_cycles = TC_WAIT_CYCLES;
+    if (g_test_fc_drop_step >= 0) {                          // armed for this one launch by the timeout test
+        prm.drop_step = g_test_fc_drop_step;
+        if (g_test_fc_wait > 0) prm.wait_cycles = g_test_fc_wait;
+        g_test_fc_drop_step = -1; g_test_fc_wait = 0;
+    }
+    const int smem = st * prm.group * sub + (int)sizeof(TcShared) + 2048;
+    return tc_launch_fc(mode, tiles_n * tiles_m * splits, smem, s, g->mapA, p->mapB, prm);
+}
+
 int ffcu_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t, const int8_t* res,
                    int32_t* acc_out, void* out, int8_t* out_bn2, int* d_err, cudaStream_t s)
 {

@@ -834,6 +834,21 @@ struct ScParams {
 int tc_launch_sc(int kc, int mode, int grid, int smem, cudaStream_t s, const CUtensorMap& mapA, const CUtensorMap& mapB,
                  const CUtensorMap& mapA2, const CUtensorMap& mapB2, const TcParams& prm, const ScParams& q);
 
+// Split-K FC (conv_tc_fc.cu)
+struct FcTcParams {
+    const float* w_scale; const float* bias;
+    float* out;              // [batch][N] f32
+    int* sums;               // [rows][N] int32 partial sums, zero between calls
+    int* tickets;            // [tiles_m * tiles_n] arrival counters, zero between calls
+    int* err;
+    int batch, N;
+    int tiles_n, tiles_m, splits, blocks_per_split;   // grid = tiles_n * tiles_m * splits; K blocks of 128 per CTA
+    int stages, group;
+    int drop_step;           // >= 0: the producer leaves out this step's activation box (timeout test); -1 otherwise
+    long long wait_cycles;   // limit of every barrier wait
+};
+int tc_launch_fc(int mode, int grid, int smem, cudaStream_t s, const CUtensorMap& mapA, const CUtensorMap& mapB, const FcTcParams& prm);
+
 // Layer chain (conv_tc_chain.cu)
 #define CHAIN_CLUSTER 8
 #define CHAIN_BN 64

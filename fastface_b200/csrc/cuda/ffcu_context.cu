@@ -63,6 +63,9 @@ struct ffcu_ctx {
     int mode = 1;
     int force_simt = 0;          // FF_CONV_IMPL=simt: every conv on the CUDA-core kernel
     int no_fc_small = 0;         // FF_FC_SMALL=0: small batches take the large-batch FC path too
+    int fc_small_max = 4;        // largest batch the CUDA-core FC kernel takes ($FF_FC_SMALL_MAX, at most 16): measured quicker than the split-K tensor-core FC up to 3 faces, equal at 4, slower from 6
+    int* d_fc_tc_scratch = nullptr; // split-K tensor-core FC: FFCU_FC_TC_TICKETS counters + int32 [fc_tc_rows][512] sums (kept zero between calls)
+    int fc_tc_rows = 0;
     int launches = 0;
     bool finalized = false;
     // The forward is captured once per (batch, mode, input kind, input/output slot) into a CUDA
@@ -131,12 +134,19 @@ extern "C" ffcu_ctx* ffcu_create(int device, int max_batch, int n_bufs, size_t b
     ok = ok && cudaMalloc(&c->d_err, sizeof(int)) == cudaSuccess;
     ok = ok && cudaMalloc(&c->d_fc_scratch, (FFCU_FC_SMALL_TICKETS + FFCU_FC_SMALL_MAX_BATCH * 512) * sizeof(int)) == cudaSuccess;
     if (ok) cudaMemset(c->d_fc_scratch, 0, (FFCU_FC_SMALL_TICKETS + FFCU_FC_SMALL_MAX_BATCH * 512) * sizeof(int));
+    c->fc_tc_rows = (max_batch + 127) / 128 * 128;
+    {
+        const size_t nb = ((size_t)FFCU_FC_TC_TICKETS + (size_t)c->fc_tc_rows * 512) * sizeof(int);
+        ok = ok && cudaMalloc(&c->d_fc_tc_scratch, nb) == cudaSuccess;
+        if (ok) cudaMemset(c->d_fc_tc_scratch, 0, nb);
+    }
     ok = ok && cudaHostAlloc(&c->h_err, sizeof(int), cudaHostAllocDefault) == cudaSuccess;
     ok = ok && cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess;
     if (ok) { cudaMemset(c->d_err, 0, sizeof(int)); *c->h_err = 0; }
     const char* impl = getenv("FF_CONV_IMPL");
     c->force_simt = (impl && strcmp(impl, "simt") == 0) ? 1 : 0;
     { const char* e = getenv("FF_FC_SMALL"); c->no_fc_small = (e && e[0] == '0') ? 1 : 0; }
+    { const char* e = getenv("FF_FC_SMALL_MAX"); if (e && atoi(e) >= 0 && atoi(e) <= FFCU_FC_SMALL_MAX_BATCH) c->fc_small_max = atoi(e); }
     { const char* e = getenv("FF_GRAPH_MAX_BATCH"); if (e && atoi(e) > 0) c->graph_max_batch = atoi(e); }
     { const char* e = getenv("FF_GRAPH"); if (e && e[0] == '0') c->graph_max_batch = 0; }
     { const char* e = getenv("FF_CHAIN"); c->no_chain = (e && e[0] == '0') ? 1 : 0; }
@@ -173,7 +183,7 @@ extern "C" void ffcu_destroy(ffcu_ctx* c)
         if (c->ev_compute_done[k]) cudaEventDestroy(c->ev_compute_done[k]);
         if (c->ev_out_copied[k]) cudaEventDestroy(c->ev_out_copied[k]);
     }
-    cudaFree(c->d_err); cudaFree(c->d_fc_scratch);
+    cudaFree(c->d_err); cudaFree(c->d_fc_scratch); cudaFree(c->d_fc_tc_scratch);
     if (c->h_err) cudaFreeHost(c->h_err);
     if (c->stream) cudaStreamDestroy(c->stream);
     if (c->s_in) cudaStreamDestroy(c->s_in);
@@ -399,10 +409,15 @@ static int launch_layer(ffcu_ctx* c, size_t k, int n, int32_t* acc_dbg, bool unf
         return ffcu_launch_bn(c->bufs[d.src_buf], c->bufs[d.dst_buf], (size_t)n * d.H * d.W, d.Cout,
                               L.tab[5], L.tab[6], L.tab[7], L.tab[4], s);
     case FFCU_FC:
-        if (n <= FFCU_FC_SMALL_MAX_BATCH && d.Cout <= 512 && !c->no_fc_small)
+        if (n <= c->fc_small_max && d.Cout <= 512 && !c->no_fc_small)
             return ffcu_launch_fc_small(c->bufs[d.src_buf], L.w, L.epi.w_scale, L.epi.bias, n, d.Cout, d.Cin, c->mode,
                                         c->d_fc_scratch, c->d_out, s);
-        if (L.tc) return ffcu_tc_launch(tc_plan_for(c, L, n), n, c->mode, L.epi, nullptr, nullptr, c->d_out, nullptr, c->d_err, s);
+        if (L.tc) {
+            TcPlan* fp = tc_plan_for(c, L, n);
+            const int rc = d.Cout == 512 ? ffcu_fc_tc_launch(fp, n, c->mode, L.epi, c->d_out, c->d_fc_tc_scratch, c->fc_tc_rows, c->d_err, s) : 1;
+            if (rc <= 0) return rc;
+            return ffcu_tc_launch(fp, n, c->mode, L.epi, nullptr, nullptr, c->d_out, nullptr, c->d_err, s);
+        }
         return ffcu_launch_fc_simt(c->bufs[d.src_buf], L.w, L.epi.w_scale, L.epi.bias, n, d.Cout, d.Cin,
                                    c->mode, c->d_out, s);
     }
@@ -619,6 +634,9 @@ extern "C" int ffcu_wait(ffcu_ctx* c)
         ffcu_set_error("device reported error word %d (a bounded wait inside a kernel ran out)", *c->h_err);
         int e = *c->h_err;
         cudaMemsetAsync(c->d_err, 0, sizeof(int), c->stream);
+        // a launch that gave up may have left partial sums or tickets behind
+        cudaMemsetAsync(c->d_fc_scratch, 0, (FFCU_FC_SMALL_TICKETS + FFCU_FC_SMALL_MAX_BATCH * 512) * sizeof(int), c->stream);
+        cudaMemsetAsync(c->d_fc_tc_scratch, 0, ((size_t)FFCU_FC_TC_TICKETS + (size_t)c->fc_tc_rows * 512) * sizeof(int), c->stream);
         return 1000 + e;
     }
     return 0;

@@ -216,6 +216,9 @@ StemTcPlan* ffcu_stem_tc_plan(int max_batch, const int8_t* d_wk, bool has_bn2, i
 void ffcu_stem_tc_free(StemTcPlan* p);
 // Column-tile width (64 / 128 / 256) for a call of `batch` faces, and the plan for one width.
 int     ffcu_tc_pick_bn(const ffcu_layer& L, int batch, int device, int fill_div = 0);
+#define FFCU_FC_TC_TICKETS 256      // (128-face row tile, 64-column tile) pairs the split-K FC can count: 4096 faces x 512 outputs
+int     ffcu_fc_tc_launch(const TcPlan* p, int batch, int mode, const EpiTables& t, float* out, int* scratch, int scratch_rows,
+                          int* d_err, cudaStream_t s);
 // NULL when the layer shape is not covered by the tensor-core kernels.
 int ffcu_stem_fused_launch(const StemTcPlan* p, const void* in_any, int in_u8, const float* inv3, int batch, int mode,
                            const EpiTables& t, int8_t* out, int8_t* out_bn2, int* d_err, cudaStream_t s);

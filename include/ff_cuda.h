@@ -153,6 +153,10 @@ void ffcu_test_arm_timeout(int drop_stage, long long full_wait_cycles);
  * sends, give up one limit later; all eight meet at the final cluster barrier, free their tensor memory
  * and return; the call reports 1000 + the error word.  Disarms itself after that one launch. */
 void ffcu_test_arm_chain_timeout(int drop_step, long long wait_cycles);
+/* The same for the split-K FC kernel: the activation box of K step drop_step never arrives in any CTA of the next FC
+ * launch and every barrier wait of that launch is limited to wait_cycles; every CTA gives up, takes no ticket, frees
+ * its tensor memory and returns; the call reports 1000 + the error word and clears the kernel's scratch sums. */
+void ffcu_test_arm_fc_timeout(int drop_step, long long wait_cycles);
 
 /* Small-batch FC (batch <= 16, N <= 512) that allocates nothing: no counterpart in the
  * reference.  For callers that hold device buffers but cannot call cudaMalloc -- a serving loop

@@ -922,17 +922,83 @@ def test_network_with_the_large_batch_tiling(built_lib, model_root, ffw4, oracle
 
 
 def test_fc_paths(built_lib, model_root, ffw4, oracle, monkeypatch):
-    """The FC runs as a split-K CUDA-core kernel for batch <= 16 and on the tensor cores above;
-    both match the reference's matvec, and FF_FC_SMALL=0 sends a small batch down the large path."""
+    """The FC runs as a split-K CUDA-core kernel for a handful of faces (up to 4 by default, up to 16 with
+    FF_FC_SMALL_MAX) and on the tensor cores above; all match the reference's matvec, FF_FC_SMALL=0 sends a small
+    batch down the large path, FF_FC_SPLITK=0 takes the one-CTA-per-tile tensor-core form."""
     faces = synth.faces(20, seed=61)
     want = oracle.forward(faces, ffo.CONTRACT)
     with ff.FastFace(ffw4, cwd=model_root, max_batch=20) as e:
         assert np.array_equal(e.embed_batch(faces), want)            # tensor-core FC
-        assert np.array_equal(e.embed_batch(faces[:5]), want[:5])    # split-K FC
-        assert np.array_equal(e.embed_batch(faces[:5]), want[:5])    # scratch accumulator left clean
+        for n in (5, 3, 3, 16, 4):                                   # tensor-core and CUDA-core FC in turn, scratch left clean
+            assert np.array_equal(e.embed_batch(faces[:n]), want[:n]), n
+    monkeypatch.setenv("FF_FC_SMALL_MAX", "16")
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=20) as e:
+        for n in (5, 16, 9, 20, 16):                                 # CUDA-core FC up to 16 faces
+            assert np.array_equal(e.embed_batch(faces[:n]), want[:n]), n
+    monkeypatch.delenv("FF_FC_SMALL_MAX")
     monkeypatch.setenv("FF_FC_SMALL", "0")
     with ff.FastFace(ffw4, cwd=model_root, max_batch=5) as e:
         assert np.array_equal(e.embed_batch(faces[:5]), want[:5])
+        assert np.array_equal(e.embed_batch(faces[:2]), want[:2])
+    monkeypatch.setenv("FF_FC_SPLITK", "0")
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=20) as e:
+        assert np.array_equal(e.embed_batch(faces), want)
+        assert np.array_equal(e.embed_batch(faces[:2]), want[:2])
+
+
+def test_fc_split_k_on_tensor_cores(built_lib, model_root, ffw4, oracle, monkeypatch):
+    """Above 16 faces the FC runs as a split-K tensor-core GEMM: each (128-face, 64-output) tile is cut into K
+    ranges, one CTA each; the CTAs add int32 partial sums into a scratch array and the one that takes a tile's last
+    ticket writes the floats and leaves sums and ticket zero.  Same bytes as the one-CTA-per-tile form
+    (FF_FC_SPLITK=0) for every face and as the oracle on a sample, in both epilogue orders, at batches that give one
+    row tile, a ragged second one, several row tiles (fewer K ranges), and repeated calls (clean scratch), also
+    inside a larger context (rows of other faces in the tile) and after a single face and a small batch."""
+    nmax = 700
+    faces = synth.faces(nmax, seed=71)
+    sample = [0, 16, 17, 127, 128, 129, 299, nmax - 1]
+    want = {m: oracle.forward(faces[sample], m) for m in (ffo.CONTRACT, ffo.STRICT)}
+    ref = {}
+    monkeypatch.setenv("FF_FC_SPLITK", "0")
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=nmax) as e:
+        for mode in (ffo.CONTRACT, ffo.STRICT):
+            e.set_epilogue_mode(mode)
+            ref[mode] = e.embed_batch(faces)
+            assert np.array_equal(ref[mode][sample], want[mode])
+    monkeypatch.delenv("FF_FC_SPLITK")
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=nmax) as e:
+        for mode in (ffo.CONTRACT, ffo.STRICT):
+            e.set_epilogue_mode(mode)
+            for B in (17, 32, 128, 129, 130, 256, 300, 700, 1, 5, 33, 700):
+                for rep in range(2):
+                    got = e.embed_batch(faces[nmax - B:]) if B > 1 else e.embed(faces[nmax - 1])[None, :]
+                    bad = np.flatnonzero((got != ref[mode][nmax - B:]).any(axis=1))
+                    assert bad.size == 0, f"mode {mode} batch {B} call {rep}: faces {bad[:8].tolist()} differ"
+    for B in (17, 128, 200):
+        with ff.FastFace(ffw4, cwd=model_root, max_batch=B) as e:
+            got = e.embed_batch(faces[:B])
+            assert np.array_equal(got, ref[ffo.CONTRACT][:B]), B
+
+
+def test_fc_split_k_bounded_waits_run_out_and_the_device_stays_usable(built_lib, model_root, ffw4):
+    """The timeout path of the split-K FC kernel, without faulting anything: the hook makes every CTA's producer leave
+    out the activation box of one K step of ONE launch and limits that launch's waits to two million cycles.  Every
+    CTA gives up, takes no ticket and returns; the call reports 1000 + an error word, the library clears the scratch
+    sums, and the next calls are bit-exact."""
+    lib = ff.load_library()
+    lib.ffcu_test_arm_fc_timeout.restype = None
+    lib.ffcu_test_arm_fc_timeout.argtypes = [C.c_int, C.c_longlong]
+    faces = synth.faces(40, seed=72)
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=8) as small:
+        want = small.embed_batch(faces)
+    with ff.FastFace(ffw4, cwd=model_root, max_batch=40) as e:
+        assert np.array_equal(e.embed_batch(faces), want)
+        lib.ffcu_test_arm_fc_timeout(1, 2_000_000)
+        with pytest.raises(RuntimeError) as ei:
+            e.embed_batch(faces)
+        assert any(f"rc={1000 + k}" in str(ei.value) for k in (1, 2, 3, 4)), str(ei.value)
+        for _ in range(2):
+            assert np.array_equal(e.embed_batch(faces), want)
+        assert np.array_equal(e.embed_batch(faces[:3]), want[:3])
 
 
 def test_chunking_and_determinism(built_lib, model_root, ffw4, oracle):
