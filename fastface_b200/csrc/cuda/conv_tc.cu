@@ -312,6 +312,7 @@ int ffcu_fc_tc_launch(const TcPlan* cp, int batch, int mode, const EpiTables& t,
     int splits = 1;
     for (int sp = 2; sp <= kblocks / 2; sp++)
         if (kblocks % sp == 0 && tiles_n * tiles_m * sp <= p->n_sm) splits = sp;
+    { const char* e = getenv("FF_FC_SPLITS"); const int v = e ? atoi(e) : 0; if (v >= 1 && v <= kblocks / 2 && kblocks % v == 0) splits = v; }
     const int bps = kblocks / splits;
     if (d.Wo != 1 || d.Ho != 1 || d.W != 1 || d.H != 1) return 1;
     const int TW = 1, TH = 1, TB = TC_TILE_M;              // a row tile = 128 consecutive faces
